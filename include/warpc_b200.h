@@ -1,0 +1,117 @@
+/* warpc_b200 -- C ABI of the B200-native fp16-in / fp32-out GEMM  C[M,N] = A[M,K] * Bt[N,K]^T.
+ *
+ * The reference (silares-ai/Warpc-public-release) has no C FFI: its operator surface is the
+ * `warpc gemm M N K` command (backend/warpc.ml:19-52), the launch header that command writes
+ * (backend/compile.ml:165-186, parsed by backend/node/header.py:12-32) and the launch / check /
+ * time harness backend/node/run_tma.py:47-216.  This library is what a binding for that surface
+ * calls: the rule and the header as functions, and the kernel behind a plan / launch pair.
+ *
+ * Conventions: every function returns 0 on success, > 0 a cudaError_t / CUresult value,
+ * < 0 a library error (WG_E_*).  Callers own A, Bt and C; a plan owns its tensor maps,
+ * hand-off flags and status words.  A plan is used from one host thread and one stream at a
+ * time.  Nothing synchronises unless stated.  There is no CPU fallback: without a CUDA device
+ * every function that touches the GPU returns an error.
+ */
+#ifndef WARPC_B200_H
+#define WARPC_B200_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  WG_OK = 0,
+  WG_E_SHAPE = -1,       /* the rule has no program for the shape (reference: OCaml failwith) */
+  WG_E_VARIANT = -2,     /* inconsistent explicit variant (reference: gemm_swapped.ml:32-48 failwith) */
+  WG_E_ARG = -3,         /* null / misaligned pointer, bad size, buffer too small */
+  WG_E_NOKERNEL = -4,    /* no compiled kernel realises the variant */
+  WG_E_DEVICE_WAIT = -5, /* a bounded device-side wait gave up; see wg_last_device_status */
+  WG_E_NODRIVER = -6,    /* CUDA driver entry points not available (no GPU / no libcuda) */
+  WG_E_LIMIT = -7        /* size beyond a stated maximum */
+};
+
+enum { WG_PROG_SWAPPED = 0, WG_PROG_PAIR = 1, WG_PROG_ONE = 2 };
+enum { WG_SM_100A = 100, WG_SM_103A = 103 };
+
+/* What the reference's rule decides for a shape, plus the geometry its kernel builder
+ * derives from that decision.  Rule fields: backend/programs.ml:46-80 (the optional
+ * arguments of Gemm_swapped.build, backend/gemm_swapped.mli:25-42).  Derived fields:
+ * backend/gemm_swapped.ml:50-108. */
+typedef struct wg_variant {
+  int prog;                 /* WG_PROG_* */
+  int tile_m, tile_n, tile_k, depth;
+  int cluster_n;            /* pairs along the rows that share a B^T tile in the reference */
+  int clc, ask_ahead, direct, serpentine, group;
+  int streamk, split, split_grid, split_add, late_launch;
+  int bufs;                 /* 0 = derive */
+  /* derived, as the reference's builder computes them */
+  int reps, atom_m, tmem_cols, nbuf, alloc_cols;
+  int tiles_m, tiles_n, total_tiles, ctas, grid, persistent, kt;
+  int a_box_rows, bt_box_rows, stage_bytes, tx_bytes, ref_dynsmem, ref_mbarriers, nflags;
+} wg_variant;
+
+/* How this library launches a variant (its own kernel's contract, what wg_header prints). */
+typedef struct wg_launch_info {
+  int kernel_id;           /* index into the compiled kernel table */
+  int cg, tile_m, tile_n, direct, epi_rows;
+  int grid, cluster, threads, dynsmem, mbarriers, tmem_cols;
+  int sched;               /* 0 one tile a CTA, 1 fixed grid by stride, 2 cluster launch control, 3 split-K over the grid, 4 stream-K */
+  int depth, nbuf, group, cl_n, serpentine, ask_ahead, split, nflags;
+  int a_box_rows, bt_box_rows, c_box_rows;
+} wg_launch_info;
+
+/* `warpc gemm M N K`: the program chosen for a shape (backend/programs.ml:46-80).
+ * sm is WG_SM_100A or WG_SM_103A (backend/warpc.ml:32-36). */
+int wg_choose(int M, int N, int K, int sm, wg_variant* out);
+
+/* `warpc swapped M N K TM TN DEPTH [flags]`, `warpc pair ...`, `warpc one ...`
+ * (backend/warpc.ml:21-28): fill the rule fields of *v (zero the rest), then derive.
+ * Returns WG_E_VARIANT where the reference's builder refuses the combination. */
+int wg_derive(int M, int N, int K, wg_variant* v);
+
+/* The kernel of this library that realises a variant, and its launch geometry. */
+int wg_realise(const wg_variant* v, int M, int N, int K, wg_launch_info* out);
+
+/* The launch header (`.kernel/.sm/.threads/.smem/.dynsmem/.tile/.tmap/.ptr/.grid/.mbarriers/
+ * .cluster/.tcgen05/.params`, backend/compile.ml:171-186) as text; returns the length
+ * written (excluding the terminator) or WG_E_ARG when cap is too small. */
+int wg_header(const wg_variant* v, int M, int N, int K, char* buf, size_t cap);
+
+/* A plan: tensor maps for dA (M x K fp16), dBt (N x K fp16), dC (M x N fp32), all row-major,
+ * 16-byte aligned device pointers on `device`; hand-off flags and status words allocated and
+ * zeroed once (backend/node/run_tma.py:88-113).  timeout_ms bounds every device-side wait
+ * (0 = the default, 2000 ms). */
+int wg_plan_create(int device, const wg_variant* v, int M, int N, int K, const void* dA, const void* dBt, void* dC,
+                   void** plan);
+int wg_plan_set_timeout_ms(void* plan, unsigned ms);
+int wg_plan_info(void* plan, wg_launch_info* out);
+/* One launch on `cuda_stream` (a cudaStream_t, NULL = the default stream); asynchronous. */
+int wg_launch(void* plan, void* cuda_stream);
+/* Synchronise the device and read the status words: out[0] = 0 when every launch so far ran
+ * to completion, else the wait that gave up (role code), out[1] its detail, out[2] the CTA,
+ * out[3] the parity / target.  Returns WG_E_DEVICE_WAIT when out[0] != 0. */
+int wg_last_device_status(void* plan, unsigned out[4]);
+/* Re-zero the flags and status words (after a launch that gave up). */
+int wg_plan_reset(void* plan);
+int wg_plan_destroy(void* plan);
+
+/* Host-buffer entry: a plan that owns device copies of A, Bt and C.  wg_host_run copies
+ * hA, hBt in, launches, copies C out to hC and synchronises -- the call the reference's
+ * harness makes around a launch (backend/node/run_tma.py:68-70, 142). */
+int wg_host_plan_create(int device, const wg_variant* v, int M, int N, int K, void** plan);
+int wg_host_run(void* plan, const void* hA, const void* hBt, void* hC);
+/* device pointers of a host plan: which = 0 A, 1 Bt, 2 C */
+void* wg_host_plan_buffer(void* plan, int which);
+
+/* Number of compiled kernels and the name of each (for listing). */
+int wg_kernel_count(void);
+const char* wg_kernel_name(int kernel_id);
+
+const char* wg_strerror(int code);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

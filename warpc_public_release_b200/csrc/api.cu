@@ -1,0 +1,287 @@
+// C ABI over the kernels: plans (tensor maps, flags, status words) and launches.
+// The harness this replaces is backend/node/run_tma.py:47-175 (encode the maps the header
+// names, allocate and zero the kernel's own buffers once, launch with the cluster
+// attribute) and backend/node/clusterlaunch.py:34-51.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <new>
+
+#include "../../include/warpc_b200.h"
+#include "gemm_kernel.cuh"
+#include "kernel_table.h"
+
+namespace {
+
+using namespace wb;
+
+// ------------------------------------------------------------------ kernel table
+template <class C>
+wb_kernel_entry entry(int id, const char* name) {
+  wb_kernel_entry e;
+  e.id = id, e.cg = C::CG, e.tile_m = C::TM, e.tile_n = C::TN, e.direct = C::DIRECT ? 1 : 0;
+  e.epi_rows = C::EPI_ROWS, e.ncols = C::NCOLS, e.stage_bytes = C::STAGE_BYTES;
+  e.smem_fixed = C::smem_bytes(0);
+  e.name = name;
+  e.fn = reinterpret_cast<const void*>(&gemm_kernel<C>);
+  return e;
+}
+
+#define WB_KERNELS(X)                       \
+  X(0, 1, 128, 128, true, "one_128x128_direct")      \
+  X(1, 2, 128, 64, true, "pair_128x64_direct")       \
+  X(2, 2, 128, 64, false, "pair_128x64_staged")      \
+  X(3, 2, 128, 128, true, "pair_128x128_direct")     \
+  X(4, 2, 128, 128, false, "pair_128x128_staged")    \
+  X(5, 2, 192, 128, true, "pair_192x128_direct")     \
+  X(6, 2, 192, 128, false, "pair_192x128_staged")    \
+  X(7, 2, 256, 128, true, "pair_256x128_direct")     \
+  X(8, 2, 256, 128, false, "pair_256x128_staged")    \
+  X(9, 2, 256, 256, true, "pair_256x256_direct")     \
+  X(10, 2, 256, 256, false, "pair_256x256_staged")   \
+  X(11, 2, 256, 64, false, "pair_256x64_staged")     \
+  X(12, 2, 128, 256, false, "pair_128x256_staged")
+
+const wb_kernel_entry* table() {
+  static wb_kernel_entry t[] = {
+#define X(id, cg, tm, tn, direct, name) entry<Cfg<cg, tm, tn, direct>>(id, name),
+      WB_KERNELS(X)
+#undef X
+  };
+  return t;
+}
+constexpr int kKernels = 13;
+
+// ------------------------------------------------------------------ driver entry points
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// A row-major rows x cols matrix, box = box_rows x box_cols, 128-byte swizzle, zero fill
+// out of bounds -- the map backend/node/run_tma.py:32-45 encodes from a `.tmap` line.
+int encode_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem, const void* ptr, int rows, int cols, int box_rows, int box_cols) {
+  EncodeTiledFn enc = encode_tiled();
+  if (!enc) return WG_E_NODRIVER;
+  cuuint64_t dims[2] = {cuuint64_t(cols), cuuint64_t(rows)};
+  cuuint64_t strides[1] = {cuuint64_t(cols) * cuuint64_t(elem)};
+  cuuint32_t box[2] = {cuuint32_t(box_cols), cuuint32_t(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? WG_OK : int(r);
+}
+
+struct Plan {
+  int device = 0;
+  wg_variant v;
+  wg_launch_info li;
+  const wb_kernel_entry* k = nullptr;
+  CUtensorMap map_a, map_b, map_c;
+  KParams p;
+  uint32_t* d_flags = nullptr;
+  uint32_t* d_status = nullptr;
+  size_t flag_bytes = 0;
+  // host plans own these
+  void *dA = nullptr, *dBt = nullptr, *dC = nullptr;
+  bool owns_buffers = false;
+  int M = 0, N = 0, K = 0;
+};
+
+#define WG_CUDA(call)                          \
+  do {                                         \
+    cudaError_t e_ = (call);                   \
+    if (e_ != cudaSuccess) return int(e_);     \
+  } while (0)
+
+int fill_plan(Plan* pl, int device, const wg_variant* v, int M, int N, int K, const void* dA, const void* dBt, void* dC) {
+  if (!v || !dA || !dBt || !dC) return WG_E_ARG;
+  if ((reinterpret_cast<uintptr_t>(dA) | reinterpret_cast<uintptr_t>(dBt) | reinterpret_cast<uintptr_t>(dC)) & 15u) return WG_E_ARG;
+  if (M <= 0 || N <= 0 || K <= 0 || K % 64 != 0 || N % 4 != 0) return WG_E_ARG;
+  pl->device = device, pl->v = *v, pl->M = M, pl->N = N, pl->K = K;
+  int r = wg_realise(v, M, N, K, &pl->li);
+  if (r != WG_OK) return r;
+  const wg_launch_info& li = pl->li;
+  pl->k = wb_kernel_at(li.kernel_id);
+  WG_CUDA(cudaSetDevice(device));
+  std::memset(&pl->map_c, 0, sizeof pl->map_c);
+  if ((r = encode_2d(&pl->map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, dA, M, K, li.a_box_rows, 64)) != WG_OK) return r;
+  if ((r = encode_2d(&pl->map_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, dBt, N, K, li.bt_box_rows, 64)) != WG_OK) return r;
+  if (!li.direct && (r = encode_2d(&pl->map_c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dC, M, N, li.c_box_rows, 32)) != WG_OK) return r;
+  pl->flag_bytes = size_t(li.nflags > 0 ? li.nflags : 1) * sizeof(uint32_t);
+  WG_CUDA(cudaMalloc(&pl->d_flags, pl->flag_bytes));
+  WG_CUDA(cudaMalloc(&pl->d_status, 8 * sizeof(uint32_t)));
+  WG_CUDA(cudaMemset(pl->d_flags, 0, pl->flag_bytes));
+  WG_CUDA(cudaMemset(pl->d_status, 0, 8 * sizeof(uint32_t)));
+  KParams& p = pl->p;
+  std::memset(&p, 0, sizeof p);
+  p.M = M, p.N = N, p.K = K;
+  p.kt = K / 64;
+  const int tiles_m = (M + li.tile_m - 1) / li.tile_m, tiles_n = (N + li.tile_n - 1) / li.tile_n;
+  p.ntiles = tiles_m * tiles_n;
+  p.cl_n = li.cl_n > 0 ? li.cl_n : 1;
+  p.group = li.group > 0 ? li.group : 1;
+  p.serp = li.serpentine;
+  p.depth = li.depth, p.nbuf = li.nbuf, p.sched = li.sched, p.ask_ahead = li.ask_ahead;
+  p.split = li.split;
+  if (li.sched == SCHED_STREAMK) {
+    const int clusters = li.grid / li.cluster, units = (p.ntiles / li.cluster) * p.kt;
+    p.sk_clusters = clusters, p.sk_q = units / clusters, p.sk_r = units % clusters;
+  }
+  p.C = static_cast<float*>(dC);
+  p.flags = pl->d_flags;
+  p.status = pl->d_status;
+  p.timeout_ns = 2000ull * 1000ull * 1000ull;
+  WG_CUDA(cudaFuncSetAttribute(pl->k->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, li.dynsmem));
+  return WG_OK;
+}
+
+}  // namespace
+
+const wb_kernel_entry* wb_find_kernel(int cg, int tile_m, int tile_n, int direct) {
+  const wb_kernel_entry* t = table();
+  for (int i = 0; i < kKernels; ++i)
+    if (t[i].cg == cg && t[i].tile_m == tile_m && t[i].tile_n == tile_n && t[i].direct == (direct ? 1 : 0)) return &t[i];
+  return nullptr;
+}
+const wb_kernel_entry* wb_kernel_at(int id) { return (id >= 0 && id < kKernels) ? &table()[id] : nullptr; }
+int wb_kernel_total() { return kKernels; }
+
+extern "C" int wg_kernel_count(void) { return kKernels; }
+extern "C" const char* wg_kernel_name(int id) {
+  const wb_kernel_entry* e = wb_kernel_at(id);
+  return e ? e->name : "?";
+}
+
+extern "C" int wg_plan_create(int device, const wg_variant* v, int M, int N, int K, const void* dA, const void* dBt, void* dC,
+                              void** plan) {
+  if (!plan) return WG_E_ARG;
+  *plan = nullptr;
+  Plan* pl = new (std::nothrow) Plan();
+  if (!pl) return WG_E_ARG;
+  const int r = fill_plan(pl, device, v, M, N, K, dA, dBt, dC);
+  if (r != WG_OK) {
+    wg_plan_destroy(pl);
+    return r;
+  }
+  *plan = pl;
+  return WG_OK;
+}
+
+extern "C" int wg_host_plan_create(int device, const wg_variant* v, int M, int N, int K, void** plan) {
+  if (!plan || !v || M <= 0 || N <= 0 || K <= 0) return WG_E_ARG;
+  *plan = nullptr;
+  Plan* pl = new (std::nothrow) Plan();
+  if (!pl) return WG_E_ARG;
+  pl->owns_buffers = true;
+  int r = int(cudaSetDevice(device));
+  if (r == 0) r = int(cudaMalloc(&pl->dA, size_t(M) * K * 2));
+  if (r == 0) r = int(cudaMalloc(&pl->dBt, size_t(N) * K * 2));
+  if (r == 0) r = int(cudaMalloc(&pl->dC, size_t(M) * N * 4));
+  if (r == 0) r = fill_plan(pl, device, v, M, N, K, pl->dA, pl->dBt, pl->dC);
+  if (r != WG_OK) {
+    wg_plan_destroy(pl);
+    return r;
+  }
+  *plan = pl;
+  return WG_OK;
+}
+
+extern "C" void* wg_host_plan_buffer(void* plan, int which) {
+  Plan* pl = static_cast<Plan*>(plan);
+  if (!pl) return nullptr;
+  return which == 0 ? pl->dA : which == 1 ? pl->dBt : which == 2 ? pl->dC : nullptr;
+}
+
+extern "C" int wg_plan_set_timeout_ms(void* plan, unsigned ms) {
+  Plan* pl = static_cast<Plan*>(plan);
+  if (!pl) return WG_E_ARG;
+  pl->p.timeout_ns = (ms ? ms : 2000u) * 1000000ull;
+  return WG_OK;
+}
+
+extern "C" int wg_plan_info(void* plan, wg_launch_info* out) {
+  Plan* pl = static_cast<Plan*>(plan);
+  if (!pl || !out) return WG_E_ARG;
+  *out = pl->li;
+  return WG_OK;
+}
+
+extern "C" int wg_launch(void* plan, void* cuda_stream) {
+  Plan* pl = static_cast<Plan*>(plan);
+  if (!pl || !pl->k) return WG_E_ARG;
+  cudaLaunchConfig_t cfg;
+  std::memset(&cfg, 0, sizeof cfg);
+  cfg.gridDim = dim3(unsigned(pl->li.grid), 1, 1);
+  cfg.blockDim = dim3(unsigned(pl->li.threads), 1, 1);
+  cfg.dynamicSmemBytes = size_t(pl->li.dynsmem);
+  cfg.stream = static_cast<cudaStream_t>(cuda_stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = unsigned(pl->li.cluster);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  void* args[4] = {&pl->map_a, &pl->map_b, &pl->map_c, &pl->p};
+  return int(cudaLaunchKernelExC(&cfg, pl->k->fn, args));
+}
+
+extern "C" int wg_last_device_status(void* plan, unsigned out[4]) {
+  Plan* pl = static_cast<Plan*>(plan);
+  if (!pl || !out) return WG_E_ARG;
+  uint32_t st[8];
+  WG_CUDA(cudaDeviceSynchronize());
+  WG_CUDA(cudaMemcpy(st, pl->d_status, sizeof st, cudaMemcpyDeviceToHost));
+  for (int i = 0; i < 4; ++i) out[i] = st[i];
+  return st[0] == 0 ? WG_OK : WG_E_DEVICE_WAIT;
+}
+
+extern "C" int wg_plan_reset(void* plan) {
+  Plan* pl = static_cast<Plan*>(plan);
+  if (!pl) return WG_E_ARG;
+  WG_CUDA(cudaDeviceSynchronize());
+  WG_CUDA(cudaMemset(pl->d_flags, 0, pl->flag_bytes));
+  WG_CUDA(cudaMemset(pl->d_status, 0, 8 * sizeof(uint32_t)));
+  return WG_OK;
+}
+
+extern "C" int wg_plan_destroy(void* plan) {
+  Plan* pl = static_cast<Plan*>(plan);
+  if (!pl) return WG_OK;
+  if (pl->d_flags) cudaFree(pl->d_flags);
+  if (pl->d_status) cudaFree(pl->d_status);
+  if (pl->owns_buffers) {
+    if (pl->dA) cudaFree(pl->dA);
+    if (pl->dBt) cudaFree(pl->dBt);
+    if (pl->dC) cudaFree(pl->dC);
+  }
+  delete pl;
+  return WG_OK;
+}
+
+extern "C" int wg_host_run(void* plan, const void* hA, const void* hBt, void* hC) {
+  Plan* pl = static_cast<Plan*>(plan);
+  if (!pl || !pl->owns_buffers || !hA || !hBt || !hC) return WG_E_ARG;
+  WG_CUDA(cudaMemcpyAsync(pl->dA, hA, size_t(pl->M) * pl->K * 2, cudaMemcpyHostToDevice, 0));
+  WG_CUDA(cudaMemcpyAsync(pl->dBt, hBt, size_t(pl->N) * pl->K * 2, cudaMemcpyHostToDevice, 0));
+  const int r = wg_launch(pl, nullptr);
+  if (r != WG_OK) return r;
+  WG_CUDA(cudaMemcpyAsync(hC, pl->dC, size_t(pl->M) * pl->N * 4, cudaMemcpyDeviceToHost, 0));
+  WG_CUDA(cudaStreamSynchronize(0));
+  return WG_OK;
+}

@@ -1,0 +1,562 @@
+// The fp16-in / fp32-out GEMM kernel, C[M,N] = A[M,K] * Bt[N,K]^T, hand-written for sm_100a.
+//
+// Orientation ("swapped", as the reference's gemm_swapped.ml:1-21 and gemm_one.ml:1-9
+// describe it): the tile of B^T is the MMA's A operand and the tile of A its B operand,
+// so a CTA's accumulator in tensor memory holds output COLUMNS as lanes and output ROWS
+// as columns.  One tcgen05.ld then gives every lane of a warp 32 consecutive columns of
+// one C row per register, and each register goes out as one contiguous 128-byte row
+// segment -- no transpose through shared memory is needed.
+//
+// CG == 2: two CTAs of a cluster share each tcgen05.mma.cta_group::2; the CTAs sit side
+// by side along the output's columns, each loading its own TN rows of B^T and half of
+// the TM rows of A.  CG == 1: one CTA a 128 x 128 tile (the rule's last fallback).
+//
+// Warp roles (256 threads): warp 0 TMA producer, warp 1 MMA issuer (the pair leader's)
+// and tensor-memory owner, warp 2 tile scheduler (cluster launch control), warp 3
+// barrier set-up, warps 4-7 epilogue.  Every wait on a barrier or a flag is bounded:
+// when it runs out the kernel records where in `status`, every other wait gives up at
+// its next poll, and all warps fall through to the common teardown, so a protocol error
+// never leaves the GPU spinning.
+#pragma once
+#include "sm100_ptx.cuh"
+
+namespace wb {
+
+enum : int { SCHED_ONE = 0, SCHED_STRIDE = 1, SCHED_CLC = 2, SCHED_SPLITK = 3, SCHED_STREAMK = 4 };
+
+// status[0] codes
+enum : uint32_t {
+  ST_OK = 0,
+  ST_WAIT_EMPTY = 1,      // producer: ring stage never released
+  ST_WAIT_FULL = 2,       // MMA warp: ring stage never filled
+  ST_WAIT_ACC_EMPTY = 3,  // MMA warp: accumulator never released
+  ST_WAIT_ACC_FULL = 4,   // epilogue: accumulator never completed
+  ST_WAIT_SCHED = 5,      // a role: no answer from the scheduler
+  ST_WAIT_SCHED_EMPTY = 6,
+  ST_WAIT_CLC = 7,
+  ST_WAIT_FLAG = 8,       // split-K / stream-K: a partner's flag never came up
+  ST_TMEM = 9
+};
+
+struct KParams {
+  int M, N, K;
+  int kt;         // K / 64 k-steps
+  int ntiles;     // CTA tiles in all
+  int cl_n;       // clusters (CG CTAs side by side) across the output
+  int group;      // cluster rows walked down before moving across; a power of two
+  int serp;       // odd bands of `group` rows run right to left
+  int depth;      // ring stages
+  int nbuf;       // accumulators in tensor memory (1 or 2)
+  int sched;      // SCHED_*
+  int ask_ahead;  // probe the next stage before releasing this one
+  int split;      // SCHED_SPLITK: runs of K per tile
+  int sk_q, sk_r, sk_clusters;  // SCHED_STREAMK: units = q * clusters + r
+  float* C;                     // direct store
+  uint32_t* flags;              // split-K / stream-K hand-off words
+  uint32_t* status;             // 8 words: [0] code, [1] site detail, [2] CTA, [3] parity/stage
+  unsigned long long timeout_ns;
+};
+
+template <int CG_, int TM_, int TN_, bool DIRECT_, int EPI_ROWS_ = 16>
+struct Cfg {
+  static constexpr int CG = CG_, TM = TM_, TN = TN_, TK = 64;
+  static constexpr bool DIRECT = DIRECT_;
+  static constexpr bool FOLD = (CG == 2 && TN == 64);  // M = 128 pair: 64 accumulator rows a CTA
+  static constexpr int REPS = (TN == 256) ? 2 : 1;    // stacked MMA atoms
+  static constexpr int MMA_M = (CG == 2) ? (FOLD ? 128 : 256) : 128;
+  static constexpr int MMA_N = TM;
+  static constexpr int SPAN = FOLD ? TM / 2 : TM;  // tensor-memory columns an atom's accumulator spans
+  __host__ __device__ static constexpr int pow2_ge(int n) { int c = 32; while (c < n) c *= 2; return c; }
+  static constexpr int NCOLS = pow2_ge(REPS * SPAN);  // columns of one accumulator
+  static constexpr int A_ROWS = TM / CG;              // rows of A this CTA loads per stage
+  static constexpr int B_ROWS = TN;                   // rows of B^T this CTA loads per stage
+  static constexpr int A_BYTES = A_ROWS * TK * 2, B_BYTES = B_ROWS * TK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr uint32_t TX_BYTES = CG * STAGE_BYTES;  // what lands on the leader's barrier per stage
+  static constexpr int EPI_ROWS = DIRECT ? 32 : EPI_ROWS_;  // C rows per epilogue block
+  static constexpr int EPI_COPY_BYTES = EPI_ROWS * 128;
+  static constexpr int STAGING_BYTES = DIRECT ? 0 : 4 * 2 * EPI_COPY_BYTES;
+  static constexpr int CHUNKS = SPAN / EPI_ROWS;  // blocks per atom per warp
+  static constexpr int NBLK = REPS * CHUNKS;
+  static constexpr int MAX_DEPTH = 16;
+  static constexpr int CTRL_BYTES = 512;
+  static_assert(A_BYTES % 1024 == 0 && B_BYTES % 1024 == 0, "ring slots keep the 1024-byte swizzle atom alignment");
+  static_assert(SPAN % EPI_ROWS == 0, "whole epilogue blocks");
+  static_assert((MMA_M == 128 && MMA_N % 16 == 0) || (MMA_M == 256 && MMA_N % 16 == 0), "UMMA shape");
+  // kind::f16 instruction descriptor: f32 accumulator, f16 operands, both K-major
+  static constexpr uint32_t IDESC = (1u << 4) | (uint32_t(MMA_N >> 3) << 17) | (uint32_t(MMA_M >> 4) << 24);
+  static constexpr size_t smem_bytes(int depth) { return 1024 + size_t(depth) * STAGE_BYTES + STAGING_BYTES + CTRL_BYTES; }
+};
+
+// control block at the end of dynamic shared memory
+struct Ctrl {
+  uint64_t full[16];
+  uint64_t empty[16];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint64_t clc_bar;      // the cancel request's 16 bytes landed (scheduler's CTA)
+  uint64_t sched_full;   // the decoded answer is in `sched_slot` (each CTA)
+  uint64_t sched_empty;  // every taker has read it (first CTA)
+  uint32_t clc_answer[4];
+  uint32_t sched_slot[2];  // valid, first CTA of the cancelled cluster
+  uint32_t tmem_base;
+  uint32_t abort;
+};
+static_assert(sizeof(Ctrl) <= 512, "control block");
+
+struct Env {
+  const KParams* p;
+  uint32_t abort_addr;  // shared
+};
+
+// K-major, 128-byte-swizzled operand tile: 8-row groups 1024 bytes apart.
+WB_DEV uint64_t smem_desc(uint32_t addr) {
+  return uint64_t((addr & 0x3FFFF) >> 4) | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32) | (uint64_t(1) << 46) |
+         (uint64_t(2) << 61);
+}
+
+WB_DEV uint32_t ld_shared_u32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
+WB_DEV void st_shared_u32(uint32_t addr, uint32_t v) { asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory"); }
+
+WB_DEV void record_failure(const KParams& p, uint32_t code, uint32_t detail, uint32_t parity) {
+  if (atomicCAS(p.status, 0u, code) == 0u) {
+    p.status[1] = detail;
+    p.status[2] = blockIdx.x;
+    p.status[3] = parity;
+    __threadfence();
+  }
+}
+
+// Bounded wait on an mbarrier phase. Returns false when the kernel is giving up.
+WB_DEV bool wait_bar(const KParams& p, uint32_t abort_addr, uint32_t bar, uint32_t parity, uint32_t code, uint32_t detail) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer();
+  uint32_t polls = 0;
+  for (;;) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++polls & 15u) == 0u) {
+      if (ld_shared_u32(abort_addr) != 0u) return false;
+      if (ld_relaxed_gpu(p.status) != 0u) {
+        st_shared_u32(abort_addr, 1u);
+        return false;
+      }
+      if (globaltimer() - t0 > p.timeout_ns) {
+        record_failure(p, code, detail, parity);
+        st_shared_u32(abort_addr, 1u);
+        return false;
+      }
+    }
+  }
+}
+
+// Bounded wait until *flag == target (split-K / stream-K hand-off between CTAs).
+WB_DEV bool wait_flag(const KParams& p, uint32_t abort_addr, const uint32_t* flag, uint32_t target, uint32_t detail) {
+  if (ld_relaxed_gpu(flag) == target) return true;
+  const uint64_t t0 = globaltimer();
+  uint32_t polls = 0;
+  for (;;) {
+    if (ld_relaxed_gpu(flag) == target) return true;
+    if ((++polls & 63u) == 0u) {
+      if (ld_shared_u32(abort_addr) != 0u) return false;
+      if (ld_relaxed_gpu(p.status) != 0u) {
+        st_shared_u32(abort_addr, 1u);
+        return false;
+      }
+      if (globaltimer() - t0 > p.timeout_ns) {
+        record_failure(p, ST_WAIT_FLAG, detail, target);
+        st_shared_u32(abort_addr, 1u);
+        return false;
+      }
+    }
+  }
+}
+
+// One unit of work for a role: an output tile and the k-steps [kb, ke) of it.
+struct Work {
+  int tile, kb, ke;
+};
+
+// The sequence of work units a CTA walks; every role of the CTA walks the same one.
+template <class C>
+struct Walker {
+  const KParams& p;
+  uint32_t abort_addr, sched_full, sched_slot, sched_empty_first;  // shared addresses (the last in the first CTA)
+  uint32_t rank, lane;
+  uint32_t sched_parity = 0;
+  int tile = -1, seg = 0, t_first = 0, t_last = -1, kb_first = 0, ke_last = 0;
+  bool started = false;
+
+  WB_DEV Walker(const KParams& p_, uint32_t ctrl_addr, uint32_t rank_, uint32_t lane_) : p(p_), rank(rank_), lane(lane_) {
+    abort_addr = ctrl_addr + offsetof(Ctrl, abort);
+    sched_full = ctrl_addr + offsetof(Ctrl, sched_full);
+    sched_slot = ctrl_addr + offsetof(Ctrl, sched_slot);
+    sched_empty_first = mapa(ctrl_addr + offsetof(Ctrl, sched_empty), 0);
+  }
+
+  WB_DEV bool next(Work& w) {
+    const int sched = p.sched;
+    if (!started) {
+      started = true;
+      tile = blockIdx.x;
+      w.tile = tile, w.kb = 0, w.ke = p.kt;
+      if (sched == SCHED_SPLITK) {
+        // cluster c is run (c mod S) of tile-cluster (c div S): k-steps [s q + s r / S, ...)
+        const int c = blockIdx.x / C::CG, S = p.split, s = c % S, q = p.kt / S, r = p.kt % S;
+        w.tile = (c / S) * C::CG + int(rank);
+        w.kb = s * q + (s * r) / S;
+        w.ke = (s + 1) * q + ((s + 1) * r) / S;
+        return true;
+      }
+      if (sched == SCHED_STREAMK) {
+        // cluster c owns units [c q + c r / G, (c+1) q + (c+1) r / G) of tiles x k-steps,
+        // walked from its last tile down to its first
+        const int c = blockIdx.x / C::CG, G = p.sk_clusters;
+        const int b = c * p.sk_q + (c * p.sk_r) / G, l = (c + 1) * p.sk_q + ((c + 1) * p.sk_r) / G - 1;
+        if (l < b) return false;
+        t_first = b / p.kt, kb_first = b % p.kt, t_last = l / p.kt, ke_last = l % p.kt + 1;
+        seg = t_last;
+      } else {
+        return tile < p.ntiles;
+      }
+    } else {
+      if (sched == SCHED_ONE || sched == SCHED_SPLITK) return false;
+      if (sched == SCHED_STRIDE) {
+        tile += gridDim.x;
+        w.tile = tile, w.kb = 0, w.ke = p.kt;
+        return tile < p.ntiles;
+      }
+      if (sched == SCHED_CLC) {
+        if (!wait_bar(p, abort_addr, sched_full, sched_parity, ST_WAIT_SCHED, 0)) return false;
+        sched_parity ^= 1u;
+        const uint32_t valid = ld_shared_u32(sched_slot), first = ld_shared_u32(sched_slot + 4);
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(sched_empty_first);
+        if (!valid) return false;
+        tile = int(first + rank);
+        w.tile = tile, w.kb = 0, w.ke = p.kt;
+        return true;
+      }
+      seg -= 1;  // stream-K
+    }
+    if (seg < t_first) return false;
+    w.tile = seg * C::CG + int(rank);
+    w.kb = (seg == t_first) ? kb_first : 0;
+    w.ke = (seg == t_last) ? ke_last : p.kt;
+    return true;
+  }
+};
+
+// Where a CTA tile sits in C: the tile index's digits, fastest first, are the CTA's rank
+// in its pair (along columns), the row within a group of `group` cluster rows, the
+// cluster column, the band; with `serp` odd bands run right to left.
+// (The reference's map: backend/tiles.ml:32-80.)
+template <class C>
+WB_DEV void tile_origin(const KParams& p, int tile, int& row, int& col) {
+  const int rank = tile % C::CG, c = tile / C::CG;
+  const int rig = c & (p.group - 1), rest = c / p.group;
+  int colc = rest % p.cl_n;
+  const int band = rest / p.cl_n;
+  if (p.serp && (band & 1)) colc ^= (p.cl_n - 1);
+  row = (band * p.group + rig) * C::TM;
+  col = (colc * C::CG + rank) * C::TN;
+}
+
+// ------------------------------------------------------------------ epilogue pieces
+
+// Issue the tcgen05.ld of block `i` of this warp: atom i / CHUNKS, rows chunk i % CHUNKS.
+template <class C>
+WB_DEV void epi_load(uint32_t tbase, int i, uint32_t* v) {
+  const int r = i / C::CHUNKS, ch = i % C::CHUNKS;
+  tmem_ld<C::EPI_ROWS>(tbase + uint32_t(r * C::SPAN + ch * C::EPI_ROWS), v);
+}
+
+// Output coordinates of block i, register 0, lane 0 for epilogue warp quarter q.
+template <class C>
+WB_DEV void epi_coords(int row, int col, int q, int i, int& y, int& x) {
+  const int r = i / C::CHUNKS, ch = i % C::CHUNKS;
+  if constexpr (C::FOLD) {
+    // 64 accumulator rows a CTA: lanes 64-127 hold the upper half of the tile's rows
+    x = col + 32 * (q & 1);
+    y = row + (C::TM / 2) * (q >> 1) + ch * C::EPI_ROWS;
+  } else {
+    x = col + 128 * r + 32 * q;
+    y = row + ch * C::EPI_ROWS;
+  }
+}
+
+template <class C>
+__global__ void __launch_bounds__(256, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+            const __grid_constant__ CUtensorMap map_c, const __grid_constant__ KParams p) {
+  constexpr int CG = C::CG;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t ring = smem_base;
+  const uint32_t staging = ring + uint32_t(p.depth) * C::STAGE_BYTES;
+  const uint32_t ctrl = staging + C::STAGING_BYTES;
+  auto ctrl_at = [&](size_t off) { return ctrl + uint32_t(off); };
+  const uint32_t abort_addr = ctrl_at(offsetof(Ctrl, abort));
+
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = (CG == 2) ? cluster_ctarank() : 0u;
+  const bool leader = (rank == 0);
+  const int depth = p.depth, nbuf = p.nbuf;
+
+  auto full_bar = [&](int s) { return ctrl_at(offsetof(Ctrl, full) + 8 * s); };
+  auto empty_bar = [&](int s) { return ctrl_at(offsetof(Ctrl, empty) + 8 * s); };
+  auto acc_full_bar = [&](int b) { return ctrl_at(offsetof(Ctrl, acc_full) + 8 * b); };
+  auto acc_empty_bar = [&](int b) { return ctrl_at(offsetof(Ctrl, acc_empty) + 8 * b); };
+
+  // ---------------------------------------------------------------- set-up
+  if (warp == 3 && lane == 0) {
+    prefetch_tmap(&map_a);
+    prefetch_tmap(&map_b);
+    if constexpr (!C::DIRECT) prefetch_tmap(&map_c);
+    for (int s = 0; s < depth; ++s) {
+      mbar_init(full_bar(s), 1);   // the leader's one arrival stating the pair's bytes
+      mbar_init(empty_bar(s), 1);  // one commit from the MMA warp
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full_bar(b), 1);        // one commit
+      mbar_init(acc_empty_bar(b), 4 * CG);  // every epilogue warp of the pair
+    }
+    mbar_init(ctrl_at(offsetof(Ctrl, clc_bar)), 1);
+    mbar_init(ctrl_at(offsetof(Ctrl, sched_full)), 1);
+    // takers of an answer: a producer a CTA, the leader's MMA warp, four epilogue warps a CTA
+    mbar_init(ctrl_at(offsetof(Ctrl, sched_empty)), CG + 1 + 4 * CG);
+    st_shared_u32(abort_addr, 0u);
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    // both CTAs of a pair allocate, each into its own slot word
+    tmem_alloc<CG>(ctrl_at(offsetof(Ctrl, tmem_base)), uint32_t(C::pow2_ge(C::NCOLS * nbuf)));
+    tmem_relinquish<CG>();
+  }
+  tc_fence_before();
+  if constexpr (CG == 2) {
+    cluster_arrive();
+    cluster_wait();
+  } else {
+    __syncthreads();
+  }
+  tc_fence_after();
+  const uint32_t tmem_base = ld_shared_u32(ctrl_at(offsetof(Ctrl, tmem_base)));
+
+  // ---------------------------------------------------------------- roles
+  if (warp == 0) {
+    // ===== producer: TMA loads into this CTA's ring, counted on the leader's barrier
+    Walker<C> walk(p, ctrl, rank, lane);
+    Work w;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    while (ok && walk.next(w)) {
+      int row, col;
+      tile_origin<C>(p, w.tile, row, col);
+      // a pair's CTAs sit side by side: same rows, so they split the A tile between them
+      const int a_row = row + int(rank) * C::A_ROWS;
+      for (int kk = w.kb; kk < w.ke; ++kk) {
+        if (!wait_bar(p, abort_addr, empty_bar(stage), phase ^ 1u, ST_WAIT_EMPTY, uint32_t(stage))) {
+          ok = false;
+          break;
+        }
+        if (lane == 0) {
+          const uint32_t bar = (CG == 2) ? mapa(full_bar(stage), 0) : full_bar(stage);
+          if (leader) mbar_arrive_expect_tx(full_bar(stage), C::TX_BYTES);
+          const uint32_t sa = ring + uint32_t(stage) * C::STAGE_BYTES, sb = sa + C::A_BYTES;
+          tma_load_2d<CG>(sa, &map_a, kk * C::TK, a_row, bar);
+          tma_load_2d<CG>(sb, &map_b, kk * C::TK, col, bar);
+        }
+        __syncwarp();
+        if (++stage == depth) stage = 0, phase ^= 1u;
+      }
+    }
+    // every stage this CTA filled has been released before it leaves
+    for (int i = 0; ok && i < depth; ++i) {
+      ok = wait_bar(p, abort_addr, empty_bar(stage), phase ^ 1u, ST_WAIT_EMPTY, 0x100u + uint32_t(stage));
+      if (++stage == depth) stage = 0, phase ^= 1u;
+    }
+  } else if (warp == 1) {
+    // ===== MMA issuer: the pair leader's warp 1 issues for both CTAs
+    if (leader) {
+      Walker<C> walk(p, ctrl, rank, lane);
+      Work w;
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      const uint16_t mask = (CG == 2) ? 0x3 : 0x1;
+      while (ok && walk.next(w)) {
+        if (!wait_bar(p, abort_addr, acc_empty_bar(acc), acc_phase ^ 1u, ST_WAIT_ACC_EMPTY, uint32_t(acc))) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d = tmem_base + uint32_t(acc * C::NCOLS);
+        uint32_t accumulate = 0;
+        bool landed = false;
+        for (int kk = w.kb; kk < w.ke; ++kk) {
+          if (!landed && !wait_bar(p, abort_addr, full_bar(stage), phase, ST_WAIT_FULL, uint32_t(stage))) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = ring + uint32_t(stage) * C::STAGE_BYTES, sb = sa + C::A_BYTES;
+          if (lane == 0) {
+#pragma unroll
+            for (int r = 0; r < C::REPS; ++r) {
+#pragma unroll
+              for (int j = 0; j < C::TK / 16; ++j) {
+                // MMA "A" = B^T rows of atom r; MMA "B" = the tile of A; 16 K-elements = 32 bytes on
+                umma_f16<CG>(d + uint32_t(r * C::SPAN), smem_desc(sb + uint32_t(r * (C::MMA_M / CG) * 128 + j * 32)),
+                             smem_desc(sa + uint32_t(j * 32)), C::IDESC, (j == 0) ? accumulate : 1u);
+              }
+            }
+          }
+          accumulate = 1;
+          int nstage = stage + 1;
+          uint32_t nphase = phase;
+          if (nstage == depth) nstage = 0, nphase ^= 1u;
+          // asking a stage ahead: has the next stage landed already?
+          landed = (p.ask_ahead && kk + 1 < w.ke) ? (mbar_test_wait(full_bar(nstage), nphase) != 0u) : false;
+          if (lane == 0) umma_commit<CG>(empty_bar(stage), mask);  // the stage is free once these MMAs have read it
+          __syncwarp();
+          stage = nstage, phase = nphase;
+        }
+        if (!ok) break;
+        if (lane == 0) umma_commit<CG>(acc_full_bar(acc), mask);  // the accumulator is complete in both CTAs
+        __syncwarp();
+        if (++acc == nbuf) acc = 0, acc_phase ^= 1u;
+      }
+      // every accumulator has been read out in both CTAs before leaving
+      for (int i = 0; ok && i < nbuf; ++i) {
+        ok = wait_bar(p, abort_addr, acc_empty_bar(acc), acc_phase ^ 1u, ST_WAIT_ACC_EMPTY, 0x100u + uint32_t(acc));
+        if (++acc == nbuf) acc = 0, acc_phase ^= 1u;
+      }
+    }
+  } else if (warp == 2) {
+    // ===== scheduler (cluster launch control): the cluster's first CTA asks for one more
+    // cluster's tiles at a time and hands the answer to every taker of both CTAs
+    if (p.sched == SCHED_CLC && leader) {
+      const uint32_t clc_bar = ctrl_at(offsetof(Ctrl, clc_bar)), answer = ctrl_at(offsetof(Ctrl, clc_answer));
+      const uint32_t sched_empty = ctrl_at(offsetof(Ctrl, sched_empty));
+      uint32_t pf = 0, pe = 0;
+      for (;;) {
+        if (!wait_bar(p, abort_addr, sched_empty, pe ^ 1u, ST_WAIT_SCHED_EMPTY, 0)) break;
+        pe ^= 1u;
+        if (lane == 0) {
+          mbar_arrive_expect_tx(clc_bar, 16);
+          clc_try_cancel(answer, clc_bar);
+        }
+        __syncwarp();
+        if (!wait_bar(p, abort_addr, clc_bar, pf, ST_WAIT_CLC, 0)) break;
+        pf ^= 1u;
+        uint32_t first = 0;
+        const uint32_t valid = clc_decode(answer, &first);
+        fence_proxy_async_smem();  // this read of the answer before the next request's write
+        __syncwarp();
+        if (lane == 0) {
+          for (uint32_t r = 0; r < uint32_t(CG); ++r) {
+            const uint32_t slot = mapa(ctrl_at(offsetof(Ctrl, sched_slot)), r);
+            st_cluster_u32(slot, valid);
+            st_cluster_u32(slot + 4, first);
+            mbar_arrive_cluster(mapa(ctrl_at(offsetof(Ctrl, sched_full)), r));
+          }
+        }
+        __syncwarp();
+        if (!valid) break;
+      }
+    }
+  } else if (warp >= 4) {
+    // ===== epilogue: tensor memory -> registers -> C
+    const int q = int(warp & 3u);
+    Walker<C> walk(p, ctrl, rank, lane);
+    Work w;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    const uint32_t acc_empty_leader = (CG == 2) ? mapa(acc_empty_bar(0), 0) : acc_empty_bar(0);
+    const uint32_t my_staging = staging + uint32_t(q) * 2u * C::EPI_COPY_BYTES;
+    while (ok && walk.next(w)) {
+      int row, col;
+      tile_origin<C>(p, w.tile, row, col);
+      if (!wait_bar(p, abort_addr, acc_full_bar(acc), acc_phase, ST_WAIT_ACC_FULL, uint32_t(acc))) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t tbase = tmem_base + uint32_t(acc * C::NCOLS) + (uint32_t(q * 32) << 16);
+      uint32_t v[2][C::EPI_ROWS];
+      epi_load<C>(tbase, 0, v[0]);
+#pragma unroll
+      for (int i = 0; i < C::NBLK; ++i) {
+        tmem_wait_ld();
+        if (i + 1 < C::NBLK) {
+          epi_load<C>(tbase, i + 1, v[(i + 1) & 1]);
+        } else {
+          // the last block is out of tensor memory: the accumulator may be overwritten
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) {
+            if constexpr (CG == 2) mbar_arrive_cluster(acc_empty_leader + 8u * uint32_t(acc));
+            else mbar_arrive(acc_empty_leader + 8u * uint32_t(acc));
+          }
+        }
+        int y, x;
+        epi_coords<C>(row, col, q, i, y, x);
+        if constexpr (C::DIRECT) {
+          // register j is row y + j; the warp's lanes are 32 consecutive columns
+          float* dst = p.C + size_t(y) * size_t(p.N) + size_t(x) + lane;
+          const bool col_ok = (x + int(lane)) < p.N;
+#pragma unroll
+          for (int j = 0; j < C::EPI_ROWS; ++j)
+            if (col_ok && (y + j) < p.M) dst[size_t(j) * size_t(p.N)] = __uint_as_float(v[i & 1][j]);
+        } else {
+          // stage the block as EPI_ROWS rows of 128 bytes, then one TMA store (clipped at C's edges)
+          const uint32_t copy = my_staging + uint32_t(i & 1) * C::EPI_COPY_BYTES;
+          if (lane == 0) bulk_wait_read<1>();  // the store that last read this copy is done with it
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < C::EPI_ROWS; ++j)  // 128-byte swizzle: 16-byte chunk index xor row-in-8
+            st_shared_u32(copy + uint32_t(j) * 128u + ((lane * 4u) ^ (uint32_t(j & 7) << 4)), v[i & 1][j]);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&map_c, x, y, copy);
+            bulk_commit();
+          }
+        }
+      }
+      if (++acc == nbuf) acc = 0, acc_phase ^= 1u;
+    }
+    if constexpr (!C::DIRECT) {
+      if (lane == 0) bulk_wait_read<0>();  // the last stores have read their staging copies
+      __syncwarp();
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  __syncwarp();
+  if (ld_shared_u32(abort_addr) != 0u) {
+    // giving up: let copies and MMAs in flight land before the shared and tensor memory go away
+    const uint64_t t0 = globaltimer();
+    while (globaltimer() - t0 < 200000ull) {
+    }
+  }
+  tc_fence_before();
+  if constexpr (CG == 2) {
+    cluster_arrive();
+    cluster_wait();
+  } else {
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc<CG>(tmem_base, uint32_t(C::pow2_ge(C::NCOLS * nbuf)));
+  }
+}
+
+}  // namespace wb

@@ -1,0 +1,19 @@
+// The compiled kernel instances: which (cta group, tile, store path) each is and what its
+// launch needs.  Filled in api.cu where the templates are instantiated.
+#pragma once
+#include <stddef.h>
+
+struct wb_kernel_entry {
+  int id;
+  int cg, tile_m, tile_n, direct;
+  int epi_rows;        // C rows per epilogue block (the C tensor map's box rows)
+  int ncols;           // tensor-memory columns of one accumulator
+  int stage_bytes;     // shared memory of one ring stage
+  size_t smem_fixed;   // alignment slack + staging + control block
+  const char* name;
+  const void* fn;      // the __global__ function
+};
+
+const wb_kernel_entry* wb_find_kernel(int cg, int tile_m, int tile_n, int direct);
+const wb_kernel_entry* wb_kernel_at(int id);
+int wb_kernel_total();

@@ -1,0 +1,361 @@
+// Host side of the operator surface: the per-shape rule (`warpc gemm M N K`), the geometry
+// a decision implies, how this library's kernels realise it, and the launch header text.
+//
+// Rule: backend/programs.ml:46-80.  Geometry: backend/gemm_swapped.ml:50-108 (swapped),
+// backend/gemm_pair.ml:16-43 (pair), backend/gemm_one.ml:17-30 (one).
+// Header: backend/compile.ml:86-88, 165-186.
+#include <climits>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <string>
+
+#include "../../include/warpc_b200.h"
+#include "kernel_table.h"
+
+namespace {
+
+constexpr int kSms = 148;
+constexpr int kTileK = 64;
+
+// clusters of `ctas` CTAs resident at once on 148 SMs (backend/gemm_swapped.ml:27)
+int resident_clusters(int ctas) {
+  switch (ctas) {
+    case 1: return kSms;
+    case 2: return 74;
+    case 4: return 33;
+    case 8: return 15;
+    default: return 0;
+  }
+}
+
+int pow2_cols(int n) {  // tensor-memory allocation: a power of two, 32 at least (backend/atom.ml:216-218)
+  int c = 32;
+  while (c < n) c *= 2;
+  return c;
+}
+
+wg_variant blank(int prog, int tm, int tn, int depth) {
+  wg_variant v;
+  std::memset(&v, 0, sizeof v);
+  v.prog = prog, v.tile_m = tm, v.tile_n = tn, v.tile_k = kTileK, v.depth = depth;
+  v.cluster_n = 1, v.group = 8, v.split = 1, v.split_grid = 1;
+  return v;
+}
+
+int derive_swapped(int m, int n, int k, wg_variant* v) {
+  const int pair = 2;
+  if (v->cluster_n < 1) v->cluster_n = 1;
+  if (v->split < 1) v->split = 1;
+  if (v->split_grid < 1) v->split_grid = 1;
+  if (v->group < 1) v->group = 8;
+  // the builder's refusals (backend/gemm_swapped.ml:32-48)
+  if (v->streamk && (v->clc || v->cluster_n > 1 || (v->direct != 0) == (v->split_add != 0))) return WG_E_VARIANT;
+  if (v->split > 1 && (v->split > 4 || v->cluster_n != v->split || v->clc || v->streamk || !v->direct)) return WG_E_VARIANT;
+  if (v->split_grid > 1 && (v->split > 1 || v->clc || v->streamk || (v->direct != 0) == (v->split_add != 0))) return WG_E_VARIANT;
+  if (v->split_add && v->split_grid == 1 && !v->streamk) return WG_E_VARIANT;
+  if (v->tile_m <= 0 || v->tile_n <= 0 || v->depth <= 0 || m <= 0 || n <= 0 || k <= 0) return WG_E_VARIANT;
+
+  const int ctas = pair * v->cluster_n;
+  const int rows_needed = v->tile_n * pair;
+  const int atom_m = rows_needed < 256 ? rows_needed : 256;
+  if (rows_needed % atom_m != 0) return WG_E_VARIANT;
+  // kind::f16 pair shapes (backend/atom.ml:146-154)
+  if (!(atom_m == 128 || atom_m == 256)) return WG_E_VARIANT;
+  if (!(v->tile_m % 16 == 0 && v->tile_m >= 16 && v->tile_m <= 256)) return WG_E_VARIANT;
+  v->atom_m = atom_m;
+  v->reps = rows_needed / atom_m;
+  const int a_rows = atom_m / pair;                   // B^T rows a CTA feeds one atom
+  const int sb_rows = v->reps * a_rows;               // = tile_n
+  const int sa_rows = v->tile_m / pair;               // A rows a CTA loads
+  const int acc_rows = atom_m / pair;                 // accumulator rows a CTA holds per atom
+  const int span = (acc_rows == 128) ? v->tile_m : v->tile_m / 2;  // backend/atom.ml:235-251
+  if (v->reps * acc_rows != v->tile_n) return WG_E_VARIANT;
+  v->tiles_m = (m + v->tile_m - 1) / v->tile_m;
+  v->tiles_n = (n + v->tile_n - 1) / v->tile_n;
+  const int sharing = v->split > 1 ? 1 : v->cluster_n;
+  if (v->tiles_m % sharing != 0 || v->tiles_n % pair != 0 || k % (kTileK * v->split) != 0 || k / kTileK < v->split_grid)
+    return WG_E_VARIANT;
+  if (v->direct && (m % v->tile_m != 0 || n % v->tile_n != 0)) return WG_E_VARIANT;
+  if (sb_rows % sharing != 0) return WG_E_VARIANT;
+  v->a_box_rows = sa_rows;
+  v->bt_box_rows = sb_rows / sharing;
+  v->tmem_cols = pow2_cols(v->reps * span);
+  v->total_tiles = v->tiles_m * v->tiles_n;
+  v->nbuf = v->bufs > 0 ? v->bufs : ((2 * v->tmem_cols <= 512 && v->total_tiles > kSms) ? 2 : 1);
+  if (v->tmem_cols * v->nbuf > 512) return WG_E_VARIANT;
+  v->alloc_cols = pow2_cols(v->tmem_cols * v->nbuf);
+  v->ctas = ctas;
+  v->persistent = (v->split == 1 && v->split_grid == 1 && (v->clc || v->total_tiles > kSms)) ? 1 : 0;
+  if (resident_clusters(ctas) == 0) return WG_E_VARIANT;
+  if (v->streamk) v->grid = kSms / ctas * ctas;
+  else if (v->split > 1) v->grid = v->total_tiles * v->split;
+  else if (v->split_grid > 1) v->grid = v->total_tiles * v->split_grid;
+  else if (v->clc || v->total_tiles <= kSms) v->grid = v->total_tiles;
+  else v->grid = resident_clusters(ctas) * ctas;
+  if (v->split_grid > 1 && v->grid / ctas > resident_clusters(ctas)) return WG_E_VARIANT;
+  v->stage_bytes = sa_rows * kTileK * 2 + sb_rows * kTileK * 2;
+  v->tx_bytes = pair * v->stage_bytes;
+  v->kt = k / kTileK / v->split;
+  if (v->streamk && !v->split_add) {
+    const int clusters = v->grid / ctas, units = v->total_tiles / ctas * v->kt;
+    if (units / clusters < v->kt) return WG_E_VARIANT;
+  }
+  const int staging = v->direct ? 0 : 4 * 2 * (8 * 32 * 4);
+  v->ref_dynsmem = v->depth * v->stage_bytes + staging;
+  if (v->ref_dynsmem + 0x400 + 0x400 > 232448) return WG_E_VARIANT;  // backend/mem.ml:228
+  v->ref_mbarriers = 2 * v->depth + 2 * v->nbuf + (v->clc ? 2 : 0) + (v->split > 1 ? 1 : 0);
+  if (v->split_add) v->nflags = v->streamk ? v->grid + v->total_tiles : v->grid;
+  else if (v->streamk || v->split_grid > 1) v->nflags = v->grid;
+  else v->nflags = 0;
+  return WG_OK;
+}
+
+int derive_pair(int m, int n, int k, wg_variant* v) {
+  // backend/gemm_pair.ml:16-43: 2x1 cluster along M, M = 256 x N = 128 atom
+  v->tile_m = 128, v->tile_n = 128, v->tile_k = kTileK;
+  if (m % 256 != 0 || n % 128 != 0 || k % kTileK != 0 || v->depth <= 0) return WG_E_VARIANT;
+  v->cluster_n = 1, v->split = 1, v->split_grid = 1, v->group = 8;
+  v->atom_m = 256, v->reps = 1, v->tmem_cols = 128, v->nbuf = 1, v->alloc_cols = 128;
+  v->tiles_m = m / 128, v->tiles_n = n / 128, v->total_tiles = v->tiles_m * v->tiles_n;
+  v->ctas = 2;
+  v->grid = v->total_tiles <= kSms ? v->total_tiles : kSms / 2 * 2;
+  v->persistent = 1;
+  v->kt = k / kTileK;
+  v->a_box_rows = 128, v->bt_box_rows = 64;
+  v->stage_bytes = 128 * 128 + 64 * 128;
+  v->tx_bytes = 2 * v->stage_bytes;
+  v->ref_dynsmem = v->depth * v->stage_bytes + 4 * 2 * (32 * 32 * 4);
+  if (v->ref_dynsmem + 0x800 > 232448) return WG_E_VARIANT;
+  v->ref_mbarriers = 2 * v->depth + 2;
+  return WG_OK;
+}
+
+int derive_one(int m, int n, int k, wg_variant* v) {
+  // backend/gemm_one.ml:17-30: one CTA a 128 x 128 tile, cta_group::1
+  v->tile_m = 128, v->tile_n = 128, v->tile_k = kTileK;
+  if (m % 128 != 0 || n % 128 != 0 || k % kTileK != 0 || v->depth <= 0) return WG_E_SHAPE;
+  v->cluster_n = 1, v->split = 1, v->split_grid = 1, v->group = 1, v->direct = 1;
+  v->atom_m = 128, v->reps = 1, v->tmem_cols = 128, v->nbuf = 1, v->alloc_cols = 128;
+  v->tiles_m = m / 128, v->tiles_n = n / 128, v->total_tiles = v->tiles_m * v->tiles_n;
+  v->ctas = 1, v->grid = v->total_tiles, v->kt = k / kTileK;
+  v->a_box_rows = 128, v->bt_box_rows = 128;
+  v->stage_bytes = 2 * 128 * 128;
+  v->tx_bytes = v->stage_bytes;
+  v->ref_dynsmem = v->depth * v->stage_bytes;
+  if (v->ref_dynsmem + 0x800 > 232448) return WG_E_VARIANT;
+  v->ref_mbarriers = 2 * v->depth + 1;
+  return WG_OK;
+}
+
+// the group of cluster rows a walk really uses (backend/tiles.ml:42-47)
+int effective_group(int group, int walked, int other) {
+  int g = 1;
+  while (g * 2 <= walked && g < group) g *= 2;
+  const bool pow2_other = other > 0 && (other & (other - 1)) == 0;
+  return (pow2_other && walked % g == 0) ? g : 1;
+}
+
+void append(std::string& s, const char* fmt, ...) {
+  char line[256];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(line, sizeof line, fmt, ap);
+  va_end(ap);
+  s += line;
+  s += '\n';
+}
+
+}  // namespace
+
+extern "C" int wg_derive(int M, int N, int K, wg_variant* v) {
+  if (!v) return WG_E_ARG;
+  switch (v->prog) {
+    case WG_PROG_SWAPPED: return derive_swapped(M, N, K, v);
+    case WG_PROG_PAIR: return derive_pair(M, N, K, v);
+    case WG_PROG_ONE: return derive_one(M, N, K, v);
+    default: return WG_E_VARIANT;
+  }
+}
+
+extern "C" int wg_choose(int m, int n, int k, int sm, wg_variant* out) {
+  if (!out || (sm != WG_SM_100A && sm != WG_SM_103A)) return WG_E_ARG;
+  if (m <= 0 || n <= 0 || k <= 0) return WG_E_SHAPE;
+  const int tiles = m / 128 * (n / 128);
+  const bool pair_fits = m % 256 == 0 && n % 128 == 0 && k % 64 == 0;
+  const bool swapped_fits = n % 256 == 0 && m % 64 == 0 && k % 64 == 0 && (m + 255) / 256 * (n / 128) >= kSms;
+  auto waves = [&](int cn) {
+    const int rc = resident_clusters(2 * cn);
+    return (m % (128 * cn) == 0) ? (tiles / (2 * cn) + rc - 1) / rc : INT_MAX;
+  };
+  const int pair_tiles = (m % 256 == 0 && n % 512 == 0) ? m / 256 * (n / 512) : 0;
+  const int runs = pair_tiles > 0 ? resident_clusters(2) / pair_tiles : 0;
+  const int mn = m < n ? m : n, mnk = mn < k ? mn : k;
+  wg_variant v;
+  if (swapped_fits && n % 512 == 0 && m % 256 == 0 && mnk >= 8192) {
+    v = blank(WG_PROG_SWAPPED, 256, 256, 4);
+    v.clc = 1, v.ask_ahead = 1, v.serpentine = 1;
+  } else if (swapped_fits && k <= 1024 && m % 256 == 0) {
+    v = blank(WG_PROG_SWAPPED, 256, 128, 5);
+    v.late_launch = 1;
+  } else if (swapped_fits) {
+    v = blank(WG_PROG_SWAPPED, 192, 128, 7);
+    v.clc = k >= 4096;
+  } else if (2 * tiles <= kSms && n % 128 == 0 && m % 128 == 0 && k % 64 == 0) {
+    if (k >= 65536 && runs >= 2 && k / 64 >= runs) {
+      v = blank(WG_PROG_SWAPPED, 256, 256, 4);
+      v.split_grid = runs, v.split_add = 1, v.ask_ahead = 1;
+    } else if (k >= 16384 && n / 128 % 2 == 0 && k % 128 == 0 && tiles / 2 <= resident_clusters(4)) {
+      v = blank(WG_PROG_SWAPPED, 128, 128, 9);
+      v.split = 2, v.cluster_n = 2, v.direct = 1;
+    } else {
+      v = blank(WG_PROG_SWAPPED, 128, 64, 13);
+      v.direct = 1, v.ask_ahead = 1, v.late_launch = (sm == WG_SM_103A);
+    }
+  } else if (tiles <= kSms && n % 256 == 0 && m % 128 == 0 && k % 64 == 0) {
+    v = blank(WG_PROG_SWAPPED, 128, 128, 6);
+    v.direct = 1, v.late_launch = 1;
+  } else if (tiles > kSms && k >= 16384 && m % 512 == 0 && n % 256 == 0 && m / 512 * (n / 256) <= resident_clusters(4)) {
+    v = blank(WG_PROG_SWAPPED, 256, 128, 6);
+    if (sm == WG_SM_100A) v.streamk = 1, v.split_add = 1, v.bufs = 2, v.ask_ahead = 1;
+    else v.cluster_n = 2, v.late_launch = 1;
+  } else if (tiles > kSms && n % 256 == 0 && k % 64 == 0 && waves(2) != INT_MAX) {
+    const int cluster_n = waves(4) <= waves(2) ? 4 : (waves(1) <= waves(2) ? 1 : 2);
+    v = blank(WG_PROG_SWAPPED, 128, 128, k >= 8192 ? 9 : 8);
+    v.clc = cluster_n > 1, v.cluster_n = cluster_n, v.late_launch = cluster_n == 4, v.group = 16;
+  } else if (pair_fits) {
+    v = blank(WG_PROG_PAIR, 128, 128, 8);
+  } else {
+    v = blank(WG_PROG_ONE, 128, 128, 4);
+  }
+  const int r = wg_derive(m, n, k, &v);
+  if (r != WG_OK) return r == WG_E_VARIANT ? WG_E_SHAPE : r;
+  *out = v;
+  return WG_OK;
+}
+
+// How this library runs a variant.  Differences from the reference's own launch, all in the
+// direction of fewer hardware features: a cluster is always the pair alone (the reference's
+// 2 x cluster_n clusters exist to multicast B^T tiles; here each CTA fetches its own tiles and
+// the L2 serves the duplicates), and split-K inside such a cluster becomes split-K over the
+// grid with the partial sums added in the L2.
+extern "C" int wg_realise(const wg_variant* v, int M, int N, int K, wg_launch_info* out) {
+  if (!v || !out) return WG_E_ARG;
+  std::memset(out, 0, sizeof *out);
+  wg_launch_info& li = *out;
+  li.threads = 256;
+  li.depth = v->depth;
+  li.ask_ahead = v->ask_ahead;
+  li.split = 1;
+  if (v->prog == WG_PROG_ONE) {
+    li.cg = 1, li.tile_m = 128, li.tile_n = 128, li.direct = 1;
+    li.grid = v->grid, li.cluster = 1, li.sched = 0, li.nbuf = 1, li.group = 1, li.cl_n = v->tiles_n;
+  } else if (v->prog == WG_PROG_PAIR) {
+    // same pair tile (256 x 128) in the swapped orientation: 256 x 64 a CTA, an M = 128 pair
+    li.cg = 2, li.tile_m = 256, li.tile_n = 64, li.direct = 0;
+    const int tiles_m = M / 256, tiles_n = N / 64, total = tiles_m * tiles_n;
+    li.cluster = 2;
+    li.grid = total <= kSms ? total : kSms / 2 * 2;
+    li.sched = total <= kSms ? 0 : 1;
+    li.nbuf = (total > kSms) ? 2 : 1;
+    li.cl_n = tiles_n / 2;
+    li.group = effective_group(8, tiles_m, li.cl_n);
+  } else {
+    li.cg = 2, li.tile_m = v->tile_m, li.tile_n = v->tile_n, li.direct = v->direct && v->split == 1;
+    li.cluster = 2;
+    li.nbuf = v->nbuf;
+    li.cl_n = v->tiles_n / 2;
+    li.group = effective_group(v->group, v->tiles_m, li.cl_n);
+    li.serpentine = v->serpentine && li.cl_n > 1 && (li.cl_n & (li.cl_n - 1)) == 0;
+    const int total = v->total_tiles;
+    if (v->streamk) {
+      li.sched = 4, li.grid = kSms / 2 * 2;
+      li.nflags = li.grid + total;
+    } else if (v->split_grid > 1 || v->split > 1) {
+      li.split = v->split_grid > 1 ? v->split_grid : v->split;
+      li.sched = 3, li.grid = total * li.split;
+      li.nflags = li.grid;
+      if (li.grid / 2 > resident_clusters(2)) return WG_E_VARIANT;
+    } else if (v->clc) {
+      li.sched = 2, li.grid = total;
+    } else if (total <= kSms) {
+      li.sched = 0, li.grid = total;
+    } else {
+      li.sched = 1, li.grid = resident_clusters(2) * 2;
+    }
+  }
+  const wb_kernel_entry* e = wb_find_kernel(li.cg, li.tile_m, li.tile_n, li.direct);
+  if (!e) return WG_E_NOKERNEL;
+  li.kernel_id = e->id;
+  li.epi_rows = e->epi_rows;
+  li.tmem_cols = e->ncols * li.nbuf > 32 ? pow2_cols(e->ncols * li.nbuf) : 32;
+  if (e->ncols * li.nbuf > 512) return WG_E_VARIANT;
+  li.dynsmem = int(e->smem_fixed + size_t(li.depth) * e->stage_bytes);
+  if (li.dynsmem > 232448 || li.depth > 16) return WG_E_VARIANT;
+  li.mbarriers = 2 * li.depth + 4 + 3;
+  li.a_box_rows = li.tile_m / li.cg;
+  li.bt_box_rows = li.tile_n;
+  li.c_box_rows = li.direct ? 0 : li.epi_rows;
+  (void)K;
+  return WG_OK;
+}
+
+extern "C" int wg_header(const wg_variant* v, int M, int N, int K, char* buf, size_t cap) {
+  if (!v || !buf) return WG_E_ARG;
+  wg_launch_info li;
+  const int r = wg_realise(v, M, N, K, &li);
+  if (r != WG_OK) return r;
+  std::string s;
+  char name[128];
+  if (v->prog == WG_PROG_SWAPPED) snprintf(name, sizeof name, "swapped_%d_%d_%d_%dx%d_s%d", M, N, K, v->tile_m, v->tile_n, v->depth);
+  else if (v->prog == WG_PROG_PAIR) snprintf(name, sizeof name, "pair_%d_%d_%d_s%d", M, N, K, v->depth);
+  else snprintf(name, sizeof name, "one_%d_%d_%d_s%d", M, N, K, v->depth);
+  if (v->prog == WG_PROG_SWAPPED) {
+    append(s, "# gemm_swapped %dx%dx%d: %dx%d a CTA, ring depth %d, cluster 2x%d, %d accumulator%s, %s%s%s%s%s%s", M, N, K,
+           v->tile_m, v->tile_n, v->depth, v->cluster_n, v->nbuf, v->nbuf > 1 ? "s" : "",
+           v->clc ? "cluster launch control" : "a fixed grid", v->ask_ahead ? ", asking a stage ahead" : "",
+           v->direct ? ", the store from the registers" : "",
+           v->split > 1 ? ", K split in the cluster" : "", v->split_grid > 1 ? ", K split over the grid" : "",
+           v->split_add ? ", the runs adding in the L2" : "");
+  } else if (v->prog == WG_PROG_PAIR) {
+    append(s, "# gemm_pair %dx%dx%d, ring depth %d, a 2x1 cluster sharing a cta_group::2 MMA", M, N, K, v->depth);
+  } else {
+    append(s, "# gemm_one %dx%dx%d, ring depth %d, one CTA a 128x128 tile", M, N, K, v->depth);
+  }
+  append(s, "# b200 kernel %s: sched %d, cluster %d, tensor memory %d columns", wg_kernel_name(li.kernel_id), li.sched, li.cluster,
+         li.tmem_cols);
+  append(s, ".kernel %s", name);
+  append(s, ".sm sm_100a");
+  append(s, ".barriers 2");
+  append(s, ".threads %d", li.threads);
+  append(s, ".smem 0");
+  append(s, ".dynsmem %d", li.dynsmem);
+  append(s, ".tile %d %d %d", v->tile_m, v->tile_n, kTileK);
+  if (li.direct) append(s, ".ptr c %d %d 4", M, N);
+  else append(s, ".tmap c %d %d 4 %d 32 128", M, N, li.c_box_rows);
+  append(s, ".tmap a %d %d 2 %d 64 128", M, K, li.a_box_rows);
+  append(s, ".tmap bt %d %d 2 %d 64 128", N, K, li.bt_box_rows);
+  if (li.nflags > 0) append(s, ".ptr flags 1 %d 4", li.nflags);
+  append(s, ".grid %d 1", li.grid);
+  append(s, ".mbarriers %d", li.mbarriers);
+  append(s, ".cluster %d", li.cluster);
+  append(s, ".tcgen05");
+  append(s, li.nflags > 0 ? ".params 8 8 8 8" : ".params 8 8 8");
+  if (s.size() + 1 > cap) return WG_E_ARG;
+  std::memcpy(buf, s.c_str(), s.size() + 1);
+  return int(s.size());
+}
+
+extern "C" const char* wg_strerror(int code) {
+  switch (code) {
+    case WG_OK: return "ok";
+    case WG_E_SHAPE: return "no program for this shape";
+    case WG_E_VARIANT: return "inconsistent variant";
+    case WG_E_ARG: return "bad argument";
+    case WG_E_NOKERNEL: return "no compiled kernel realises the variant";
+    case WG_E_DEVICE_WAIT: return "a device-side wait gave up";
+    case WG_E_NODRIVER: return "CUDA driver not available";
+    case WG_E_LIMIT: return "size beyond the stated maximum";
+    default: return code > 0 ? "CUDA error" : "unknown error";
+  }
+}

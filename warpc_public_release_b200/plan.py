@@ -1,0 +1,87 @@
+"""Plans and launches over the C ABI (include/warpc_b200.h). Device memory comes from the
+caller (any allocator: raw pointers are passed); a HostPlan owns device copies and moves
+host buffers in and out, the way backend/node/run_tma.py:68-70, 142 does around a launch."""
+import ctypes
+
+from . import _lib
+from ._lib import LaunchInfo, check
+
+STATUS_NAMES = {0: "ok", 1: "producer: ring stage never released", 2: "MMA: ring stage never filled",
+                3: "MMA: accumulator never released", 4: "epilogue: accumulator never completed",
+                5: "no answer from the scheduler", 6: "scheduler: answer never taken", 7: "scheduler: no answer to the request",
+                8: "a partner's flag never came up", 9: "tensor memory"}
+
+
+class DeviceWaitError(RuntimeError):
+    """A bounded device-side wait gave up; `.status` is (code, detail, cta, parity)."""
+
+    def __init__(self, status):
+        self.status = tuple(status)
+        super().__init__("device wait gave up: %s (detail %#x, CTA %d, parity/target %d)" %
+                         (STATUS_NAMES.get(status[0], "code %d" % status[0]), status[1], status[2], status[3]))
+
+
+class _Base:
+    _h = None
+
+    def info(self):
+        li = LaunchInfo()
+        check(_lib.lib().wg_plan_info(self._h, ctypes.byref(li)), "wg_plan_info")
+        return li
+
+    def set_timeout_ms(self, ms):
+        check(_lib.lib().wg_plan_set_timeout_ms(self._h, int(ms)), "wg_plan_set_timeout_ms")
+
+    def launch(self, stream=None):
+        """One asynchronous launch on `stream` (an integer cudaStream_t; None = default stream)."""
+        check(_lib.lib().wg_launch(self._h, ctypes.c_void_p(stream or 0)), "wg_launch")
+
+    def status(self):
+        """Synchronise and raise DeviceWaitError if any launch gave up."""
+        st = (ctypes.c_uint * 4)()
+        r = _lib.lib().wg_last_device_status(self._h, ctypes.byref(st))
+        if r == _lib.WG_E_DEVICE_WAIT:
+            raise DeviceWaitError(list(st))
+        check(r, "wg_last_device_status")
+        return tuple(st)
+
+    def reset(self):
+        check(_lib.lib().wg_plan_reset(self._h), "wg_plan_reset")
+
+    def close(self):
+        if self._h is not None:
+            _lib.lib().wg_plan_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Plan(_Base):
+    """Tensor maps + kernel-owned words for device pointers dA (M x K fp16), dBt (N x K fp16),
+    dC (M x N fp32), row-major, 16-byte aligned."""
+
+    def __init__(self, variant, m, n, k, dA, dBt, dC, device=0):
+        h = ctypes.c_void_p()
+        check(_lib.lib().wg_plan_create(device, ctypes.byref(variant), m, n, k, ctypes.c_void_p(dA), ctypes.c_void_p(dBt),
+                                        ctypes.c_void_p(dC), ctypes.byref(h)), "wg_plan_create")
+        self._h, self.shape, self.variant = h, (m, n, k), variant
+
+
+class HostPlan(_Base):
+    """A plan that owns device buffers; run(hA, hBt, hC) copies in, launches, copies out, synchronises."""
+
+    def __init__(self, variant, m, n, k, device=0):
+        h = ctypes.c_void_p()
+        check(_lib.lib().wg_host_plan_create(device, ctypes.byref(variant), m, n, k, ctypes.byref(h)), "wg_host_plan_create")
+        self._h, self.shape, self.variant = h, (m, n, k), variant
+
+    def run(self, hA, hBt, hC):
+        """hA, hBt, hC: integer host addresses (e.g. numpy `.ctypes.data`, pinned torch `.data_ptr()`)."""
+        check(_lib.lib().wg_host_run(self._h, ctypes.c_void_p(hA), ctypes.c_void_p(hBt), ctypes.c_void_p(hC)), "wg_host_run")
+
+    def buffer(self, which):
+        return _lib.lib().wg_host_plan_buffer(self._h, which)
