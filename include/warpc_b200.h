@@ -105,6 +105,19 @@ int wg_host_run(void* plan, const void* hA, const void* hBt, void* hC);
 /* device pointers of a host plan: which = 0 A, 1 Bt, 2 C */
 void* wg_host_plan_buffer(void* plan, int which);
 
+/* Mean milliseconds of `repeat` back-to-back launches between two CUDA events on the default
+ * stream after `warmup` untimed ones (backend/node/run_tma.py:171-175, backend/node/cuda.py:79-92). */
+int wg_time_launches(void* plan, int warmup, int repeat, float* ms_mean);
+
+/* Timing builds (the reference's: backend/stamp.ml:9-16, decoded in run_tma.py:176-192): turn
+ * per-phase stamps on or off for the launches that follow, and read them back: 16 events x
+ * 4 tiles of the GPU nanosecond timer per CTA, grid*64 words; returns the words written. */
+int wg_plan_enable_stamps(void* plan, int on);
+int wg_plan_read_stamps(void* plan, unsigned long long* out, size_t cap_words);
+
+/* Where CTA tile index `tile` sits in C under a launch's tile walk (backend/tiles.ml:32-80). */
+int wg_tile_origin(const wg_launch_info* li, int tile, int* row, int* col);
+
 /* Number of compiled kernels and the name of each (for listing). */
 int wg_kernel_count(void);
 const char* wg_kernel_name(int kernel_id);

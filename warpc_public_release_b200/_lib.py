@@ -66,6 +66,10 @@ def lib():
         "wg_host_plan_create": ([i, PV, i, i, i, ctypes.POINTER(vp)], i),
         "wg_host_run": ([vp, vp, vp, vp], i),
         "wg_host_plan_buffer": ([vp, i], vp),
+        "wg_time_launches": ([vp, i, i, ctypes.POINTER(ctypes.c_float)], i),
+        "wg_plan_enable_stamps": ([vp, i], i),
+        "wg_plan_read_stamps": ([vp, ctypes.POINTER(ctypes.c_ulonglong), ctypes.c_size_t], i),
+        "wg_tile_origin": ([PL, i, ctypes.POINTER(i), ctypes.POINTER(i)], i),
         "wg_kernel_count": ([], i),
         "wg_kernel_name": ([i], ctypes.c_char_p),
         "wg_strerror": ([i], ctypes.c_char_p),

@@ -95,6 +95,7 @@ struct Plan {
   KParams p;
   uint32_t* d_flags = nullptr;
   uint32_t* d_status = nullptr;
+  unsigned long long* d_stamps = nullptr;
   size_t flag_bytes = 0;
   // host plans own these
   void *dA = nullptr, *dBt = nullptr, *dC = nullptr;
@@ -265,6 +266,7 @@ extern "C" int wg_plan_destroy(void* plan) {
   if (!pl) return WG_OK;
   if (pl->d_flags) cudaFree(pl->d_flags);
   if (pl->d_status) cudaFree(pl->d_status);
+  if (pl->d_stamps) cudaFree(pl->d_stamps);
   if (pl->owns_buffers) {
     if (pl->dA) cudaFree(pl->dA);
     if (pl->dBt) cudaFree(pl->dBt);
@@ -283,5 +285,57 @@ extern "C" int wg_host_run(void* plan, const void* hA, const void* hBt, void* hC
   if (r != WG_OK) return r;
   WG_CUDA(cudaMemcpyAsync(hC, pl->dC, size_t(pl->M) * pl->N * 4, cudaMemcpyDeviceToHost, 0));
   WG_CUDA(cudaStreamSynchronize(0));
+  return WG_OK;
+}
+
+// Mean milliseconds of `repeat` launches back to back between two CUDA events on the default
+// stream, after `warmup` untimed ones -- the timing backend/node/run_tma.py:171-175 takes.
+extern "C" int wg_time_launches(void* plan, int warmup, int repeat, float* ms_mean) {
+  Plan* pl = static_cast<Plan*>(plan);
+  if (!pl || !ms_mean || repeat < 1) return WG_E_ARG;
+  cudaEvent_t e0, e1;
+  WG_CUDA(cudaEventCreate(&e0));
+  WG_CUDA(cudaEventCreate(&e1));
+  int r = WG_OK;
+  for (int i = 0; i < warmup && r == WG_OK; ++i) r = wg_launch(pl, nullptr);
+  if (r == WG_OK) r = int(cudaEventRecord(e0, 0));
+  for (int i = 0; i < repeat && r == WG_OK; ++i) r = wg_launch(pl, nullptr);
+  if (r == WG_OK) r = int(cudaEventRecord(e1, 0));
+  if (r == WG_OK) r = int(cudaEventSynchronize(e1));
+  float ms = 0;
+  if (r == WG_OK) r = int(cudaEventElapsedTime(&ms, e0, e1));
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  *ms_mean = ms / float(repeat);
+  return r;
+}
+
+// Timing runs: phase stamps (16 events x 4 tiles of the GPU nanosecond timer per CTA) of the
+// launches that follow; wg_plan_read_stamps synchronises and copies grid*64 words out.
+extern "C" int wg_plan_enable_stamps(void* plan, int on) {
+  Plan* pl = static_cast<Plan*>(plan);
+  if (!pl) return WG_E_ARG;
+  const size_t bytes = size_t(pl->li.grid) * 64 * sizeof(unsigned long long);
+  if (on && !pl->d_stamps) {
+    WG_CUDA(cudaMalloc(&pl->d_stamps, bytes));
+  }
+  if (on) WG_CUDA(cudaMemset(pl->d_stamps, 0, bytes));
+  pl->p.stamps = on ? pl->d_stamps : nullptr;
+  return WG_OK;
+}
+
+extern "C" int wg_plan_read_stamps(void* plan, unsigned long long* out, size_t cap_words) {
+  Plan* pl = static_cast<Plan*>(plan);
+  if (!pl || !out || !pl->d_stamps) return WG_E_ARG;
+  const size_t words = size_t(pl->li.grid) * 64;
+  if (cap_words < words) return WG_E_ARG;
+  WG_CUDA(cudaDeviceSynchronize());
+  WG_CUDA(cudaMemcpy(out, pl->d_stamps, words * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+  return int(words);
+}
+
+extern "C" int wg_tile_origin(const wg_launch_info* li, int tile, int* row, int* col) {
+  if (!li || !row || !col || tile < 0) return WG_E_ARG;
+  wb_tile_origin(tile, li->cg, li->tile_m, li->tile_n, li->group > 0 ? li->group : 1, li->cl_n > 0 ? li->cl_n : 1, li->serpentine, row, col);
   return WG_OK;
 }

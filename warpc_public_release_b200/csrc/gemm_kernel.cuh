@@ -19,6 +19,7 @@
 // never leaves the GPU spinning.
 #pragma once
 #include "sm100_ptx.cuh"
+#include "tile_map.h"
 
 namespace wb {
 
@@ -55,6 +56,7 @@ struct KParams {
   uint32_t* flags;              // split-K / stream-K hand-off words
   uint32_t* status;             // 8 words: [0] code, [1] site detail, [2] CTA, [3] parity/stage
   unsigned long long timeout_ns;
+  unsigned long long* stamps;   // timing builds: 16 events x 4 tiles of %globaltimer per CTA, or null
 };
 
 template <int CG_, int TM_, int TN_, bool DIRECT_, int EPI_ROWS_ = 16>
@@ -90,6 +92,7 @@ struct Cfg {
 
 // control block at the end of dynamic shared memory
 struct Ctrl {
+  uint32_t clc_answer[4];  // 16-byte aligned: written by the hardware, read with one 128-bit load
   uint64_t full[16];
   uint64_t empty[16];
   uint64_t acc_full[2];
@@ -97,17 +100,12 @@ struct Ctrl {
   uint64_t clc_bar;      // the cancel request's 16 bytes landed (scheduler's CTA)
   uint64_t sched_full;   // the decoded answer is in `sched_slot` (each CTA)
   uint64_t sched_empty;  // every taker has read it (first CTA)
-  uint32_t clc_answer[4];
   uint32_t sched_slot[2];  // valid, first CTA of the cancelled cluster
   uint32_t tmem_base;
   uint32_t abort;
 };
-static_assert(sizeof(Ctrl) <= 512, "control block");
+static_assert(sizeof(Ctrl) <= 512 && offsetof(Ctrl, clc_answer) % 16 == 0, "control block");
 
-struct Env {
-  const KParams* p;
-  uint32_t abort_addr;  // shared
-};
 
 // K-major, 128-byte-swizzled operand tile: 8-row groups 1024 bytes apart.
 WB_DEV uint64_t smem_desc(uint32_t addr) {
@@ -129,6 +127,14 @@ WB_DEV void record_failure(const KParams& p, uint32_t code, uint32_t detail, uin
     p.status[3] = parity;
     __threadfence();
   }
+}
+
+// Phase stamps of a timing run (the reference's are backend/stamp.ml:9-16): event `ev` of
+// the CTA's `slot`-th tile, on the GPU-wide nanosecond timer.
+enum : int { EV_ENTRY = 0, EV_SETUP = 1, EV_LOAD_FIRST = 2, EV_LOAD_LAST = 3, EV_MMA_FIRST = 4, EV_MMA_LAST = 5,
+             EV_ACC_READY = 6, EV_STORED = 7, EV_TEARDOWN = 8, EV_EXIT = 9, EV_ACC_FREE = 10 };
+WB_DEV void stamp(const KParams& p, int ev, int slot) {
+  if (p.stamps != nullptr && slot < 4) p.stamps[(size_t(blockIdx.x) * 16 + ev) * 4 + slot] = globaltimer();
 }
 
 // Bounded wait on an mbarrier phase. Returns false when the kernel is giving up.
@@ -250,19 +256,9 @@ struct Walker {
   }
 };
 
-// Where a CTA tile sits in C: the tile index's digits, fastest first, are the CTA's rank
-// in its pair (along columns), the row within a group of `group` cluster rows, the
-// cluster column, the band; with `serp` odd bands run right to left.
-// (The reference's map: backend/tiles.ml:32-80.)
 template <class C>
 WB_DEV void tile_origin(const KParams& p, int tile, int& row, int& col) {
-  const int rank = tile % C::CG, c = tile / C::CG;
-  const int rig = c & (p.group - 1), rest = c / p.group;
-  int colc = rest % p.cl_n;
-  const int band = rest / p.cl_n;
-  if (p.serp && (band & 1)) colc ^= (p.cl_n - 1);
-  row = (band * p.group + rig) * C::TM;
-  col = (colc * C::CG + rank) * C::TN;
+  wb_tile_origin(tile, C::CG, C::TM, C::TN, p.group, p.cl_n, p.serp, &row, &col);
 }
 
 // ------------------------------------------------------------------ epilogue pieces
@@ -288,6 +284,75 @@ WB_DEV void epi_coords(int row, int col, int q, int i, int& y, int& x) {
   }
 }
 
+// One tile's accumulator out through the staging copies: each block loaded from tensor
+// memory while the block before it is staged and handed to the copy engine.  `add` selects
+// the reducing store (C += block, performed in the L2).  The accumulator is released on the
+// leader's barrier as soon as the last block is in registers.
+template <class C>
+WB_DEV void epi_staged_tile(const CUtensorMap* map_c, uint32_t tbase, uint32_t my_staging, int row, int col, int q, uint32_t lane,
+                            bool add, uint32_t acc_empty_addr) {
+  uint32_t v[2][C::EPI_ROWS];
+  epi_load<C>(tbase, 0, v[0]);
+#pragma unroll
+  for (int i = 0; i < C::NBLK; ++i) {
+    tmem_wait_ld();
+    if (i + 1 < C::NBLK) {
+      epi_load<C>(tbase, i + 1, v[(i + 1) & 1]);
+    } else {
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if constexpr (C::CG == 2) mbar_arrive_cluster(acc_empty_addr);
+        else mbar_arrive(acc_empty_addr);
+      }
+    }
+    int y, x;
+    epi_coords<C>(row, col, q, i, y, x);
+    const uint32_t copy = my_staging + uint32_t(i & 1) * C::EPI_COPY_BYTES;
+    if (lane == 0) bulk_wait_read<1>();  // the store that last read this copy is done with it
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < C::EPI_ROWS; ++j)  // 128-byte swizzle: 16-byte chunk index xor row-in-8
+      st_shared_u32(copy + uint32_t(j) * 128u + ((lane * 4u) ^ (uint32_t(j & 7) << 4)), v[i & 1][j]);
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      if (add) tma_reduce_add_2d(map_c, x, y, copy);
+      else tma_store_2d(map_c, x, y, copy);
+      bulk_commit();
+    }
+  }
+}
+
+// Straight from the registers: register j of a block is row y + j, the warp's lanes are 32
+// consecutive columns, so each register goes out as one 128-byte row segment.
+template <class C>
+WB_DEV void epi_direct_tile(const KParams& p, uint32_t tbase, int row, int col, int q, uint32_t lane, uint32_t acc_empty_addr) {
+  uint32_t v[2][C::EPI_ROWS];
+  epi_load<C>(tbase, 0, v[0]);
+#pragma unroll
+  for (int i = 0; i < C::NBLK; ++i) {
+    tmem_wait_ld();
+    if (i + 1 < C::NBLK) {
+      epi_load<C>(tbase, i + 1, v[(i + 1) & 1]);
+    } else {
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if constexpr (C::CG == 2) mbar_arrive_cluster(acc_empty_addr);
+        else mbar_arrive(acc_empty_addr);
+      }
+    }
+    int y, x;
+    epi_coords<C>(row, col, q, i, y, x);
+    float* dst = p.C + size_t(y) * size_t(p.N) + size_t(x) + lane;
+    const bool col_ok = (x + int(lane)) < p.N;
+#pragma unroll
+    for (int j = 0; j < C::EPI_ROWS; ++j)
+      if (col_ok && (y + j) < p.M) dst[size_t(j) * size_t(p.N)] = __uint_as_float(v[i & 1][j]);
+  }
+}
+
 template <class C>
 __global__ void __launch_bounds__(256, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -305,6 +370,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   const uint32_t rank = (CG == 2) ? cluster_ctarank() : 0u;
   const bool leader = (rank == 0);
   const int depth = p.depth, nbuf = p.nbuf;
+  if (threadIdx.x == 0) stamp(p, EV_ENTRY, 0);
 
   auto full_bar = [&](int s) { return ctrl_at(offsetof(Ctrl, full) + 8 * s); };
   auto empty_bar = [&](int s) { return ctrl_at(offsetof(Ctrl, empty) + 8 * s); };
@@ -345,13 +411,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   }
   tc_fence_after();
   const uint32_t tmem_base = ld_shared_u32(ctrl_at(offsetof(Ctrl, tmem_base)));
+  if (threadIdx.x == 0) stamp(p, EV_SETUP, 0);
 
   // ---------------------------------------------------------------- roles
   if (warp == 0) {
     // ===== producer: TMA loads into this CTA's ring, counted on the leader's barrier
     Walker<C> walk(p, ctrl, rank, lane);
     Work w;
-    int stage = 0;
+    int stage = 0, nth = 0;
     uint32_t phase = 0;
     bool ok = true;
     while (ok && walk.next(w)) {
@@ -370,10 +437,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           const uint32_t sa = ring + uint32_t(stage) * C::STAGE_BYTES, sb = sa + C::A_BYTES;
           tma_load_2d<CG>(sa, &map_a, kk * C::TK, a_row, bar);
           tma_load_2d<CG>(sb, &map_b, kk * C::TK, col, bar);
+          if (kk == w.kb) stamp(p, EV_LOAD_FIRST, nth);
         }
         __syncwarp();
         if (++stage == depth) stage = 0, phase ^= 1u;
       }
+      if (lane == 0) stamp(p, EV_LOAD_LAST, nth);
+      ++nth;
     }
     // every stage this CTA filled has been released before it leaves
     for (int i = 0; ok && i < depth; ++i) {
@@ -385,7 +455,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     if (leader) {
       Walker<C> walk(p, ctrl, rank, lane);
       Work w;
-      int stage = 0, acc = 0;
+      int stage = 0, acc = 0, nth = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
       const uint16_t mask = (CG == 2) ? 0x3 : 0x1;
@@ -395,6 +465,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           break;
         }
         tc_fence_after();
+        if (lane == 0) stamp(p, EV_ACC_FREE, nth);
         const uint32_t d = tmem_base + uint32_t(acc * C::NCOLS);
         uint32_t accumulate = 0;
         bool landed = false;
@@ -404,6 +475,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             break;
           }
           tc_fence_after();
+          if (kk == w.kb && lane == 0) stamp(p, EV_MMA_FIRST, nth);
           const uint32_t sa = ring + uint32_t(stage) * C::STAGE_BYTES, sb = sa + C::A_BYTES;
           if (lane == 0) {
 #pragma unroll
@@ -427,9 +499,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           stage = nstage, phase = nphase;
         }
         if (!ok) break;
-        if (lane == 0) umma_commit<CG>(acc_full_bar(acc), mask);  // the accumulator is complete in both CTAs
+        if (lane == 0) {
+          umma_commit<CG>(acc_full_bar(acc), mask);  // the accumulator is complete in both CTAs
+          stamp(p, EV_MMA_LAST, nth);
+        }
         __syncwarp();
         if (++acc == nbuf) acc = 0, acc_phase ^= 1u;
+        ++nth;
       }
       // every accumulator has been read out in both CTAs before leaving
       for (int i = 0; ok && i < nbuf; ++i) {
@@ -473,64 +549,113 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   } else if (warp >= 4) {
     // ===== epilogue: tensor memory -> registers -> C
     const int q = int(warp & 3u);
+    const bool first_warp = (warp == 4);
     Walker<C> walk(p, ctrl, rank, lane);
     Work w;
-    int acc = 0;
+    int acc = 0, nth = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
     const uint32_t acc_empty_leader = (CG == 2) ? mapa(acc_empty_bar(0), 0) : acc_empty_bar(0);
     const uint32_t my_staging = staging + uint32_t(q) * 2u * C::EPI_COPY_BYTES;
-    while (ok && walk.next(w)) {
+    // K split between CTAs (split-K over the grid, stream-K): hand-off words count launches,
+    // never reset: every CTA's own word holds how many launches have gone by, so one past it
+    // is the value all flags of this launch reach (gemm_swapped.ml:608-626)
+    const bool shared_k = !C::DIRECT && (p.sched == SCHED_SPLITK || p.sched == SCHED_STREAMK);
+    uint32_t target = 0;
+    if (shared_k) {
+      target = ld_relaxed_gpu(p.flags + blockIdx.x) + 1u;
+      if (p.sched == SCHED_STREAMK) {
+        named_bar_sync(2, 128);  // every epilogue thread has read the word before it moves on
+        if (first_warp && lane == 0) st_relaxed_gpu(p.flags + blockIdx.x, target);
+      }
+    }
+    while (walk.next(w)) {
       int row, col;
       tile_origin<C>(p, w.tile, row, col);
-      if (!wait_bar(p, abort_addr, acc_full_bar(acc), acc_phase, ST_WAIT_ACC_FULL, uint32_t(acc))) {
-        ok = false;
-        break;
-      }
-      tc_fence_after();
       const uint32_t tbase = tmem_base + uint32_t(acc * C::NCOLS) + (uint32_t(q * 32) << 16);
-      uint32_t v[2][C::EPI_ROWS];
-      epi_load<C>(tbase, 0, v[0]);
+      const uint32_t acc_empty_addr = acc_empty_leader + 8u * uint32_t(acc);
+      if constexpr (C::DIRECT) {
+        if (!wait_bar(p, abort_addr, acc_full_bar(acc), acc_phase, ST_WAIT_ACC_FULL, uint32_t(acc))) break;
+        tc_fence_after();
+        if (first_warp && lane == 0) stamp(p, EV_ACC_READY, nth);
+        epi_direct_tile<C>(p, tbase, row, col, q, lane, acc_empty_addr);
+      } else if (!shared_k) {
+        if (!wait_bar(p, abort_addr, acc_full_bar(acc), acc_phase, ST_WAIT_ACC_FULL, uint32_t(acc))) break;
+        tc_fence_after();
+        if (first_warp && lane == 0) stamp(p, EV_ACC_READY, nth);
+        epi_staged_tile<C>(&map_c, tbase, my_staging, row, col, q, lane, false, acc_empty_addr);
+      } else if (p.sched == SCHED_SPLITK) {
+        // ---- split-K over the grid, adding in the L2 (gemm_swapped.ml:660-710).  The S runs
+        // of a tile first zero disjoint shares of it (while their k loops run), raise their
+        // flags, and once all S flags are up each adds its whole accumulator to C.
+        // No warp leaves this block early: all four meet at the named barriers.
+        const int S = p.split, c = int(blockIdx.x) / CG, s = c % S;
+        if (lane == 0) bulk_wait_read<0>();
+        __syncwarp();
 #pragma unroll
-      for (int i = 0; i < C::NBLK; ++i) {
-        tmem_wait_ld();
-        if (i + 1 < C::NBLK) {
-          epi_load<C>(tbase, i + 1, v[(i + 1) & 1]);
-        } else {
-          // the last block is out of tensor memory: the accumulator may be overwritten
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) {
-            if constexpr (CG == 2) mbar_arrive_cluster(acc_empty_leader + 8u * uint32_t(acc));
-            else mbar_arrive(acc_empty_leader + 8u * uint32_t(acc));
+        for (int j = 0; j < C::EPI_ROWS; ++j) st_shared_u32(my_staging + uint32_t(j) * 128u + lane * 4u, 0u);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          for (int i = 0; i < C::NBLK; ++i) {
+            if (i * S / C::NBLK != s) continue;
+            int y, x;
+            epi_coords<C>(row, col, q, i, y, x);
+            tma_store_2d(&map_c, x, y, my_staging);
           }
+          bulk_commit();
+          bulk_wait<0>();  // the zeros are written, not just read out of shared memory
+          fence_proxy_async_global();
         }
-        int y, x;
-        epi_coords<C>(row, col, q, i, y, x);
-        if constexpr (C::DIRECT) {
-          // register j is row y + j; the warp's lanes are 32 consecutive columns
-          float* dst = p.C + size_t(y) * size_t(p.N) + size_t(x) + lane;
-          const bool col_ok = (x + int(lane)) < p.N;
-#pragma unroll
-          for (int j = 0; j < C::EPI_ROWS; ++j)
-            if (col_ok && (y + j) < p.M) dst[size_t(j) * size_t(p.N)] = __uint_as_float(v[i & 1][j]);
-        } else {
-          // stage the block as EPI_ROWS rows of 128 bytes, then one TMA store (clipped at C's edges)
-          const uint32_t copy = my_staging + uint32_t(i & 1) * C::EPI_COPY_BYTES;
-          if (lane == 0) bulk_wait_read<1>();  // the store that last read this copy is done with it
-          __syncwarp();
-#pragma unroll
-          for (int j = 0; j < C::EPI_ROWS; ++j)  // 128-byte swizzle: 16-byte chunk index xor row-in-8
-            st_shared_u32(copy + uint32_t(j) * 128u + ((lane * 4u) ^ (uint32_t(j & 7) << 4)), v[i & 1][j]);
-          fence_proxy_async_smem();
-          __syncwarp();
+        __syncwarp();
+        fence_acq_rel_gpu();
+        named_bar_sync(2, 128);
+        if (first_warp && lane == 0) st_relaxed_gpu(p.flags + blockIdx.x, target);
+        ok = wait_bar(p, abort_addr, acc_full_bar(acc), acc_phase, ST_WAIT_ACC_FULL, uint32_t(acc));
+        tc_fence_after();
+        if (first_warp && lane == 0) stamp(p, EV_ACC_READY, nth);
+        if (first_warp) {
+          // the flags of the tile's S runs, same rank: lane j polls run j's
+          const int base = (c / S) * S;
+          for (int j = int(lane); ok && j < S; j += 32)
+            ok = wait_flag(p, abort_addr, p.flags + (base + j) * CG + int(rank), target, uint32_t(j));
+        }
+        fence_acq_rel_gpu();
+        fence_proxy_async_global();
+        named_bar_sync(2, 128);
+        ok = ok && (ld_shared_u32(abort_addr) == 0u);
+        if (ok) epi_staged_tile<C>(&map_c, tbase, my_staging, row, col, q, lane, true, acc_empty_addr);
+      } else {
+        // ---- stream-K, adding in the L2 (gemm_swapped.ml:633-659): the segment holding the
+        // tile's first k-step stores and raises the tile's flag; the others wait for it and add.
+        uint32_t* tile_flag = p.flags + gridDim.x + w.tile;
+        if (w.kb == 0) {
+          ok = wait_bar(p, abort_addr, acc_full_bar(acc), acc_phase, ST_WAIT_ACC_FULL, uint32_t(acc));
+          tc_fence_after();
+          if (ok) epi_staged_tile<C>(&map_c, tbase, my_staging, row, col, q, lane, false, acc_empty_addr);
           if (lane == 0) {
-            tma_store_2d(&map_c, x, y, copy);
-            bulk_commit();
+            bulk_wait<0>();
+            fence_proxy_async_global();
           }
+          __syncwarp();
+          fence_acq_rel_gpu();
+          named_bar_sync(2, 128);
+          if (ok && first_warp && lane == 0) st_relaxed_gpu(tile_flag, target);
+        } else {
+          if (first_warp) ok = wait_flag(p, abort_addr, tile_flag, target, uint32_t(w.tile));
+          fence_acq_rel_gpu();
+          fence_proxy_async_global();
+          named_bar_sync(2, 128);
+          ok = ok && (ld_shared_u32(abort_addr) == 0u);
+          ok = ok && wait_bar(p, abort_addr, acc_full_bar(acc), acc_phase, ST_WAIT_ACC_FULL, uint32_t(acc));
+          tc_fence_after();
+          if (ok) epi_staged_tile<C>(&map_c, tbase, my_staging, row, col, q, lane, true, acc_empty_addr);
         }
       }
+      if (!ok) break;
+      if (first_warp && lane == 0) stamp(p, EV_STORED, nth);
       if (++acc == nbuf) acc = 0, acc_phase ^= 1u;
+      ++nth;
     }
     if constexpr (!C::DIRECT) {
       if (lane == 0) bulk_wait_read<0>();  // the last stores have read their staging copies
@@ -540,6 +665,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 
   // ---------------------------------------------------------------- teardown
   __syncwarp();
+  if (threadIdx.x == 0) stamp(p, EV_TEARDOWN, 0);
   if (ld_shared_u32(abort_addr) != 0u) {
     // giving up: let copies and MMAs in flight land before the shared and tensor memory go away
     const uint64_t t0 = globaltimer();
@@ -557,6 +683,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     tc_fence_after();
     tmem_dealloc<CG>(tmem_base, uint32_t(C::pow2_ge(C::NCOLS * nbuf)));
   }
+  if (threadIdx.x == 0) stamp(p, EV_EXIT, 0);
 }
 
 }  // namespace wb

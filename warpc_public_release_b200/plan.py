@@ -36,6 +36,25 @@ class _Base:
         """One asynchronous launch on `stream` (an integer cudaStream_t; None = default stream)."""
         check(_lib.lib().wg_launch(self._h, ctypes.c_void_p(stream or 0)), "wg_launch")
 
+    def time_launches(self, repeat, warmup=3):
+        """Mean milliseconds of `repeat` back-to-back launches between CUDA events (run_tma.py:171-175)."""
+        ms = ctypes.c_float()
+        check(_lib.lib().wg_time_launches(self._h, int(warmup), int(repeat), ctypes.byref(ms)), "wg_time_launches")
+        return ms.value
+
+    def enable_stamps(self, on=True):
+        check(_lib.lib().wg_plan_enable_stamps(self._h, int(bool(on))), "wg_plan_enable_stamps")
+
+    def read_stamps(self):
+        """Phase stamps of the last launches: array [grid, 16 events, 4 tiles] of GPU-timer nanoseconds (0 = not reached)."""
+        import numpy as np
+        grid = self.info().grid
+        buf = (ctypes.c_ulonglong * (grid * 64))()
+        r = _lib.lib().wg_plan_read_stamps(self._h, buf, grid * 64)
+        if r < 0:
+            check(r, "wg_plan_read_stamps")
+        return np.frombuffer(buf, dtype=np.uint64).reshape(grid, 16, 4).copy()
+
     def status(self):
         """Synchronise and raise DeviceWaitError if any launch gave up."""
         st = (ctypes.c_uint * 4)()
