@@ -115,6 +115,11 @@ int wg_time_launches(void* plan, int warmup, int repeat, float* ms_mean);
 int wg_plan_enable_stamps(void* plan, int on);
 int wg_plan_read_stamps(void* plan, unsigned long long* out, size_t cap_words);
 
+/* Test hook for the bounded device-side waits (the reference's kernels spin without bound,
+ * backend/sass.ml:339; its harness only has a reader for "waits that gave up",
+ * backend/node/run_tma.py:129-137): overwrite hand-off word `index` of a split-K / stream-K plan. */
+int wg_plan_debug_set_flag(void* plan, int index, unsigned value);
+
 /* Where CTA tile index `tile` sits in C under a launch's tile walk (backend/tiles.ml:32-80). */
 int wg_tile_origin(const wg_launch_info* li, int tile, int* row, int* col);
 

@@ -1,0 +1,163 @@
+"""Host side of the C ABI, no GPU needed: the library loads and exports what include/*.h
+declares; the C++ rule, geometry, tile walk and header agree with the oracle and with the
+fixtures the reference's own reader produced."""
+import ctypes
+import json
+import os
+import re
+import subprocess
+import sys
+
+import pytest
+
+import warpc_public_release_b200 as w
+from warpc_public_release_b200 import _lib, launch_header
+from oracle import rule
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+BENCH_SHAPES = [(1024, 1024, 1024), (1536, 1536, 1536), (2048, 2048, 2048), (3072, 1280, 2048), (4096, 4096, 1024),
+                (4096, 4096, 4096), (8192, 2048, 4096), (8192, 8192, 8192), (16384, 16384, 16384), (2048, 2048, 16384),
+                (1024, 1024, 65536)]
+
+
+def test_library_exports_every_declared_symbol():
+    text = open(os.path.join(ROOT, "include", "warpc_b200.h")).read()
+    declared = sorted(set(re.findall(r"\b(wg_[a-z_0-9]+)\s*\(", text)))
+    assert len(declared) >= 20
+    lib = ctypes.CDLL(_lib.LIB_PATH)
+    missing = [name for name in declared if not hasattr(lib, name)]
+    assert missing == []
+    assert _lib.lib().wg_kernel_count() >= 12
+    assert _lib.lib().wg_strerror(-1).decode() == "no program for this shape"
+
+
+RULE_FIELDS = ("tile_m", "tile_n", "depth", "cluster_n", "clc", "ask_ahead", "direct", "serpentine", "group", "streamk", "split",
+               "split_grid", "split_add", "late_launch", "reps", "atom_m", "tmem_cols", "nbuf", "alloc_cols", "tiles_m", "tiles_n",
+               "total_tiles", "ctas", "grid", "kt", "a_box_rows", "bt_box_rows", "stage_bytes", "tx_bytes", "nflags")
+
+
+def _same(v, r):
+    assert ("swapped", "pair", "one")[v.prog] == r["prog"]
+    if r["prog"] != "swapped":
+        assert (v.grid, v.total_tiles, v.depth, v.ref_dynsmem) == (r["grid"], r["total_tiles"], r["depth"], r["dynsmem"])
+        return
+    for f in RULE_FIELDS:
+        assert int(getattr(v, f)) == int(r[f]), (f, getattr(v, f), r[f])
+    assert v.ref_dynsmem == r["dynsmem"] and v.ref_mbarriers == r["mbarriers"]
+
+
+@pytest.mark.parametrize("sm", ["sm_100a", "sm_103a"])
+def test_rule_matches_oracle_on_benchmark_shapes(sm):
+    for s in BENCH_SHAPES + [(2048, 16384, 16384), (4096, 16384, 16384), (8192, 16384, 16384)]:
+        _same(w.choose(*s, sm=sm), rule.choose(*s, target=sm))
+
+
+def test_rule_matches_oracle_on_a_grid_of_shapes():
+    ms = [64, 128, 192, 256, 384, 512, 640, 1024, 1152, 1536, 2048, 2304, 3072, 4096, 8192]
+    ks = [64, 128, 1024, 4096, 8192, 16384, 65536]
+    checked = refused = 0
+    for m in ms:
+        for n in ms:
+            for k in ks:
+                try:
+                    r = rule.choose(m, n, k)
+                except rule.Refused:
+                    with pytest.raises(_lib.WarpcError) as e:
+                        w.choose(m, n, k)
+                    assert e.value.code == _lib.WG_E_SHAPE
+                    refused += 1
+                    continue
+                _same(w.choose(m, n, k), r)
+                checked += 1
+    assert checked > 1000 and refused > 0
+
+
+def test_explicit_variants_and_refusals():
+    _same(w.swapped(1024, 1024, 65536, 256, 256, 4, split_grid=9, split_add=True, ask_ahead=True), rule.choose(1024, 1024, 65536))
+    _same(w.swapped(4096, 4096, 4096, 128, 128, 8, cluster_n=2, clc=True), rule.swapped(4096, 4096, 4096, 128, 128, 8, cluster_n=2, clc=True))
+    _same(w.pair(2048, 1152, 512, 8), rule.pair(2048, 1152, 512, 8))
+    _same(w.one(1152, 1152, 64, 4), rule.one(1152, 1152, 64, 4))
+    for kw in (dict(streamk=True, clc=True), dict(direct=True, split_grid=2, split_add=True), dict(split_add=True),
+               dict(split=2, cluster_n=1, direct=True)):
+        with pytest.raises(rule.Refused):
+            rule.swapped(1024, 1024, 1024, 128, 128, 4, **kw)
+        with pytest.raises(_lib.WarpcError) as e:
+            w.swapped(1024, 1024, 1024, 128, 128, 4, **kw)
+        assert e.value.code == _lib.WG_E_VARIANT
+    with pytest.raises(_lib.WarpcError):
+        w.swapped(1000, 1024, 1024, 128, 128, 4, direct=True)   # the store from the registers needs whole tiles
+    with pytest.raises(_lib.WarpcError):
+        w.swapped(1024, 1024, 1024, 256, 256, 8)                # shared memory
+    with pytest.raises(ValueError):
+        w.choose(1024, 1024, 1024, sm="sm_90a")
+
+
+def test_tile_walk_matches_oracle():
+    r, c = ctypes.c_int(), ctypes.c_int()
+    for s in BENCH_SHAPES[:8] + [(2048, 2048, 16384), (1024, 1024, 65536), (512, 768, 512)]:
+        v = w.choose(*s)
+        li = w.realise(v, *s)
+        tiles_m, tiles_n = -(-s[0] // li.tile_m), -(-s[1] // li.tile_n)
+        seen = set()
+        for t in range(tiles_m * tiles_n):
+            assert _lib.lib().wg_tile_origin(ctypes.byref(li), t, ctypes.byref(r), ctypes.byref(c)) == 0
+            want = rule.tile_origin(t, tiles_m, tiles_n, li.tile_m, li.tile_n, pair=li.cg, pairs=1, pair_on_cols=True,
+                                    group=v.group if li.cg == 2 else 1, serpentine=bool(v.serpentine))
+            assert (r.value, c.value) == want, (s, t)
+            seen.add(want)
+        assert len(seen) == tiles_m * tiles_n
+
+
+def test_headers_match_what_the_reference_reader_parsed(golden_dir):
+    gold = json.load(open(os.path.join(golden_dir, "headers.json")))["headers"]
+    assert len(gold) == 11
+    for g in gold:
+        m, n, k = g["shape"]
+        text = w.header(w.choose(m, n, k), m, n, k)
+        assert text == g["text"], "header text changed: rerun tests/golden/make_golden.py"
+        assert launch_header.parse_header(text) == g["parsed_by_reference"]
+        hdr = launch_header.parse_header(text)
+        assert launch_header.shape_of(hdr) == (m, n, k)
+        li = w.realise(w.choose(m, n, k), m, n, k)
+        assert int(hdr["dynsmem"]) == li.dynsmem and hdr["grid"] == "%d 1" % li.grid and int(hdr["cluster"]) == li.cluster
+        assert hdr["kernel"] == rule.choose(m, n, k)["name"]
+        a, bt = launch_header.parameter(hdr, "a"), launch_header.parameter(hdr, "bt")
+        assert (a["box_rows"], a["box_cols"], a["swizzle"]) == (li.a_box_rows, 64, 128)
+        assert (bt["box_rows"], bt["box_cols"], bt["swizzle"]) == (li.bt_box_rows, 64, 128)
+        assert li.dynsmem <= 232448 and li.tmem_cols <= 512
+
+
+def test_realisation_invariants():
+    for s in BENCH_SHAPES + [(2048, 1152, 512), (1152, 1152, 64), (256, 384, 512)]:
+        v = w.choose(*s)
+        li = w.realise(v, *s)
+        assert li.grid % li.cluster == 0 and li.threads == 256
+        if li.sched in (3, 4):        # K shared between CTAs: every CTA resident at once, flags sized for the grid
+            assert li.grid <= 148 and li.nflags >= li.grid
+        if li.sched == 1:
+            assert li.grid == 148
+        assert li.group & (li.group - 1) == 0
+
+
+def test_gemm_command_line():
+    run = lambda *a: subprocess.run([sys.executable, "-m", "warpc_public_release_b200.gemm", *a], cwd=ROOT, capture_output=True, text=True)
+    ok = run("gemm", "2048", "2048", "2048")
+    assert ok.returncode == 0 and ".kernel swapped_2048_2048_2048_128x128_s8" in ok.stdout and ".cluster 2" in ok.stdout
+    assert run("--sm", "sm_103a", "gemm", "1024", "1024", "1024").returncode == 0
+    assert run("gemm", "100", "100", "100").returncode == 1
+    assert run("--sm", "sm_90a", "gemm", "1024", "1024", "1024").returncode == 1
+    assert run("frobnicate").returncode == 2
+    sw = run("swapped", "1024", "1024", "65536", "256", "256", "4", "--split-grid", "9", "--split-add", "--ask-ahead")
+    assert sw.returncode == 0 and ".ptr flags 1 144 4" in sw.stdout
+
+
+def test_no_cpu_fallback_without_a_device():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    v = w.choose(256, 256, 64)
+    with pytest.raises(_lib.WarpcError) as e:
+        w.Plan(v, 256, 256, 64, 0x1000, 0x2000, 0x3000)
+    assert e.value.code != 0
+    with pytest.raises(_lib.WarpcError):
+        w.HostPlan(v, 256, 256, 64)

@@ -1,0 +1,64 @@
+"""The multi-GPU plan's host logic on CPU ranks (gloo, world size 2): which rows a rank owns,
+which program its slab gets, and that gathering the slabs in rank order rebuilds C.  The slabs'
+values come from the oracle here (no GPU); the GPU path swaps in the kernel for that one step."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank, world, port, m, n, k, out_dir):
+    sys.path.insert(0, ROOT)
+    import torch
+    import torch.distributed as dist
+    from warpc_public_release_b200 import shard
+    from oracle import gemm_ref
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    a, bt = gemm_ref.inputs_integers(m, n, k)          # every rank draws the same matrices, keeps its rows
+    lo, hi = shard.slab_rows(m, world, rank)
+    c_full = torch.full((m, n), float("nan"), dtype=torch.float32)
+    c_local = c_full[lo:hi]
+    c_local.copy_(torch.from_numpy(gemm_ref.gemm_ref(a[lo:hi], bt)))   # stand-in for the rank's kernel launch
+    shard.gather_slabs(c_full, c_local)
+    np.save(os.path.join(out_dir, "c_rank%d.npy" % rank), c_full.numpy())
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_row_sharded_gemm_world_size_2(tmp_path):
+    import torch.multiprocessing as mp
+    from oracle import gemm_ref
+    m, n, k, world = 512, 256, 128, 2
+    mp.spawn(_rank_main, args=(world, _free_port(), m, n, k, str(tmp_path)), nprocs=world, join=True)
+    a, bt = gemm_ref.inputs_integers(m, n, k)
+    ref = gemm_ref.gemm_ref(a, bt)
+    for r in range(world):
+        assert np.array_equal(np.load(tmp_path / ("c_rank%d.npy" % r)), ref)
+
+
+def test_slab_rows_and_programs():
+    from warpc_public_release_b200 import shard
+    assert [shard.slab_rows(16384, 8, r) for r in (0, 3, 7)] == [(0, 2048), (6144, 8192), (14336, 16384)]
+    with pytest.raises(ValueError):
+        shard.slab_rows(1000, 3, 0)
+    covered = sorted(shard.slab_rows(16384, 4, r) for r in range(4))
+    assert covered[0][0] == 0 and covered[-1][1] == 16384 and all(covered[i][1] == covered[i + 1][0] for i in range(3))
+    # every slab of the sharded shape keeps the large-shape program; the rule alone would drop to 192 x 128 at 8 GPUs
+    for g in (1, 2, 4, 8):
+        v = shard.slab_variant(16384 // g, 16384, 16384)
+        assert (v.tile_m, v.tile_n, v.depth, v.clc, v.serpentine) == (256, 256, 4, 1, 1)
+    v = shard.slab_variant(2048, 16384, 16384, pin_large=False)
+    assert (v.tile_m, v.tile_n) == (192, 128)
+    v = shard.slab_variant(1024, 1024, 1024)
+    assert (v.tile_m, v.tile_n) == (128, 64)

@@ -69,6 +69,7 @@ def lib():
         "wg_time_launches": ([vp, i, i, ctypes.POINTER(ctypes.c_float)], i),
         "wg_plan_enable_stamps": ([vp, i], i),
         "wg_plan_read_stamps": ([vp, ctypes.POINTER(ctypes.c_ulonglong), ctypes.c_size_t], i),
+        "wg_plan_debug_set_flag": ([vp, i, u], i),
         "wg_tile_origin": ([PL, i, ctypes.POINTER(i), ctypes.POINTER(i)], i),
         "wg_kernel_count": ([], i),
         "wg_kernel_name": ([i], ctypes.c_char_p),

@@ -339,3 +339,14 @@ extern "C" int wg_tile_origin(const wg_launch_info* li, int tile, int* row, int*
   wb_tile_origin(tile, li->cg, li->tile_m, li->tile_n, li->group > 0 ? li->group : 1, li->cl_n > 0 ? li->cl_n : 1, li->serpentine, row, col);
   return WG_OK;
 }
+
+// Test hook for the bounded waits: overwrite one hand-off word of a split-K / stream-K plan.
+// A CTA whose word disagrees with its partners' makes their flag waits run out, which must end
+// as a recorded status (WG_E_DEVICE_WAIT), never as a hang.
+extern "C" int wg_plan_debug_set_flag(void* plan, int index, unsigned value) {
+  Plan* pl = static_cast<Plan*>(plan);
+  if (!pl || index < 0 || size_t(index) * sizeof(uint32_t) >= pl->flag_bytes) return WG_E_ARG;
+  WG_CUDA(cudaDeviceSynchronize());
+  WG_CUDA(cudaMemcpy(pl->d_flags + index, &value, sizeof value, cudaMemcpyHostToDevice));
+  return WG_OK;
+}

@@ -290,6 +290,9 @@ extern "C" int wg_realise(const wg_variant* v, int M, int N, int K, wg_launch_in
   li.epi_rows = e->epi_rows;
   li.tmem_cols = e->ncols * li.nbuf > 32 ? pow2_cols(e->ncols * li.nbuf) : 32;
   if (e->ncols * li.nbuf > 512) return WG_E_VARIANT;
+  // this kernel's staging copies and control block are larger than the reference's: where the
+  // reference's ring depth no longer fits beside them, the ring is one or two stages shorter
+  while (li.depth > 2 && e->smem_fixed + size_t(li.depth) * e->stage_bytes > 232448) li.depth -= 1;
   li.dynsmem = int(e->smem_fixed + size_t(li.depth) * e->stage_bytes);
   if (li.dynsmem > 232448 || li.depth > 16) return WG_E_VARIANT;
   li.mbarriers = 2 * li.depth + 4 + 3;

@@ -64,6 +64,9 @@ class _Base:
         check(r, "wg_last_device_status")
         return tuple(st)
 
+    def debug_set_flag(self, index, value):
+        check(_lib.lib().wg_plan_debug_set_flag(self._h, int(index), int(value)), "wg_plan_debug_set_flag")
+
     def reset(self):
         check(_lib.lib().wg_plan_reset(self._h), "wg_plan_reset")
 
