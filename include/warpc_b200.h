@@ -123,6 +123,27 @@ int wg_plan_debug_set_flag(void* plan, int index, unsigned value);
 /* Where CTA tile index `tile` sits in C under a launch's tile walk (backend/tiles.ml:32-80). */
 int wg_tile_origin(const wg_launch_info* li, int tile, int* row, int* col);
 
+/* One launch that allocates nothing.  It has no counterpart in the reference (whose harness
+ * allocates every buffer up front, backend/node/run_tma.py:68-95).  It is for callers that
+ * cannot allocate device memory where they call: inside another framework's memory pool or a
+ * fixed memory budget, in a latency-critical loop (cudaMalloc synchronises the device), or
+ * after the application has given all free memory to its own allocator.  The kernel's own
+ * words (split-K / stream-K hand-off flags, status) live in a device array built into the
+ * library: wg_noalloc_max_flags() + 8 words (16 KiB + 32 B) held by every GPU that loads it.
+ *   - v == NULL takes the rule's program for the shape (wg_choose); dA, dBt, dC as wg_plan_create.
+ *   - WG_E_LIMIT when the program needs more hand-off words than wg_noalloc_max_flags().
+ *   - The first call on a device looks up the array's device address; make that call before
+ *     any stream capture begins.
+ *   - Every call on a device shares the array: the call clears the words it uses on `cuda_stream`
+ *     ahead of its kernel, so calls on one stream are safe back to back, but two calls that
+ *     overlap on the GPU (different streams, no dependency) race on it.
+ *   - No cudaMalloc / cudaFree / allocating library routine is called.
+ * wg_noalloc_status synchronises the device and reports the status words like wg_last_device_status. */
+int wg_launch_noalloc(int device, const wg_variant* v, int M, int N, int K, const void* dA, const void* dBt, void* dC,
+                      void* cuda_stream);
+int wg_noalloc_status(int device, unsigned out[4]);
+int wg_noalloc_max_flags(void);
+
 /* Number of compiled kernels and the name of each (for listing). */
 int wg_kernel_count(void);
 const char* wg_kernel_name(int kernel_id);

@@ -71,6 +71,9 @@ def lib():
         "wg_plan_read_stamps": ([vp, ctypes.POINTER(ctypes.c_ulonglong), ctypes.c_size_t], i),
         "wg_plan_debug_set_flag": ([vp, i, u], i),
         "wg_tile_origin": ([PL, i, ctypes.POINTER(i), ctypes.POINTER(i)], i),
+        "wg_launch_noalloc": ([i, PV, i, i, i, vp, vp, vp, vp], i),
+        "wg_noalloc_status": ([i, ctypes.POINTER(u * 4)], i),
+        "wg_noalloc_max_flags": ([], i),
         "wg_kernel_count": ([], i),
         "wg_kernel_name": ([i], ctypes.c_char_p),
         "wg_strerror": ([i], ctypes.c_char_p),

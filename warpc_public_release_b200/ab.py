@@ -1,0 +1,220 @@
+"""A/B GPU time per call: this library's kernel against cuBLASLt, in one process on one warm GPU.
+
+The method is the reference's (README.md:504-525; backend/node/ab.py:63-93, ktrace.cpp): each
+call runs alone (a synchronise after every launch), its GPU time is the kernel's start-to-end
+from CUPTI activity records, a side's figure is the median over its last N calls, the sides run
+interleaved ours, cuBLASLt, cuBLASLt, ours, twice, and the inputs are the index-hash integers in
+[-3, 3] (or uniform[-1, 1] with --inputs uniform) so both sides multiply the same values.
+cuBLASLt is timed on the fastest algorithm of its heuristic's list whose result is exact.
+Before each side's turn the GPU is kept busy for a few tens of milliseconds so the clocks are
+the loaded ones, not the idle ones.
+
+    python -m warpc_public_release_b200.ab [--inputs hash|uniform] [--json out.json] [M N K ...]
+"""
+import argparse
+import ctypes
+import json
+import os
+import sys
+
+from . import _lib, programs
+from .plan import Plan
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+SHAPES = [(1024, 1024, 1024), (1536, 1536, 1536), (2048, 2048, 2048), (3072, 1280, 2048), (4096, 4096, 1024),
+          (4096, 4096, 4096), (8192, 2048, 4096), (8192, 8192, 8192), (16384, 16384, 16384), (2048, 2048, 16384),
+          (1024, 1024, 65536)]
+# calls whose median is taken, by how long one call is (README.md:508-511)
+LAST = {(4096, 4096, 1024): 300, (4096, 4096, 4096): 200, (8192, 2048, 4096): 200, (2048, 2048, 16384): 200,
+        (1024, 1024, 65536): 200, (8192, 8192, 8192): 40, (16384, 16384, 16384): 12}
+# what the reference publishes for its own kernels and for cuBLASLt 13.8 on its B200 (README.md:81-91), us
+PUBLISHED = {(1024, 1024, 1024): (4.655, 5.41), (1536, 1536, 1536): (7.87, 7.84), (2048, 2048, 2048): (14.46, 13.79),
+             (3072, 1280, 2048): (14.08, 13.57), (4096, 4096, 1024): (26.11, 26.85), (4096, 4096, 4096): (75.875, 75.55),
+             (8192, 2048, 4096): (75.905, 75.87), (8192, 8192, 8192): (553.7, 557.6), (16384, 16384, 16384): (4186.1, 4159.7),
+             (2048, 2048, 16384): (74.015, 78.43), (1024, 1024, 65536): (77.075, 84.96)}
+
+
+class KernelTimer:
+    def __init__(self):
+        self.l = ctypes.CDLL(os.path.join(HERE, "libwarpc_b200_ktimer.so"))
+        self.l.wk_median.argtypes = [ctypes.c_char_p, ctypes.c_int] + [ctypes.POINTER(ctypes.c_double)] * 3
+        if self.l.wk_begin() != 0:
+            raise RuntimeError("CUPTI activity recording is not available")
+
+    def clear(self):
+        self.l.wk_flush()
+        self.l.wk_clear()
+
+    def median(self, substr, last):
+        self.l.wk_flush()
+        med, lo, hi = ctypes.c_double(), ctypes.c_double(), ctypes.c_double()
+        n = self.l.wk_median(substr.encode(), last, ctypes.byref(med), ctypes.byref(lo), ctypes.byref(hi))
+        return (med.value, n) if n else (float("nan"), 0)
+
+    def names(self):
+        self.l.wk_flush()
+        self.l.wk_get.argtypes = [ctypes.c_int, ctypes.c_char_p, ctypes.c_size_t, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double)]
+        out = {}
+        buf = ctypes.create_string_buffer(256)
+        for i in range(self.l.wk_count()):
+            self.l.wk_get(i, buf, 256, None, None)
+            out[buf.value.decode()] = out.get(buf.value.decode(), 0) + 1
+        return out
+
+    def close(self):
+        self.l.wk_end()
+
+
+class CublasLt:
+    def __init__(self, m, n, k, dA, dBt, dC, workspace=256 << 20):
+        self.l = ctypes.CDLL(os.path.join(HERE, "libwarpc_b200_cublaslt.so"))
+        self.l.wc_create.argtypes = [ctypes.c_int] * 3 + [ctypes.c_void_p] * 3 + [ctypes.c_size_t, ctypes.POINTER(ctypes.c_void_p),
+                                                                                 ctypes.POINTER(ctypes.c_int)]
+        self.l.wc_run.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
+        self.l.wc_destroy.argtypes = [ctypes.c_void_p]
+        self.h, n_algos = ctypes.c_void_p(), ctypes.c_int()
+        r = self.l.wc_create(m, n, k, dA, dBt, dC, workspace, ctypes.byref(self.h), ctypes.byref(n_algos))
+        if r != 0:
+            raise RuntimeError("cuBLASLt set-up failed: %d" % r)
+        self.n_algos = n_algos.value
+        self.version = self.l.wc_version()
+
+    def run(self, algo):
+        r = self.l.wc_run(self.h, algo, None)
+        if r != 0:
+            raise RuntimeError("cublasLtMatmul: %d" % r)
+
+    def close(self):
+        self.l.wc_destroy(self.h)
+
+
+def make_inputs(torch, kind, m, n, k):
+    """The reference's index-hash inputs (run_tma.py:58-62) or uniform[-1,1], built on the device."""
+    if kind == "hash":
+        def val(count, salt):
+            i = torch.arange(count, dtype=torch.int64, device="cuda")
+            return ((((i * 2654435761 + salt) >> 13) % 7) - 3).to(torch.float16)
+        return val(m * k, 1).reshape(m, k), val(n * k, 7).reshape(n, k)
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    a = (torch.rand((m, k), generator=gen, device="cuda") * 2 - 1).to(torch.float16)
+    bt = (torch.rand((n, k), generator=gen, device="cuda") * 2 - 1).to(torch.float16)
+    return a, bt
+
+
+def ab_shape(torch, timer, m, n, k, inputs="hash", rounds=2, variant=None, busy_ms=30.0):
+    a, bt = make_inputs(torch, inputs, m, n, k)
+    c_ours = torch.zeros((m, n), dtype=torch.float32, device="cuda")
+    c_lib = torch.zeros((m, n), dtype=torch.float32, device="cuda")
+    v = variant or programs.choose(m, n, k)
+    plan = Plan(v, m, n, k, a.data_ptr(), bt.data_ptr(), c_ours.data_ptr())
+    lt = CublasLt(m, n, k, a.data_ptr(), bt.data_ptr(), c_lib.data_ptr())
+    plan.launch()
+    plan.status()
+    exact = inputs == "hash"
+    tol = 0.0 if exact else 1e-3 * (k ** 0.5)
+    last = LAST.get((m, n, k), 400)
+    calls = last + max(5, last // 10)
+
+    def busy(run):
+        # keep the GPU loaded with the side's own kernel for about busy_ms before its isolated calls
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); run(); e1.record(); torch.cuda.synchronize()
+        one = max(e0.elapsed_time(e1), 1e-3)
+        for _ in range(int(min(max(busy_ms / one, 3), 3000))):
+            run()
+        torch.cuda.synchronize()
+
+    # the fastest correct cuBLASLt algorithm, by a quick event timing of each candidate
+    best, best_ms, correct = -1, None, 0
+    for algo in range(lt.n_algos):
+        c_lib.zero_()
+        try:
+            lt.run(algo)
+        except RuntimeError:
+            continue
+        torch.cuda.synchronize()
+        err = float((c_lib - c_ours).abs().max().item())
+        if err > tol:
+            continue
+        correct += 1
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(3):
+            lt.run(algo)
+        reps = 20 if m * n * k < 2 ** 36 else 5
+        e0.record()
+        for _ in range(reps):
+            lt.run(algo)
+        e1.record(); torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        if best_ms is None or ms < best_ms:
+            best, best_ms = algo, ms
+    if best < 0:
+        raise RuntimeError("no correct cuBLASLt algorithm for %dx%dx%d" % (m, n, k))
+
+    def isolated(run, tag):
+        busy(run)
+        timer.clear()
+        for _ in range(calls):
+            run()
+            torch.cuda.synchronize()
+        return timer.median(tag, last)
+
+    ours, lib, lib_kernels = [], [], None
+    for _ in range(rounds):
+        for side in ("ours", "lib", "lib", "ours"):
+            if side == "ours":
+                ours.append(isolated(plan.launch, "gemm_kernel")[0])
+            else:
+                # a cuBLASLt call may be more than one kernel: its GPU time is the sum of its kernels' medians
+                busy(lambda: lt.run(best))
+                timer.clear()
+                for _ in range(calls):
+                    lt.run(best)
+                    torch.cuda.synchronize()
+                names = [nm for nm in timer.names() if "gemm_kernel" not in nm]
+                lib_kernels = names
+                lib.append(sum(timer.median(nm, last)[0] for nm in names))
+    plan.status()
+    err = float((c_lib - c_ours).abs().max().item())
+    flops = 2.0 * m * n * k
+    mid = lambda xs: (min(xs) + max(xs)) / 2
+    row = {"shape": [m, n, k], "inputs": inputs, "program": "%dx%d d%d" % (v.tile_m, v.tile_n, v.depth), "calls_in_median": last,
+           "ours_us": [min(ours), max(ours)], "cublaslt_us": [min(lib), max(lib)], "cublaslt_algo": best,
+           "cublaslt_correct_algos": "%d of %d" % (correct, lt.n_algos), "cublaslt_version": lt.version,
+           "cublaslt_kernels": lib_kernels, "ours_tflops": flops / mid(ours) / 1e6, "cublaslt_tflops": flops / mid(lib) / 1e6,
+           "ours_vs_cublaslt_pct": 100.0 * (min(lib) / mid(ours) - 1.0), "max_abs_diff_vs_cublaslt": err,
+           "published_warpc_us": PUBLISHED.get((m, n, k), (None, None))[0], "published_cublas138_us": PUBLISHED.get((m, n, k), (None, None))[1]}
+    plan.close()
+    lt.close()
+    return row
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--inputs", default="hash", choices=["hash", "uniform"])
+    ap.add_argument("--json", default=None)
+    ap.add_argument("--rounds", type=int, default=2)
+    ap.add_argument("dims", nargs="*", type=int)
+    args = ap.parse_args(argv)
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("ab: needs a CUDA device")
+    shapes = [tuple(args.dims[i:i + 3]) for i in range(0, len(args.dims), 3)] or [s for s in SHAPES if s != (16384, 16384, 16384)]
+    timer = KernelTimer()
+    rows = []
+    print("%-18s %-12s %17s %17s %8s   %s" % ("M x N x K", "program", "ours us", "cuBLASLt us", "vs lib", "published warpc / cuBLAS 13.8 us"))
+    for (m, n, k) in shapes:
+        row = ab_shape(torch, timer, m, n, k, inputs=args.inputs, rounds=args.rounds)
+        rows.append(row)
+        print("%-18s %-12s %8.2f-%-8.2f %8.2f-%-8.2f %+7.1f%%   %s / %s" % (
+            "%dx%dx%d" % (m, n, k), row["program"], *row["ours_us"], *row["cublaslt_us"], row["ours_vs_cublaslt_pct"],
+            row["published_warpc_us"], row["published_cublas138_us"]), flush=True)
+        if args.json:
+            json.dump({"method": "CUPTI kernel start-to-end, each call alone, median of the last N, ours/lib/lib/ours x %d" % args.rounds,
+                       "rows": rows}, open(args.json, "w"), indent=1)
+    timer.close()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

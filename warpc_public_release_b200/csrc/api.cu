@@ -350,3 +350,113 @@ extern "C" int wg_plan_debug_set_flag(void* plan, int index, unsigned value) {
   WG_CUDA(cudaMemcpy(pl->d_flags + index, &value, sizeof value, cudaMemcpyHostToDevice));
   return WG_OK;
 }
+
+// ------------------------------------------------------------------ launch without allocating
+// Some callers must not allocate device memory at the point of the call: code running inside
+// another framework's memory pool or under a fixed memory budget, a real-time loop where
+// cudaMalloc's implicit synchronisation is not acceptable, a library initialised after the
+// application has handed all free memory to its own allocator.  For them the kernel's own
+// words -- the split-K / stream-K hand-off flags and the status words -- live in one
+// file-scope device array that every GPU loading this library holds until exit
+// (WG_NOALLOC_MAX_FLAGS + 8 words = 16 KiB + 32 B).  Tensor maps travel as kernel parameters,
+// so nothing else is needed.
+constexpr int kNoAllocMaxFlags = 4096;
+static __device__ __align__(256) uint32_t g_noalloc_scratch[kNoAllocMaxFlags + 8];
+
+namespace {
+constexpr int kMaxDevices = 64;
+uint32_t* g_noalloc_ptr[kMaxDevices];  // device address of g_noalloc_scratch per device, 0 until set up
+std::mutex g_noalloc_mutex;
+
+// Once per device, with that device current: the array's name is only a host-side stand-in,
+// the kernel needs the address the runtime reports for it.
+int noalloc_setup(int device, uint32_t** out) {
+  if (device < 0 || device >= kMaxDevices) return WG_E_ARG;
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (!g_noalloc_ptr[device]) {
+    WG_CUDA(cudaSetDevice(device));
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess) return int(e);
+    if (!p) return WG_E_NODRIVER;
+    g_noalloc_ptr[device] = static_cast<uint32_t*>(p);
+  }
+  *out = g_noalloc_ptr[device];
+  return WG_OK;
+}
+}  // namespace
+
+extern "C" int wg_noalloc_max_flags(void) { return kNoAllocMaxFlags; }
+
+extern "C" int wg_launch_noalloc(int device, const wg_variant* v, int M, int N, int K, const void* dA, const void* dBt, void* dC,
+                                 void* cuda_stream) {
+  if (!dA || !dBt || !dC) return WG_E_ARG;
+  if ((reinterpret_cast<uintptr_t>(dA) | reinterpret_cast<uintptr_t>(dBt) | reinterpret_cast<uintptr_t>(dC)) & 15u) return WG_E_ARG;
+  if (M <= 0 || N <= 0 || K <= 0 || K % 64 != 0 || N % 4 != 0) return WG_E_ARG;
+  wg_variant chosen;
+  if (!v) {
+    const int r = wg_choose(M, N, K, WG_SM_100A, &chosen);
+    if (r != WG_OK) return r;
+    v = &chosen;
+  }
+  wg_launch_info li;
+  int r = wg_realise(v, M, N, K, &li);
+  if (r != WG_OK) return r;
+  if (li.nflags > kNoAllocMaxFlags) return WG_E_LIMIT;  // the shape needs more hand-off words than the array holds
+  uint32_t* scratch = nullptr;
+  if ((r = noalloc_setup(device, &scratch)) != WG_OK) return r;
+  WG_CUDA(cudaSetDevice(device));
+  const wb_kernel_entry* k = wb_kernel_at(li.kernel_id);
+  CUtensorMap map_a, map_b, map_c;
+  std::memset(&map_c, 0, sizeof map_c);
+  if ((r = encode_2d(&map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, dA, M, K, li.a_box_rows, 64)) != WG_OK) return r;
+  if ((r = encode_2d(&map_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, dBt, N, K, li.bt_box_rows, 64)) != WG_OK) return r;
+  if (!li.direct && (r = encode_2d(&map_c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dC, M, N, li.c_box_rows, 32)) != WG_OK) return r;
+  KParams p;
+  std::memset(&p, 0, sizeof p);
+  p.M = M, p.N = N, p.K = K, p.kt = K / 64;
+  p.ntiles = ((M + li.tile_m - 1) / li.tile_m) * ((N + li.tile_n - 1) / li.tile_n);
+  p.cl_n = li.cl_n > 0 ? li.cl_n : 1, p.group = li.group > 0 ? li.group : 1, p.serp = li.serpentine;
+  p.depth = li.depth, p.nbuf = li.nbuf, p.sched = li.sched, p.ask_ahead = li.ask_ahead, p.split = li.split;
+  if (li.sched == SCHED_STREAMK) {
+    const int clusters = li.grid / li.cluster, units = (p.ntiles / li.cluster) * p.kt;
+    p.sk_clusters = clusters, p.sk_q = units / clusters, p.sk_r = units % clusters;
+  }
+  p.C = static_cast<float*>(dC);
+  p.status = scratch;      // 8 status words, then the flags
+  p.flags = scratch + 8;
+  p.timeout_ns = 2000ull * 1000ull * 1000ull;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  // the array keeps the last call's contents and the flags of one launch must all start equal:
+  // clear the words this launch uses (and the status) on the stream, ahead of the kernel
+  WG_CUDA(cudaMemsetAsync(scratch, 0, size_t(8 + (li.nflags > 0 ? li.nflags : 0)) * sizeof(uint32_t), stream));
+  WG_CUDA(cudaFuncSetAttribute(k->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, li.dynsmem));
+  cudaLaunchConfig_t cfg;
+  std::memset(&cfg, 0, sizeof cfg);
+  cfg.gridDim = dim3(unsigned(li.grid), 1, 1);
+  cfg.blockDim = dim3(unsigned(li.threads), 1, 1);
+  cfg.dynamicSmemBytes = size_t(li.dynsmem);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = unsigned(li.cluster);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  void* args[4] = {&map_a, &map_b, &map_c, &p};
+  return int(cudaLaunchKernelExC(&cfg, k->fn, args));
+}
+
+extern "C" int wg_noalloc_status(int device, unsigned out[4]) {
+  if (!out) return WG_E_ARG;
+  uint32_t* scratch = nullptr;
+  const int r = noalloc_setup(device, &scratch);
+  if (r != WG_OK) return r;
+  uint32_t st[4];
+  WG_CUDA(cudaSetDevice(device));
+  WG_CUDA(cudaDeviceSynchronize());
+  WG_CUDA(cudaMemcpy(st, scratch, sizeof st, cudaMemcpyDeviceToHost));
+  for (int i = 0; i < 4; ++i) out[i] = st[i];
+  return st[0] == 0 ? WG_OK : WG_E_DEVICE_WAIT;
+}

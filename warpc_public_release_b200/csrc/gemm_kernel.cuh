@@ -59,7 +59,7 @@ struct KParams {
   unsigned long long* stamps;   // timing builds: 16 events x 4 tiles of %globaltimer per CTA, or null
 };
 
-template <int CG_, int TM_, int TN_, bool DIRECT_, int EPI_ROWS_ = 16>
+template <int CG_, int TM_, int TN_, bool DIRECT_, int EPI_ROWS_ = 16, int EPI_COPIES_ = 2>
 struct Cfg {
   static constexpr int CG = CG_, TM = TM_, TN = TN_, TK = 64;
   static constexpr bool DIRECT = DIRECT_;
@@ -77,7 +77,8 @@ struct Cfg {
   static constexpr uint32_t TX_BYTES = CG * STAGE_BYTES;  // what lands on the leader's barrier per stage
   static constexpr int EPI_ROWS = DIRECT ? 32 : EPI_ROWS_;  // C rows per epilogue block
   static constexpr int EPI_COPY_BYTES = EPI_ROWS * 128;
-  static constexpr int STAGING_BYTES = DIRECT ? 0 : 4 * 2 * EPI_COPY_BYTES;
+  static constexpr int EPI_COPIES = EPI_COPIES_;  // staging copies a warp cycles through
+  static constexpr int STAGING_BYTES = DIRECT ? 0 : 4 * EPI_COPIES * EPI_COPY_BYTES;
   static constexpr int CHUNKS = SPAN / EPI_ROWS;  // blocks per atom per warp
   static constexpr int NBLK = REPS * CHUNKS;
   static constexpr int MAX_DEPTH = 16;
@@ -290,12 +291,15 @@ WB_DEV void epi_coords(int row, int col, int q, int i, int& y, int& x) {
 // leader's barrier as soon as the last block is in registers.
 template <class C>
 WB_DEV void epi_staged_tile(const CUtensorMap* map_c, uint32_t tbase, uint32_t my_staging, int row, int col, int q, uint32_t lane,
-                            bool add, uint32_t acc_empty_addr) {
+                            bool add, uint32_t acc_empty_addr, unsigned long long* prof = nullptr) {
   uint32_t v[2][C::EPI_ROWS];
+  long long t_ld = 0, t_copy = 0, t_sts = 0, t_tma = 0, t0 = 0;
   epi_load<C>(tbase, 0, v[0]);
 #pragma unroll
   for (int i = 0; i < C::NBLK; ++i) {
+    if (prof) t0 = clock64();
     tmem_wait_ld();
+    if (prof) t_ld += clock64() - t0;
     if (i + 1 < C::NBLK) {
       epi_load<C>(tbase, i + 1, v[(i + 1) & 1]);
     } else {
@@ -308,20 +312,25 @@ WB_DEV void epi_staged_tile(const CUtensorMap* map_c, uint32_t tbase, uint32_t m
     }
     int y, x;
     epi_coords<C>(row, col, q, i, y, x);
-    const uint32_t copy = my_staging + uint32_t(i & 1) * C::EPI_COPY_BYTES;
-    if (lane == 0) bulk_wait_read<1>();  // the store that last read this copy is done with it
+    const uint32_t copy = my_staging + uint32_t(i % C::EPI_COPIES) * C::EPI_COPY_BYTES;
+    if (prof) t0 = clock64();
+    if (lane == 0) bulk_wait_read<C::EPI_COPIES - 1>();  // the store that last read this copy is done with it
     __syncwarp();
+    if (prof) t_copy += clock64() - t0, t0 = clock64();
 #pragma unroll
     for (int j = 0; j < C::EPI_ROWS; ++j)  // 128-byte swizzle: 16-byte chunk index xor row-in-8
       st_shared_u32(copy + uint32_t(j) * 128u + ((lane * 4u) ^ (uint32_t(j & 7) << 4)), v[i & 1][j]);
     fence_proxy_async_smem();
     __syncwarp();
+    if (prof) t_sts += clock64() - t0, t0 = clock64();
     if (lane == 0) {
       if (add) tma_reduce_add_2d(map_c, x, y, copy);
       else tma_store_2d(map_c, x, y, copy);
       bulk_commit();
     }
+    if (prof) t_tma += clock64() - t0;
   }
+  if (prof && lane == 0) prof[0] = t_ld, prof[4] = t_copy, prof[8] = t_sts, prof[12] = t_tma;
 }
 
 // Straight from the registers: register j of a block is row y + j, the warp's lanes are 32
@@ -556,7 +565,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     uint32_t acc_phase = 0;
     bool ok = true;
     const uint32_t acc_empty_leader = (CG == 2) ? mapa(acc_empty_bar(0), 0) : acc_empty_bar(0);
-    const uint32_t my_staging = staging + uint32_t(q) * 2u * C::EPI_COPY_BYTES;
+    const uint32_t my_staging = staging + uint32_t(q) * uint32_t(C::EPI_COPIES) * C::EPI_COPY_BYTES;
     // K split between CTAs (split-K over the grid, stream-K): hand-off words count launches,
     // never reset: every CTA's own word holds how many launches have gone by, so one past it
     // is the value all flags of this launch reach (gemm_swapped.ml:608-626)
@@ -583,7 +592,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         if (!wait_bar(p, abort_addr, acc_full_bar(acc), acc_phase, ST_WAIT_ACC_FULL, uint32_t(acc))) break;
         tc_fence_after();
         if (first_warp && lane == 0) stamp(p, EV_ACC_READY, nth);
-        epi_staged_tile<C>(&map_c, tbase, my_staging, row, col, q, lane, false, acc_empty_addr);
+        // timing runs: the first warp's cycles in each part of the tile's store, events 11-14
+        unsigned long long* prof = (p.stamps != nullptr && first_warp && nth < 4) ? p.stamps + (size_t(blockIdx.x) * 16 + 11) * 4 + nth : nullptr;
+        epi_staged_tile<C>(&map_c, tbase, my_staging, row, col, q, lane, false, acc_empty_addr, prof);
       } else if (p.sched == SCHED_SPLITK) {
         // ---- split-K over the grid, adding in the L2 (gemm_swapped.ml:660-710).  The S runs
         // of a tile first zero disjoint shares of it (while their k loops run), raise their

@@ -107,3 +107,29 @@ class HostPlan(_Base):
 
     def buffer(self, which):
         return _lib.lib().wg_host_plan_buffer(self._h, which)
+
+
+def launch_noalloc(variant, m, n, k, dA, dBt, dC, device=0, stream=None):
+    """One launch that allocates no device memory (wg_launch_noalloc): for callers that may
+    not call cudaMalloc where they call the GEMM -- code inside another framework's memory
+    pool or a fixed memory budget, latency-critical loops.  The kernel's flags and status words
+    sit in an array built into the library (up to `noalloc_max_flags()` hand-off words); calls
+    on one device share it, so calls that overlap on the GPU race.  `variant` None = the rule's
+    choice.  Make the first call on a device before any stream capture."""
+    vref = ctypes.byref(variant) if variant is not None else None
+    check(_lib.lib().wg_launch_noalloc(device, vref, m, n, k, ctypes.c_void_p(dA), ctypes.c_void_p(dBt), ctypes.c_void_p(dC),
+                                       ctypes.c_void_p(stream or 0)), "wg_launch_noalloc")
+
+
+def noalloc_status(device=0):
+    """Synchronise and raise DeviceWaitError if a no-allocation launch gave up."""
+    st = (ctypes.c_uint * 4)()
+    r = _lib.lib().wg_noalloc_status(device, ctypes.byref(st))
+    if r == _lib.WG_E_DEVICE_WAIT:
+        raise DeviceWaitError(list(st))
+    check(r, "wg_noalloc_status")
+    return tuple(st)
+
+
+def noalloc_max_flags():
+    return _lib.lib().wg_noalloc_max_flags()
