@@ -110,8 +110,8 @@ void* wg_host_plan_buffer(void* plan, int which);
 int wg_time_launches(void* plan, int warmup, int repeat, float* ms_mean);
 
 /* Timing builds (the reference's: backend/stamp.ml:9-16, decoded in run_tma.py:176-192): turn
- * per-phase stamps on or off for the launches that follow, and read them back: 16 events x
- * 4 tiles of the GPU nanosecond timer per CTA, grid*64 words; returns the words written. */
+ * per-phase stamps on or off for the launches that follow, and read them back: 32 events x
+ * 4 tiles per CTA (GPU nanosecond timer; events 11-14 and 16-20 are cycle sums), grid*128 words; returns the words written. */
 int wg_plan_enable_stamps(void* plan, int on);
 int wg_plan_read_stamps(void* plan, unsigned long long* out, size_t cap_words);
 

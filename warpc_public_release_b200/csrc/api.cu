@@ -310,12 +310,12 @@ extern "C" int wg_time_launches(void* plan, int warmup, int repeat, float* ms_me
   return r;
 }
 
-// Timing runs: phase stamps (16 events x 4 tiles of the GPU nanosecond timer per CTA) of the
-// launches that follow; wg_plan_read_stamps synchronises and copies grid*64 words out.
+// Timing runs: phase stamps (32 events x 4 tiles per CTA: GPU nanosecond timer, plus cycle sums) of the
+// launches that follow; wg_plan_read_stamps synchronises and copies grid*128 words out.
 extern "C" int wg_plan_enable_stamps(void* plan, int on) {
   Plan* pl = static_cast<Plan*>(plan);
   if (!pl) return WG_E_ARG;
-  const size_t bytes = size_t(pl->li.grid) * 64 * sizeof(unsigned long long);
+  const size_t bytes = size_t(pl->li.grid) * 128 * sizeof(unsigned long long);
   if (on && !pl->d_stamps) {
     WG_CUDA(cudaMalloc(&pl->d_stamps, bytes));
   }
@@ -327,7 +327,7 @@ extern "C" int wg_plan_enable_stamps(void* plan, int on) {
 extern "C" int wg_plan_read_stamps(void* plan, unsigned long long* out, size_t cap_words) {
   Plan* pl = static_cast<Plan*>(plan);
   if (!pl || !out || !pl->d_stamps) return WG_E_ARG;
-  const size_t words = size_t(pl->li.grid) * 64;
+  const size_t words = size_t(pl->li.grid) * 128;
   if (cap_words < words) return WG_E_ARG;
   WG_CUDA(cudaDeviceSynchronize());
   WG_CUDA(cudaMemcpy(out, pl->d_stamps, words * sizeof(unsigned long long), cudaMemcpyDeviceToHost));

@@ -56,7 +56,7 @@ struct KParams {
   uint32_t* flags;              // split-K / stream-K hand-off words
   uint32_t* status;             // 8 words: [0] code, [1] site detail, [2] CTA, [3] parity/stage
   unsigned long long timeout_ns;
-  unsigned long long* stamps;   // timing builds: 16 events x 4 tiles of %globaltimer per CTA, or null
+  unsigned long long* stamps;   // timing builds: 32 events x 4 tiles per CTA, or null
 };
 
 template <int CG_, int TM_, int TN_, bool DIRECT_, int EPI_ROWS_ = 16, int EPI_COPIES_ = 2>
@@ -134,46 +134,52 @@ WB_DEV void record_failure(const KParams& p, uint32_t code, uint32_t detail, uin
 // the CTA's `slot`-th tile, on the GPU-wide nanosecond timer.
 enum : int { EV_ENTRY = 0, EV_SETUP = 1, EV_LOAD_FIRST = 2, EV_LOAD_LAST = 3, EV_MMA_FIRST = 4, EV_MMA_LAST = 5,
              EV_ACC_READY = 6, EV_STORED = 7, EV_TEARDOWN = 8, EV_EXIT = 9, EV_ACC_FREE = 10 };
+// cycle counters of a timing run: events 16.. hold sums of clock64() intervals, not times
+enum : int { EV_CYC_PROD_WAIT = 16, EV_CYC_PROD_ISSUE = 17, EV_CYC_MMA_WAIT = 18, EV_CYC_MMA_ISSUE = 19, EV_CYC_MMA_ACC_WAIT = 20 };
+WB_DEV void stamp_value(const KParams& p, int ev, int slot, long long value) {
+  if (p.stamps != nullptr && slot < 4) p.stamps[(size_t(blockIdx.x) * 32 + ev) * 4 + slot] = (unsigned long long)value;
+}
 WB_DEV void stamp(const KParams& p, int ev, int slot) {
-  if (p.stamps != nullptr && slot < 4) p.stamps[(size_t(blockIdx.x) * 16 + ev) * 4 + slot] = globaltimer();
+  if (p.stamps != nullptr && slot < 4) p.stamps[(size_t(blockIdx.x) * 32 + ev) * 4 + slot] = globaltimer();
 }
 
-// Bounded wait on an mbarrier phase. Returns false when the kernel is giving up.
+// Bounded wait on an mbarrier phase by a whole, converged warp.  Returns false when the kernel
+// is giving up.  The common case is one asm-internal spin; its outcome is made warp-uniform with
+// a vote so that every branch the roles take on it is a uniform branch.  Only when 4096 polls
+// (each already sleeping in hardware) have failed does the warp look at the abort words and the
+// GPU-wide timer, which is slow to read.
+// CLUSTER: acquire at cluster scope (data another CTA stored before arriving).
+template <bool CLUSTER = false>
 WB_DEV bool wait_bar(const KParams& p, uint32_t abort_addr, uint32_t bar, uint32_t parity, uint32_t code, uint32_t detail) {
-  if (mbar_try_wait(bar, parity)) return true;
+  if (__all_sync(0xffffffffu, mbar_spin_wait<CLUSTER>(bar, parity, 1u << 12))) return true;
   const uint64_t t0 = globaltimer();
-  uint32_t polls = 0;
   for (;;) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((++polls & 15u) == 0u) {
-      if (ld_shared_u32(abort_addr) != 0u) return false;
-      if (ld_relaxed_gpu(p.status) != 0u) {
-        st_shared_u32(abort_addr, 1u);
-        return false;
-      }
-      if (globaltimer() - t0 > p.timeout_ns) {
-        record_failure(p, code, detail, parity);
-        st_shared_u32(abort_addr, 1u);
-        return false;
-      }
+    if (__all_sync(0xffffffffu, mbar_spin_wait<CLUSTER>(bar, parity, 64))) return true;
+    uint32_t bad = ld_shared_u32(abort_addr) | ld_relaxed_gpu(p.status);
+    const bool late = globaltimer() - t0 > p.timeout_ns;
+    if (late && bad == 0u) record_failure(p, code, detail, parity);
+    if (__any_sync(0xffffffffu, bad != 0u || late)) {
+      st_shared_u32(abort_addr, 1u);
+      return false;
     }
   }
 }
 
 // Bounded wait until *flag == target (split-K / stream-K hand-off between CTAs).
 WB_DEV bool wait_flag(const KParams& p, uint32_t abort_addr, const uint32_t* flag, uint32_t target, uint32_t detail) {
-  if (ld_relaxed_gpu(flag) == target) return true;
-  const uint64_t t0 = globaltimer();
   uint32_t polls = 0;
+  uint64_t t0 = 0;
   for (;;) {
     if (ld_relaxed_gpu(flag) == target) return true;
-    if ((++polls & 63u) == 0u) {
+    if ((++polls & 255u) == 0u) {
       if (ld_shared_u32(abort_addr) != 0u) return false;
       if (ld_relaxed_gpu(p.status) != 0u) {
         st_shared_u32(abort_addr, 1u);
         return false;
       }
-      if (globaltimer() - t0 > p.timeout_ns) {
+      const uint64_t now = globaltimer();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > p.timeout_ns) {
         record_failure(p, ST_WAIT_FLAG, detail, target);
         st_shared_u32(abort_addr, 1u);
         return false;
@@ -237,10 +243,9 @@ struct Walker {
         return tile < p.ntiles;
       }
       if (sched == SCHED_CLC) {
-        if (!wait_bar(p, abort_addr, sched_full, sched_parity, ST_WAIT_SCHED, 0)) return false;
+        if (!wait_bar<true>(p, abort_addr, sched_full, sched_parity, ST_WAIT_SCHED, 0)) return false;
         sched_parity ^= 1u;
-        const uint32_t valid = ld_shared_u32(sched_slot), first = ld_shared_u32(sched_slot + 4);
-        __syncwarp();
+        const uint32_t valid = warp_uniform(ld_shared_u32(sched_slot)), first = warp_uniform(ld_shared_u32(sched_slot + 4));
         if (lane == 0) mbar_arrive_cluster(sched_empty_first);
         if (!valid) return false;
         tile = int(first + rank);
@@ -305,16 +310,14 @@ WB_DEV void epi_staged_tile(const CUtensorMap* map_c, uint32_t tbase, uint32_t m
     } else {
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) {
-        if constexpr (C::CG == 2) mbar_arrive_cluster(acc_empty_addr);
-        else mbar_arrive(acc_empty_addr);
-      }
+      if constexpr (C::CG == 2) mbar_arrive_cluster_if(lane == 0 ? 1u : 0u, acc_empty_addr);
+      else mbar_arrive_if(lane == 0 ? 1u : 0u, acc_empty_addr);
     }
     int y, x;
     epi_coords<C>(row, col, q, i, y, x);
     const uint32_t copy = my_staging + uint32_t(i % C::EPI_COPIES) * C::EPI_COPY_BYTES;
     if (prof) t0 = clock64();
-    if (lane == 0) bulk_wait_read<C::EPI_COPIES - 1>();  // the store that last read this copy is done with it
+    bulk_wait_read<C::EPI_COPIES - 1>();  // the store that last read this copy is done with it (only the issuing lane has groups)
     __syncwarp();
     if (prof) t_copy += clock64() - t0, t0 = clock64();
 #pragma unroll
@@ -323,11 +326,7 @@ WB_DEV void epi_staged_tile(const CUtensorMap* map_c, uint32_t tbase, uint32_t m
     fence_proxy_async_smem();
     __syncwarp();
     if (prof) t_sts += clock64() - t0, t0 = clock64();
-    if (lane == 0) {
-      if (add) tma_reduce_add_2d(map_c, x, y, copy);
-      else tma_store_2d(map_c, x, y, copy);
-      bulk_commit();
-    }
+    tma_store_commit_if(lane == 0 ? 1u : 0u, add ? 1u : 0u, map_c, x, y, copy);
     if (prof) t_tma += clock64() - t0;
   }
   if (prof && lane == 0) prof[0] = t_ld, prof[4] = t_copy, prof[8] = t_sts, prof[12] = t_tma;
@@ -347,10 +346,8 @@ WB_DEV void epi_direct_tile(const KParams& p, uint32_t tbase, int row, int col, 
     } else {
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) {
-        if constexpr (C::CG == 2) mbar_arrive_cluster(acc_empty_addr);
-        else mbar_arrive(acc_empty_addr);
-      }
+      if constexpr (C::CG == 2) mbar_arrive_cluster_if(lane == 0 ? 1u : 0u, acc_empty_addr);
+      else mbar_arrive_if(lane == 0 ? 1u : 0u, acc_empty_addr);
     }
     int y, x;
     epi_coords<C>(row, col, q, i, y, x);
@@ -375,9 +372,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   auto ctrl_at = [&](size_t off) { return ctrl + uint32_t(off); };
   const uint32_t abort_addr = ctrl_at(offsetof(Ctrl, abort));
 
-  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t rank = (CG == 2) ? cluster_ctarank() : 0u;
+  // warp index, cluster rank and (below) the tensor-memory base are the same in every lane: a
+  // shuffle from lane 0 lets the compiler see that, so what the single-lane issue paths compute
+  // from them can live in uniform registers
+  const uint32_t warp = warp_uniform(threadIdx.x >> 5), lane = threadIdx.x & 31;
+  const uint32_t rank = (CG == 2) ? warp_uniform(cluster_ctarank()) : 0u;
   const bool leader = (rank == 0);
+  const uint32_t issuer = (lane == 0) ? 1u : 0u;  // the lane that issues its warp's single-lane instructions
   const int depth = p.depth, nbuf = p.nbuf;
   if (threadIdx.x == 0) stamp(p, EV_ENTRY, 0);
 
@@ -419,7 +420,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     __syncthreads();
   }
   tc_fence_after();
-  const uint32_t tmem_base = ld_shared_u32(ctrl_at(offsetof(Ctrl, tmem_base)));
+  const uint32_t tmem_base = warp_uniform(ld_shared_u32(ctrl_at(offsetof(Ctrl, tmem_base))));
   if (threadIdx.x == 0) stamp(p, EV_SETUP, 0);
 
   // ---------------------------------------------------------------- roles
@@ -430,28 +431,36 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     int stage = 0, nth = 0;
     uint32_t phase = 0;
     bool ok = true;
+    const bool prof = p.stamps != nullptr;
+    // what a stage's loads need, kept as running values so the issuing lane's chain is short
+    const uint32_t full_leader0 = (CG == 2) ? mapa(full_bar(0), 0) : full_bar(0);
     while (ok && walk.next(w)) {
       int row, col;
       tile_origin<C>(p, w.tile, row, col);
       // a pair's CTAs sit side by side: same rows, so they split the A tile between them
       const int a_row = row + int(rank) * C::A_ROWS;
-      for (int kk = w.kb; kk < w.ke; ++kk) {
+      long long cyc_wait = 0, cyc_issue = 0, c0 = 0;
+      int x = w.kb * C::TK;
+      for (int kk = w.kb; kk < w.ke; ++kk, x += C::TK) {
+        if (prof) c0 = clock64();
         if (!wait_bar(p, abort_addr, empty_bar(stage), phase ^ 1u, ST_WAIT_EMPTY, uint32_t(stage))) {
           ok = false;
           break;
         }
-        if (lane == 0) {
-          const uint32_t bar = (CG == 2) ? mapa(full_bar(stage), 0) : full_bar(stage);
-          if (leader) mbar_arrive_expect_tx(full_bar(stage), C::TX_BYTES);
-          const uint32_t sa = ring + uint32_t(stage) * C::STAGE_BYTES, sb = sa + C::A_BYTES;
-          tma_load_2d<CG>(sa, &map_a, kk * C::TK, a_row, bar);
-          tma_load_2d<CG>(sb, &map_b, kk * C::TK, col, bar);
-          if (kk == w.kb) stamp(p, EV_LOAD_FIRST, nth);
+        if (prof) cyc_wait += clock64() - c0, c0 = clock64();
+        const uint32_t sa = ring + uint32_t(stage) * C::STAGE_BYTES, sb = sa + C::A_BYTES;
+        const uint32_t bar = full_leader0 + 8u * uint32_t(stage);
+        mbar_arrive_expect_tx_if(issuer & uint32_t(leader), full_bar(stage), C::TX_BYTES);
+        tma_load_2d_if<CG>(issuer, sa, &map_a, x, a_row, bar);
+        tma_load_2d_if<CG>(issuer, sb, &map_b, x, col, bar);
+        if (prof) {
+          if (kk == w.kb && lane == 0) stamp(p, EV_LOAD_FIRST, nth);
+          cyc_issue += clock64() - c0;
         }
-        __syncwarp();
         if (++stage == depth) stage = 0, phase ^= 1u;
       }
-      if (lane == 0) stamp(p, EV_LOAD_LAST, nth);
+      if (prof && lane == 0)
+        stamp(p, EV_LOAD_LAST, nth), stamp_value(p, EV_CYC_PROD_WAIT, nth, cyc_wait), stamp_value(p, EV_CYC_PROD_ISSUE, nth, cyc_issue);
       ++nth;
     }
     // every stage this CTA filled has been released before it leaves
@@ -467,52 +476,63 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       int stage = 0, acc = 0, nth = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
-      const uint16_t mask = (CG == 2) ? 0x3 : 0x1;
+      const bool prof = p.stamps != nullptr;
+      constexpr uint16_t mask = (CG == 2) ? 0x3 : 0x1;
+      // shared-memory descriptors: the high word is fixed (SBO 1024 B, version 1, 128-byte swizzle);
+      // the low word is (address >> 4) | LBO field, so a stage, an atom or a 16-element k-step on
+      // is a plain add to it
+      constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
+      constexpr uint32_t STAGE16 = C::STAGE_BYTES >> 4, ATOM16 = uint32_t((C::MMA_M / CG) * 128) >> 4;
+      const uint32_t a_lo0 = ((ring & 0x3FFFFu) >> 4) | (1u << 16);  // the stage's A tile (the MMA's B operand)
+      const uint32_t b_lo0 = a_lo0 + (C::A_BYTES >> 4);              // the stage's B^T tile (the MMA's A operand)
+      uint32_t stage16 = 0;
       while (ok && walk.next(w)) {
         if (!wait_bar(p, abort_addr, acc_empty_bar(acc), acc_phase ^ 1u, ST_WAIT_ACC_EMPTY, uint32_t(acc))) {
           ok = false;
           break;
         }
         tc_fence_after();
-        if (lane == 0) stamp(p, EV_ACC_FREE, nth);
+        if (prof && lane == 0) stamp(p, EV_ACC_FREE, nth);
         const uint32_t d = tmem_base + uint32_t(acc * C::NCOLS);
         uint32_t accumulate = 0;
         bool landed = false;
+        long long cyc_wait = 0, cyc_issue = 0, c0 = 0;
         for (int kk = w.kb; kk < w.ke; ++kk) {
+          if (prof) c0 = clock64();
           if (!landed && !wait_bar(p, abort_addr, full_bar(stage), phase, ST_WAIT_FULL, uint32_t(stage))) {
             ok = false;
             break;
           }
           tc_fence_after();
-          if (kk == w.kb && lane == 0) stamp(p, EV_MMA_FIRST, nth);
-          const uint32_t sa = ring + uint32_t(stage) * C::STAGE_BYTES, sb = sa + C::A_BYTES;
-          if (lane == 0) {
+          if (prof) {
+            cyc_wait += clock64() - c0, c0 = clock64();
+            if (kk == w.kb && lane == 0) stamp(p, EV_MMA_FIRST, nth);
+          }
+          const uint32_t a_lo = a_lo0 + stage16, b_lo = b_lo0 + stage16;
 #pragma unroll
-            for (int r = 0; r < C::REPS; ++r) {
+          for (int r = 0; r < C::REPS; ++r) {
 #pragma unroll
-              for (int j = 0; j < C::TK / 16; ++j) {
-                // MMA "A" = B^T rows of atom r; MMA "B" = the tile of A; 16 K-elements = 32 bytes on
-                umma_f16<CG>(d + uint32_t(r * C::SPAN), smem_desc(sb + uint32_t(r * (C::MMA_M / CG) * 128 + j * 32)),
-                             smem_desc(sa + uint32_t(j * 32)), C::IDESC, (j == 0) ? accumulate : 1u);
-              }
+            for (int j = 0; j < C::TK / 16; ++j) {
+              // MMA "A" = B^T rows of atom r; MMA "B" = the tile of A; 16 K-elements = 32 bytes on
+              const uint64_t adesc = (uint64_t(DESC_HI) << 32) | uint64_t(b_lo + uint32_t(r) * ATOM16 + uint32_t(j) * 2u);
+              const uint64_t bdesc = (uint64_t(DESC_HI) << 32) | uint64_t(a_lo + uint32_t(j) * 2u);
+              umma_f16_if<CG>(issuer, d + uint32_t(r * C::SPAN), adesc, bdesc, C::IDESC, (j == 0) ? accumulate : 1u);
             }
           }
           accumulate = 1;
           int nstage = stage + 1;
-          uint32_t nphase = phase;
-          if (nstage == depth) nstage = 0, nphase ^= 1u;
+          uint32_t nphase = phase, nstage16 = stage16 + STAGE16;
+          if (nstage == depth) nstage = 0, nphase ^= 1u, nstage16 = 0;
           // asking a stage ahead: has the next stage landed already?
-          landed = (p.ask_ahead && kk + 1 < w.ke) ? (mbar_test_wait(full_bar(nstage), nphase) != 0u) : false;
-          if (lane == 0) umma_commit<CG>(empty_bar(stage), mask);  // the stage is free once these MMAs have read it
-          __syncwarp();
-          stage = nstage, phase = nphase;
+          landed = (p.ask_ahead && kk + 1 < w.ke) ? (__all_sync(0xffffffffu, mbar_test_wait(full_bar(nstage), nphase)) != 0) : false;
+          umma_commit_if<CG>(issuer, empty_bar(stage), mask);  // the stage is free once these MMAs have read it
+          if (prof) cyc_issue += clock64() - c0;
+          stage = nstage, phase = nphase, stage16 = nstage16;
         }
         if (!ok) break;
-        if (lane == 0) {
-          umma_commit<CG>(acc_full_bar(acc), mask);  // the accumulator is complete in both CTAs
-          stamp(p, EV_MMA_LAST, nth);
-        }
-        __syncwarp();
+        umma_commit_if<CG>(issuer, acc_full_bar(acc), mask);  // the accumulator is complete in both CTAs
+        if (prof && lane == 0)
+          stamp(p, EV_MMA_LAST, nth), stamp_value(p, EV_CYC_MMA_WAIT, nth, cyc_wait), stamp_value(p, EV_CYC_MMA_ISSUE, nth, cyc_issue);
         if (++acc == nbuf) acc = 0, acc_phase ^= 1u;
         ++nth;
       }
@@ -593,7 +613,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         tc_fence_after();
         if (first_warp && lane == 0) stamp(p, EV_ACC_READY, nth);
         // timing runs: the first warp's cycles in each part of the tile's store, events 11-14
-        unsigned long long* prof = (p.stamps != nullptr && first_warp && nth < 4) ? p.stamps + (size_t(blockIdx.x) * 16 + 11) * 4 + nth : nullptr;
+        unsigned long long* prof = (p.stamps != nullptr && first_warp && nth < 4) ? p.stamps + (size_t(blockIdx.x) * 32 + 11) * 4 + nth : nullptr;
         epi_staged_tile<C>(&map_c, tbase, my_staging, row, col, q, lane, false, acc_empty_addr, prof);
       } else if (p.sched == SCHED_SPLITK) {
         // ---- split-K over the grid, adding in the L2 (gemm_swapped.ml:660-710).  The S runs

@@ -51,7 +51,22 @@ WB_DEV void mbar_arrive(uint32_t bar) {
 WB_DEV void mbar_arrive_cluster(uint32_t bar) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// CTA-scope acquire (the default): enough for data landed by TMA / released by tcgen05.commit,
+// and cheap -- these waits sit on the ring's critical path.
 WB_DEV uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+// Cluster-scope acquire: for words another CTA of the cluster wrote with ordinary stores
+// before its remote arrive (the scheduler's forwarded answer).
+WB_DEV uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
@@ -66,13 +81,54 @@ WB_DEV uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
       : "memory");
   return ok;
 }
+
+// Spin on a barrier phase inside one asm block (no compiler-visible branch on a per-thread
+// value, so the code around it stays provably warp-uniform): up to `limit` try_waits, each of
+// which already sleeps in hardware.  Returns 1 when the phase completed.
+template <bool CLUSTER>
+WB_DEV uint32_t mbar_spin_wait(uint32_t bar, uint32_t parity, uint32_t limit) {
+  uint32_t ok;
+  if constexpr (CLUSTER) {
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t.reg .u32 n;\n\tmov.u32 n, 0;\n"
+        "WB_SPIN:\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "@p bra WB_DONE;\n\t"
+        "add.u32 n, n, 1;\n\t"
+        "setp.lt.u32 q, n, %3;\n\t"
+        "@q bra WB_SPIN;\n"
+        "WB_DONE:\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(limit)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t.reg .u32 n;\n\tmov.u32 n, 0;\n"
+        "WB_SPIN:\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "@p bra WB_DONE;\n\t"
+        "add.u32 n, n, 1;\n\t"
+        "setp.lt.u32 q, n, %3;\n\t"
+        "@q bra WB_SPIN;\n"
+        "WB_DONE:\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(limit)
+        : "memory");
+  }
+  return ok;
+}
+
+// A value every lane of a converged warp holds alike, in a form the compiler can see is uniform.
+WB_DEV uint32_t warp_uniform(uint32_t v) { return __shfl_sync(0xffffffffu, v, 0); }
 
 // ---------------------------------------------------------------- fences
 WB_DEV void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -240,6 +296,90 @@ WB_DEV void tmem_ld(uint32_t taddr, uint32_t* v) {
   if constexpr (N == 8) tmem_ld_x8(taddr, v);
   if constexpr (N == 16) tmem_ld_x16(taddr, v);
   if constexpr (N == 32) tmem_ld_x32(taddr, v);
+}
+
+// ---------------------------------------------------------------- predicated single-lane issue
+// The instructions one lane issues for its warp (TMA copies, MMAs, commits, arrives) are
+// predicated INSIDE the asm block on `issuer` (non-zero in the issuing lane) rather than wrapped
+// in a C++ `if`: the warp then never diverges around them, and the operands -- the same in every
+// lane -- can be computed on the uniform datapath instead of being moved there per instruction.
+WB_DEV void mbar_arrive_expect_tx_if(uint32_t issuer, uint32_t bar, uint32_t tx) {
+  asm volatile("{\n\t.reg .pred e;\n\tsetp.ne.u32 e, %0, 0;\n\t@e mbarrier.arrive.expect_tx.shared::cta.b64 _, [%1], %2;\n\t}" ::"r"(issuer),
+               "r"(bar), "r"(tx)
+               : "memory");
+}
+WB_DEV void mbar_arrive_if(uint32_t issuer, uint32_t bar) {
+  asm volatile("{\n\t.reg .pred e;\n\tsetp.ne.u32 e, %0, 0;\n\t@e mbarrier.arrive.shared::cta.b64 _, [%1];\n\t}" ::"r"(issuer), "r"(bar) : "memory");
+}
+WB_DEV void mbar_arrive_cluster_if(uint32_t issuer, uint32_t bar) {
+  asm volatile("{\n\t.reg .pred e;\n\tsetp.ne.u32 e, %0, 0;\n\t@e mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%1];\n\t}" ::"r"(issuer),
+               "r"(bar)
+               : "memory");
+}
+template <int CG>
+WB_DEV void tma_load_2d_if(uint32_t issuer, uint32_t dst, const void* map, int x, int y, uint32_t bar) {
+  if constexpr (CG == 2) {
+    asm volatile(
+        "{\n\t.reg .pred e;\n\tsetp.ne.u32 e, %0, 0;\n\t"
+        "@e cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%1], [%2, {%3, %4}], [%5];\n\t}" ::"r"(issuer),
+        "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred e;\n\tsetp.ne.u32 e, %0, 0;\n\t"
+        "@e cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%1], [%2, {%3, %4}], [%5];\n\t}" ::"r"(issuer),
+        "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+  }
+}
+// store (add == 0) or reducing store (add != 0) of one staged box, then close the bulk group
+WB_DEV void tma_store_commit_if(uint32_t issuer, uint32_t add, const void* map, int x, int y, uint32_t src) {
+  asm volatile(
+      "{\n\t.reg .pred e, s, r;\n\t"
+      "setp.ne.u32 e, %0, 0;\n\t"
+      "setp.eq.and.u32 s, %1, 0, e;\n\t"
+      "setp.ne.and.u32 r, %1, 0, e;\n\t"
+      "@s cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%2, {%3, %4}], [%5];\n\t"
+      "@r cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%2, {%3, %4}], [%5];\n\t"
+      "@e cp.async.bulk.commit_group;\n\t}" ::"r"(issuer),
+      "r"(add), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(src)
+      : "memory");
+}
+template <int CG>
+WB_DEV void umma_f16_if(uint32_t issuer, uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  if constexpr (CG == 2) {
+    asm volatile(
+        "{\n\t.reg .pred p, e;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\tsetp.ne.u32 e, %0, 0;\n\t"
+        "@e tcgen05.mma.cta_group::2.kind::f16 [%1], %2, %3, %4, p;\n\t}" ::"r"(issuer),
+        "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p, e;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\tsetp.ne.u32 e, %0, 0;\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%1], %2, %3, %4, p;\n\t}" ::"r"(issuer),
+        "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+template <int CG>
+WB_DEV void umma_commit_if(uint32_t issuer, uint32_t bar, uint16_t mask) {
+  if constexpr (CG == 2) {
+    asm volatile(
+        "{\n\t.reg .pred e;\n\tsetp.ne.u32 e, %0, 0;\n\t"
+        "@e tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%1], %2;\n\t}" ::"r"(issuer),
+        "r"(bar), "h"(mask)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred e;\n\tsetp.ne.u32 e, %0, 0;\n\t"
+        "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%1];\n\t}" ::"r"(issuer),
+        "r"(bar)
+        : "memory");
+  }
 }
 
 // ---------------------------------------------------------------- cluster launch control

@@ -46,14 +46,14 @@ class _Base:
         check(_lib.lib().wg_plan_enable_stamps(self._h, int(bool(on))), "wg_plan_enable_stamps")
 
     def read_stamps(self):
-        """Phase stamps of the last launches: array [grid, 16 events, 4 tiles] of GPU-timer nanoseconds (0 = not reached)."""
+        """Phase stamps of the last launches: array [grid, 32 events, 4 tiles]; events 11-14 and 16-20 are cycle sums of GPU-timer nanoseconds (0 = not reached)."""
         import numpy as np
         grid = self.info().grid
-        buf = (ctypes.c_ulonglong * (grid * 64))()
-        r = _lib.lib().wg_plan_read_stamps(self._h, buf, grid * 64)
+        buf = (ctypes.c_ulonglong * (grid * 128))()
+        r = _lib.lib().wg_plan_read_stamps(self._h, buf, grid * 128)
         if r < 0:
             check(r, "wg_plan_read_stamps")
-        return np.frombuffer(buf, dtype=np.uint64).reshape(grid, 16, 4).copy()
+        return np.frombuffer(buf, dtype=np.uint64).reshape(grid, 32, 4).copy()
 
     def status(self):
         """Synchronise and raise DeviceWaitError if any launch gave up."""

@@ -1,0 +1,134 @@
+"""Launch, check and time one GEMM kernel -- the reference's harness contract
+(backend/node/run_tma.py:47-230) over this library's C ABI.
+
+    python -m warpc_public_release_b200.gemm gemm 2048 2048 2048 > k.hdr
+    python -m warpc_public_release_b200.run_tma k.hdr [repeat]          # the header names shape and program
+    python -m warpc_public_release_b200.run_tma M N K [repeat]          # or: the rule's program for a shape
+
+Like the reference: inputs from `np.random.default_rng(1)`, A drawn first, integers in [-3, 3]
+(WARPC_INPUTS=hash: the index hash; WARPC_INPUTS=uniform: uniform[-1, 1], checked within
+1e-3 sqrt(K)); the first launch is waited for and checked against numpy's fp32 matmul, "first
+launch done, N wrong" goes to stderr, then `repeat` launches run back to back between two CUDA
+events and the last line reads
+
+    NAME MxNxK grid=(G, 1)  MATCH|MISMATCH bad=x/y  ms  TFLOP/s
+
+WARPC_NO_CHECK=1 skips the check (prints UNCHECKED), WARPC_VERIFY_LAST=1 also checks what the
+last timed launch left, WARPC_STAMPS=1 prints the phase stamps of one more launch.  Returns
+True when the check passed.  The numpy product is the harness's checker, exactly as in the
+reference; the kernel never runs on the CPU.
+"""
+import os
+import sys
+
+import numpy as np
+
+from . import launch_header, programs
+from .plan import Plan
+
+STAMP_NAMES = ["entry", "barriers initialised, cluster met", "producer: first stage issued", "producer: last stage issued",
+               "MMA: first stage landed", "MMA: last stage issued", "epilogue: accumulator ready", "epilogue: tile's stores issued",
+               "roles done", "exit", "MMA: accumulator free"]
+
+
+def make_inputs(m, n, k, seed=1):
+    kind = os.environ.get("WARPC_INPUTS", "integers")
+    rng = np.random.default_rng(seed)
+    if kind == "hash":
+        def val(count, salt):
+            i = np.arange(count, dtype=np.uint64)
+            return ((((i * np.uint64(2654435761)) + np.uint64(salt)) >> np.uint64(13)) % np.uint64(7)).astype(np.int64) - 3
+        return val(m * k, 1).reshape(m, k).astype(np.float16), val(n * k, 7).reshape(n, k).astype(np.float16), 1e-3
+    if kind == "uniform":
+        a = rng.uniform(-1.0, 1.0, size=(m, k)).astype(np.float16)
+        return a, rng.uniform(-1.0, 1.0, size=(n, k)).astype(np.float16), 1e-3 * k ** 0.5
+    a = rng.integers(-3, 4, size=(m, k)).astype(np.float16)
+    return a, rng.integers(-3, 4, size=(n, k)).astype(np.float16), 1e-3
+
+
+def variant_from_header(hdr, m, n, k):
+    """The program a header names: `.kernel swapped_M_N_K_TMxTN_sD` plus the flags in its note line."""
+    name = hdr["kernel"]
+    if name.startswith("one_"):
+        return programs.one(m, n, k, int(name.rsplit("_s", 1)[1]))
+    if name.startswith("pair_"):
+        return programs.pair(m, n, k, int(name.rsplit("_s", 1)[1]))
+    chosen = programs.choose(m, n, k)
+    tm, tn, _ = map(int, hdr["tile"].split())
+    depth = int(name.rsplit("_s", 1)[1])
+    if (chosen.tile_m, chosen.tile_n, chosen.depth) == (tm, tn, depth):
+        return chosen
+    return programs.swapped(m, n, k, tm, tn, depth, direct=launch_header.parameter(hdr, "c")["kind"] == "ptr",
+                            clc=int(hdr["grid"].split()[0]) > 148)
+
+
+def run(variant, m, n, k, repeat=20, seed=1, name=None, out=sys.stdout):
+    import torch
+    if not torch.cuda.is_available():
+        raise RuntimeError("run_tma: no CUDA device (this library has no CPU path)")
+    hdr = launch_header.parse_header(programs.header(variant, m, n, k))
+    name = name or hdr["kernel"]
+    if launch_header.shape_of(hdr) != (m, n, k):
+        raise RuntimeError("%s: the kernel was built for %dx%dx%d, the run is %dx%dx%d" % ((name,) + launch_header.shape_of(hdr) + (m, n, k)))
+    a, bt, tol = make_inputs(m, n, k, seed)
+    ref = None if os.environ.get("WARPC_NO_CHECK") else a.astype(np.float32) @ bt.astype(np.float32).T
+    da, db = torch.from_numpy(a).cuda(), torch.from_numpy(bt).cuda()
+    dc = torch.zeros((m, n), dtype=torch.float32, device="cuda")
+    plan = Plan(variant, m, n, k, da.data_ptr(), db.data_ptr(), dc.data_ptr())
+    grid = tuple(int(x) for x in hdr["grid"].split())
+    plan.launch()
+    plan.status()
+    if ref is None:
+        ms = plan.time_launches(repeat, warmup=0)
+        print("%-28s %dx%dx%d grid=%s  UNCHECKED  %.4f ms" % (name, m, n, k, grid, ms), file=out)
+        return True
+    c = dc.cpu().numpy()
+    bad = np.argwhere(~(np.abs(c - ref) <= tol))
+    print("first launch done, %d wrong" % len(bad), file=sys.stderr, flush=True)
+    ms = plan.time_launches(repeat, warmup=0)
+    plan.status()
+    if os.environ.get("WARPC_STAMPS"):
+        plan.enable_stamps(True)
+        plan.launch()
+        st = plan.read_stamps().astype(np.int64)
+        plan.enable_stamps(False)
+        t0 = st[:, 0, 0][st[:, 0, 0] > 0].min()
+        print("  %d CTAs ran; ns from the first CTA's entry: count:min/median/max per tile" % int((st[:, 0, 0] > 0).sum()), file=out)
+        for ev, label in enumerate(STAMP_NAMES):
+            cells = []
+            for t in range(4):
+                col = st[:, ev, t]
+                col = col[col > 0] - t0
+                cells.append("%5d:%7d/%7d/%7d" % (len(col), col.min(), np.median(col), col.max()) if len(col) else " " * 29)
+            print("  %2d %-34s %s" % (ev, label, "  ".join(cells)), file=out)
+    if os.environ.get("WARPC_VERIFY_LAST"):
+        c2 = dc.cpu().numpy()
+        print("  last launch: %d wrong" % int(np.count_nonzero(~(np.abs(c2 - ref) <= tol))), file=out)
+    flops = 2.0 * m * n * k
+    print("%-28s %dx%dx%d grid=%s  %s bad=%d/%d  %.4f ms  %.1f TFLOP/s" % (
+        name, m, n, k, grid, "MATCH" if len(bad) == 0 else "MISMATCH", len(bad), m * n, ms, flops / ms / 1e9), file=out)
+    if len(bad):
+        i, j = bad[0]
+        print("   first bad (%d,%d): got %s ref %s" % (i, j, c[i, j], ref[i, j]), file=out)
+    plan.close()
+    return len(bad) == 0
+
+
+def main(argv=None):
+    args = list(sys.argv[1:] if argv is None else argv)
+    if not args:
+        print(__doc__, file=sys.stderr)
+        return 2
+    if os.path.exists(args[0]):
+        hdr = launch_header.read_header(args[0])
+        m, n, k = launch_header.shape_of(hdr)
+        variant, rest = variant_from_header(hdr, m, n, k), args[1:]
+    else:
+        m, n, k = map(int, args[:3])
+        variant, rest = programs.choose(m, n, k), args[3:]
+    ok = run(variant, m, n, k, repeat=int(rest[0]) if rest else 30)
+    return 0 if ok else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())
