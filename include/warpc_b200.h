@@ -50,6 +50,9 @@ typedef struct wg_variant {
   int reps, atom_m, tmem_cols, nbuf, alloc_cols;
   int tiles_m, tiles_n, total_tiles, ctas, grid, persistent, kt;
   int a_box_rows, bt_box_rows, stage_bytes, tx_bytes, ref_dynsmem, ref_mbarriers, nflags;
+  /* 1 (set by wg_choose): wg_realise may run the program on the tile this library measured
+   * fastest on a B200 without TMA multicast; 0 (wg_derive): the tile named is the tile run. */
+  int retile;
 } wg_variant;
 
 /* How this library launches a variant (its own kernel's contract, what wg_header prints). */
@@ -111,7 +114,7 @@ int wg_time_launches(void* plan, int warmup, int repeat, float* ms_mean);
 
 /* Timing builds (the reference's: backend/stamp.ml:9-16, decoded in run_tma.py:176-192): turn
  * per-phase stamps on or off for the launches that follow, and read them back: 32 events x
- * 4 tiles per CTA (GPU nanosecond timer; events 11-14 and 16-20 are cycle sums), grid*128 words; returns the words written. */
+ * 4 tiles per CTA (GPU nanosecond timer; events 11-14 and 16-20 are cycle sums), grid*256 words (the second half: four 32-entry per-stage cycle traces of the first tile); returns the words written. */
 int wg_plan_enable_stamps(void* plan, int on);
 int wg_plan_read_stamps(void* plan, unsigned long long* out, size_t cap_words);
 
@@ -119,6 +122,10 @@ int wg_plan_read_stamps(void* plan, unsigned long long* out, size_t cap_words);
  * backend/sass.ml:339; its harness only has a reader for "waits that gave up",
  * backend/node/run_tma.py:129-137): overwrite hand-off word `index` of a split-K / stream-K plan. */
 int wg_plan_debug_set_flag(void* plan, int index, unsigned value);
+
+/* Timing experiments only (no reference counterpart): bit 0 = load nothing, bit 1 = issue no
+ * MMAs; barriers and the ring still cycle, results are meaningless. */
+int wg_plan_debug_set_mode(void* plan, unsigned flags);
 
 /* Where CTA tile index `tile` sits in C under a launch's tile walk (backend/tiles.ml:32-80). */
 int wg_tile_origin(const wg_launch_info* li, int tile, int* row, int* col);

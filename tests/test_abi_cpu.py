@@ -102,7 +102,7 @@ def test_tile_walk_matches_oracle():
         for t in range(tiles_m * tiles_n):
             assert _lib.lib().wg_tile_origin(ctypes.byref(li), t, ctypes.byref(r), ctypes.byref(c)) == 0
             want = rule.tile_origin(t, tiles_m, tiles_n, li.tile_m, li.tile_n, pair=li.cg, pairs=1, pair_on_cols=True,
-                                    group=v.group if li.cg == 2 else 1, serpentine=bool(v.serpentine))
+                                    group=li.group, serpentine=bool(li.serpentine))
             assert (r.value, c.value) == want, (s, t)
             seen.add(want)
         assert len(seen) == tiles_m * tiles_n
@@ -137,6 +137,12 @@ def test_realisation_invariants():
         if li.sched == 1:
             assert li.grid == 148
         assert li.group & (li.group - 1) == 0
+        if v.prog == 0 and not (v.streamk or v.split_grid > 1 or v.split > 1):
+            assert li.direct == 0                                  # the rule's programs run through the staged store
+    # an explicitly named tile is the tile run; the rule's choice may be re-tiled for this machine
+    assert w.realise(w.swapped(2048, 2048, 2048, 128, 128, 8), 2048, 2048, 2048).tile_m == 128
+    assert w.realise(w.choose(2048, 2048, 2048), 2048, 2048, 2048).tile_m == 256
+    assert w.choose(2048, 2048, 2048).tile_m == 128 and w.choose(2048, 2048, 2048).retile == 1
 
 
 def test_gemm_command_line():

@@ -17,7 +17,7 @@ class Variant(ctypes.Structure):
         "prog", "tile_m", "tile_n", "tile_k", "depth", "cluster_n", "clc", "ask_ahead", "direct", "serpentine", "group",
         "streamk", "split", "split_grid", "split_add", "late_launch", "bufs",
         "reps", "atom_m", "tmem_cols", "nbuf", "alloc_cols", "tiles_m", "tiles_n", "total_tiles", "ctas", "grid",
-        "persistent", "kt", "a_box_rows", "bt_box_rows", "stage_bytes", "tx_bytes", "ref_dynsmem", "ref_mbarriers", "nflags")]
+        "persistent", "kt", "a_box_rows", "bt_box_rows", "stage_bytes", "tx_bytes", "ref_dynsmem", "ref_mbarriers", "nflags", "retile")]
 
     def as_dict(self):
         return {n: getattr(self, n) for n, _ in self._fields_}
@@ -70,6 +70,7 @@ def lib():
         "wg_plan_enable_stamps": ([vp, i], i),
         "wg_plan_read_stamps": ([vp, ctypes.POINTER(ctypes.c_ulonglong), ctypes.c_size_t], i),
         "wg_plan_debug_set_flag": ([vp, i, u], i),
+        "wg_plan_debug_set_mode": ([vp, u], i),
         "wg_tile_origin": ([PL, i, ctypes.POINTER(i), ctypes.POINTER(i)], i),
         "wg_launch_noalloc": ([i, PV, i, i, i, vp, vp, vp, vp], i),
         "wg_noalloc_status": ([i, ctypes.POINTER(u * 4)], i),

@@ -72,9 +72,11 @@ EncodeTiledFn encode_tiled() {
   return fn;
 }
 
-// A row-major rows x cols matrix, box = box_rows x box_cols, 128-byte swizzle, zero fill
+// A row-major rows x cols matrix, box = box_rows x box_cols, 128-byte swizzle (operands) or none
+// (the C staging boxes), zero fill
 // out of bounds -- the map backend/node/run_tma.py:32-45 encodes from a `.tmap` line.
-int encode_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem, const void* ptr, int rows, int cols, int box_rows, int box_cols) {
+int encode_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem, const void* ptr, int rows, int cols, int box_rows, int box_cols,
+              CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   EncodeTiledFn enc = encode_tiled();
   if (!enc) return WG_E_NODRIVER;
   cuuint64_t dims[2] = {cuuint64_t(cols), cuuint64_t(rows)};
@@ -82,7 +84,7 @@ int encode_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem, const void* pt
   cuuint32_t box[2] = {cuuint32_t(box_cols), cuuint32_t(box_rows)};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                   swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? WG_OK : int(r);
 }
 
@@ -122,7 +124,7 @@ int fill_plan(Plan* pl, int device, const wg_variant* v, int M, int N, int K, co
   std::memset(&pl->map_c, 0, sizeof pl->map_c);
   if ((r = encode_2d(&pl->map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, dA, M, K, li.a_box_rows, 64)) != WG_OK) return r;
   if ((r = encode_2d(&pl->map_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, dBt, N, K, li.bt_box_rows, 64)) != WG_OK) return r;
-  if (!li.direct && (r = encode_2d(&pl->map_c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dC, M, N, li.c_box_rows, 32)) != WG_OK) return r;
+  if (!li.direct && (r = encode_2d(&pl->map_c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dC, M, N, li.c_box_rows, 32, CU_TENSOR_MAP_SWIZZLE_NONE)) != WG_OK) return r;
   pl->flag_bytes = size_t(li.nflags > 0 ? li.nflags : 1) * sizeof(uint32_t);
   WG_CUDA(cudaMalloc(&pl->d_flags, pl->flag_bytes));
   WG_CUDA(cudaMalloc(&pl->d_status, 8 * sizeof(uint32_t)));
@@ -310,12 +312,12 @@ extern "C" int wg_time_launches(void* plan, int warmup, int repeat, float* ms_me
   return r;
 }
 
-// Timing runs: phase stamps (32 events x 4 tiles per CTA: GPU nanosecond timer, plus cycle sums) of the
-// launches that follow; wg_plan_read_stamps synchronises and copies grid*128 words out.
+// Timing runs: phase stamps (per CTA: 32 events x 4 tiles on the GPU nanosecond timer or as cycle sums, then four 32-entry per-stage cycle traces of the first tile) of the
+// launches that follow; wg_plan_read_stamps synchronises and copies grid*256 words out.
 extern "C" int wg_plan_enable_stamps(void* plan, int on) {
   Plan* pl = static_cast<Plan*>(plan);
   if (!pl) return WG_E_ARG;
-  const size_t bytes = size_t(pl->li.grid) * 128 * sizeof(unsigned long long);
+  const size_t bytes = size_t(pl->li.grid) * 256 * sizeof(unsigned long long);
   if (on && !pl->d_stamps) {
     WG_CUDA(cudaMalloc(&pl->d_stamps, bytes));
   }
@@ -327,7 +329,7 @@ extern "C" int wg_plan_enable_stamps(void* plan, int on) {
 extern "C" int wg_plan_read_stamps(void* plan, unsigned long long* out, size_t cap_words) {
   Plan* pl = static_cast<Plan*>(plan);
   if (!pl || !out || !pl->d_stamps) return WG_E_ARG;
-  const size_t words = size_t(pl->li.grid) * 128;
+  const size_t words = size_t(pl->li.grid) * 256;
   if (cap_words < words) return WG_E_ARG;
   WG_CUDA(cudaDeviceSynchronize());
   WG_CUDA(cudaMemcpy(out, pl->d_stamps, words * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
@@ -411,7 +413,7 @@ extern "C" int wg_launch_noalloc(int device, const wg_variant* v, int M, int N, 
   std::memset(&map_c, 0, sizeof map_c);
   if ((r = encode_2d(&map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, dA, M, K, li.a_box_rows, 64)) != WG_OK) return r;
   if ((r = encode_2d(&map_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, dBt, N, K, li.bt_box_rows, 64)) != WG_OK) return r;
-  if (!li.direct && (r = encode_2d(&map_c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dC, M, N, li.c_box_rows, 32)) != WG_OK) return r;
+  if (!li.direct && (r = encode_2d(&map_c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dC, M, N, li.c_box_rows, 32, CU_TENSOR_MAP_SWIZZLE_NONE)) != WG_OK) return r;
   KParams p;
   std::memset(&p, 0, sizeof p);
   p.M = M, p.N = N, p.K = K, p.kt = K / 64;
@@ -459,4 +461,13 @@ extern "C" int wg_noalloc_status(int device, unsigned out[4]) {
   WG_CUDA(cudaMemcpy(st, scratch, sizeof st, cudaMemcpyDeviceToHost));
   for (int i = 0; i < 4; ++i) out[i] = st[i];
   return st[0] == 0 ? WG_OK : WG_E_DEVICE_WAIT;
+}
+
+// Timing experiments: bit 0 = the producer loads nothing (barriers still cycle), bit 1 = no MMAs
+// are issued (commits still are).  Results are then meaningless; only the time is of interest.
+extern "C" int wg_plan_debug_set_mode(void* plan, unsigned flags) {
+  Plan* pl = static_cast<Plan*>(plan);
+  if (!pl) return WG_E_ARG;
+  pl->p.debug = flags;
+  return WG_OK;
 }

@@ -56,10 +56,11 @@ struct KParams {
   uint32_t* flags;              // split-K / stream-K hand-off words
   uint32_t* status;             // 8 words: [0] code, [1] site detail, [2] CTA, [3] parity/stage
   unsigned long long timeout_ns;
+  unsigned int debug;           // timing experiments only: bit 0 the producer loads nothing, bit 1 no MMAs are issued
   unsigned long long* stamps;   // timing builds: 32 events x 4 tiles per CTA, or null
 };
 
-template <int CG_, int TM_, int TN_, bool DIRECT_, int EPI_ROWS_ = 16, int EPI_COPIES_ = 2>
+template <int CG_, int TM_, int TN_, bool DIRECT_, int EPI_ROWS_ = 32, int EPI_COPIES_ = 2>
 struct Cfg {
   static constexpr int CG = CG_, TM = TM_, TN = TN_, TK = 64;
   static constexpr bool DIRECT = DIRECT_;
@@ -119,6 +120,7 @@ WB_DEV uint32_t ld_shared_u32(uint32_t addr) {
   asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
   return v;
 }
+WB_DEV void st_shared_plain(uint32_t addr, uint32_t v) { asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory"); }
 WB_DEV void st_shared_u32(uint32_t addr, uint32_t v) { asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory"); }
 
 WB_DEV void record_failure(const KParams& p, uint32_t code, uint32_t detail, uint32_t parity) {
@@ -137,28 +139,36 @@ enum : int { EV_ENTRY = 0, EV_SETUP = 1, EV_LOAD_FIRST = 2, EV_LOAD_LAST = 3, EV
 // cycle counters of a timing run: events 16.. hold sums of clock64() intervals, not times
 enum : int { EV_CYC_PROD_WAIT = 16, EV_CYC_PROD_ISSUE = 17, EV_CYC_MMA_WAIT = 18, EV_CYC_MMA_ISSUE = 19, EV_CYC_MMA_ACC_WAIT = 20 };
 WB_DEV void stamp_value(const KParams& p, int ev, int slot, long long value) {
-  if (p.stamps != nullptr && slot < 4) p.stamps[(size_t(blockIdx.x) * 32 + ev) * 4 + slot] = (unsigned long long)value;
+  if (p.stamps != nullptr && slot < 4) p.stamps[(size_t(blockIdx.x) * 64 + ev) * 4 + slot] = (unsigned long long)value;
+}
+// per-stage trace of a CTA's first tile: SM cycle counter at k-step `kk` (< 32) of trace `which`
+// (0 producer saw the slot empty, 1 producer issued, 2 MMA warp saw it full, 3 MMA warp issued)
+WB_DEV void trace(const KParams& p, int which, int kk) {
+  if (p.stamps != nullptr && kk < 32) p.stamps[size_t(blockIdx.x) * 256 + 128 + which * 32 + kk] = (unsigned long long)clock64();
 }
 WB_DEV void stamp(const KParams& p, int ev, int slot) {
-  if (p.stamps != nullptr && slot < 4) p.stamps[(size_t(blockIdx.x) * 32 + ev) * 4 + slot] = globaltimer();
+  if (p.stamps != nullptr && slot < 4) p.stamps[(size_t(blockIdx.x) * 64 + ev) * 4 + slot] = globaltimer();
 }
 
-// Bounded wait on an mbarrier phase by a whole, converged warp.  Returns false when the kernel
-// is giving up.  The common case is one asm-internal spin; its outcome is made warp-uniform with
-// a vote so that every branch the roles take on it is a uniform branch.  Only when 4096 polls
-// (each already sleeping in hardware) have failed does the warp look at the abort words and the
-// GPU-wide timer, which is slow to read.
-// CLUSTER: acquire at cluster scope (data another CTA stored before arriving).
-template <bool CLUSTER = false>
+// Bounded wait on an mbarrier phase.  Returns false when the kernel is giving up.
+// WARP: called by a whole, converged warp (the outcome is made warp-uniform with a vote);
+// otherwise by a single lane that runs its role alone (the TMA producer and the MMA issuer:
+// one lane's try_wait is one request to the barrier unit, a warp's is thirty-two).
+// The common case is one asm-internal spin.  Only when 4096 polls (each already sleeping in
+// hardware) have failed does the waiter look at the abort words and the GPU-wide timer, which
+// is slow to read.  CLUSTER: acquire at cluster scope (data another CTA stored before arriving).
+template <bool CLUSTER = false, bool WARP = true>
 WB_DEV bool wait_bar(const KParams& p, uint32_t abort_addr, uint32_t bar, uint32_t parity, uint32_t code, uint32_t detail) {
-  if (__all_sync(0xffffffffu, mbar_spin_wait<CLUSTER>(bar, parity, 1u << 12))) return true;
+  auto all = [](uint32_t ok) { return WARP ? (__all_sync(0xffffffffu, ok) != 0) : (ok != 0u); };
+  auto any = [](bool bad) { return WARP ? (__any_sync(0xffffffffu, bad) != 0) : bad; };
+  if (all(mbar_spin_wait<CLUSTER>(bar, parity, 1u << 12))) return true;
   const uint64_t t0 = globaltimer();
   for (;;) {
-    if (__all_sync(0xffffffffu, mbar_spin_wait<CLUSTER>(bar, parity, 64))) return true;
+    if (all(mbar_spin_wait<CLUSTER>(bar, parity, 64))) return true;
     uint32_t bad = ld_shared_u32(abort_addr) | ld_relaxed_gpu(p.status);
     const bool late = globaltimer() - t0 > p.timeout_ns;
     if (late && bad == 0u) record_failure(p, code, detail, parity);
-    if (__any_sync(0xffffffffu, bad != 0u || late)) {
+    if (any(bad != 0u || late)) {
       st_shared_u32(abort_addr, 1u);
       return false;
     }
@@ -194,7 +204,7 @@ struct Work {
 };
 
 // The sequence of work units a CTA walks; every role of the CTA walks the same one.
-template <class C>
+template <class C, bool WARP = true>
 struct Walker {
   const KParams& p;
   uint32_t abort_addr, sched_full, sched_slot, sched_empty_first;  // shared addresses (the last in the first CTA)
@@ -243,9 +253,10 @@ struct Walker {
         return tile < p.ntiles;
       }
       if (sched == SCHED_CLC) {
-        if (!wait_bar<true>(p, abort_addr, sched_full, sched_parity, ST_WAIT_SCHED, 0)) return false;
+        if (!wait_bar<true, WARP>(p, abort_addr, sched_full, sched_parity, ST_WAIT_SCHED, 0)) return false;
         sched_parity ^= 1u;
-        const uint32_t valid = warp_uniform(ld_shared_u32(sched_slot)), first = warp_uniform(ld_shared_u32(sched_slot + 4));
+        const uint32_t valid = ld_shared_u32(sched_slot), first = ld_shared_u32(sched_slot + 4);
+        if (WARP) __syncwarp();
         if (lane == 0) mbar_arrive_cluster(sched_empty_first);
         if (!valid) return false;
         tile = int(first + rank);
@@ -320,9 +331,11 @@ WB_DEV void epi_staged_tile(const CUtensorMap* map_c, uint32_t tbase, uint32_t m
     bulk_wait_read<C::EPI_COPIES - 1>();  // the store that last read this copy is done with it (only the issuing lane has groups)
     __syncwarp();
     if (prof) t_copy += clock64() - t0, t0 = clock64();
+    // register j is one C row: the warp's 32 lanes write its 128 bytes side by side (no bank
+    // conflict, so the staging box needs no swizzle)
+    const uint32_t mine = copy + lane * 4u;
 #pragma unroll
-    for (int j = 0; j < C::EPI_ROWS; ++j)  // 128-byte swizzle: 16-byte chunk index xor row-in-8
-      st_shared_u32(copy + uint32_t(j) * 128u + ((lane * 4u) ^ (uint32_t(j & 7) << 4)), v[i & 1][j]);
+    for (int j = 0; j < C::EPI_ROWS; ++j) st_shared_plain(mine + uint32_t(j) * 128u, v[i & 1][j]);
     fence_proxy_async_smem();
     __syncwarp();
     if (prof) t_sts += clock64() - t0, t0 = clock64();
@@ -425,123 +438,90 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 
   // ---------------------------------------------------------------- roles
   if (warp == 0) {
-    // ===== producer: TMA loads into this CTA's ring, counted on the leader's barrier
-    Walker<C> walk(p, ctrl, rank, lane);
-    Work w;
-    int stage = 0, nth = 0;
-    uint32_t phase = 0;
-    bool ok = true;
-    const bool prof = p.stamps != nullptr;
-    // what a stage's loads need, kept as running values so the issuing lane's chain is short
-    const uint32_t full_leader0 = (CG == 2) ? mapa(full_bar(0), 0) : full_bar(0);
-    while (ok && walk.next(w)) {
-      int row, col;
-      tile_origin<C>(p, w.tile, row, col);
-      // a pair's CTAs sit side by side: same rows, so they split the A tile between them
-      const int a_row = row + int(rank) * C::A_ROWS;
-      long long cyc_wait = 0, cyc_issue = 0, c0 = 0;
-      int x = w.kb * C::TK;
-      for (int kk = w.kb; kk < w.ke; ++kk, x += C::TK) {
-        if (prof) c0 = clock64();
-        if (!wait_bar(p, abort_addr, empty_bar(stage), phase ^ 1u, ST_WAIT_EMPTY, uint32_t(stage))) {
-          ok = false;
-          break;
-        }
-        if (prof) cyc_wait += clock64() - c0, c0 = clock64();
-        const uint32_t sa = ring + uint32_t(stage) * C::STAGE_BYTES, sb = sa + C::A_BYTES;
-        const uint32_t bar = full_leader0 + 8u * uint32_t(stage);
-        mbar_arrive_expect_tx_if(issuer & uint32_t(leader), full_bar(stage), C::TX_BYTES);
-        tma_load_2d_if<CG>(issuer, sa, &map_a, x, a_row, bar);
-        tma_load_2d_if<CG>(issuer, sb, &map_b, x, col, bar);
-        if (prof) {
-          if (kk == w.kb && lane == 0) stamp(p, EV_LOAD_FIRST, nth);
-          cyc_issue += clock64() - c0;
-        }
-        if (++stage == depth) stage = 0, phase ^= 1u;
-      }
-      if (prof && lane == 0)
-        stamp(p, EV_LOAD_LAST, nth), stamp_value(p, EV_CYC_PROD_WAIT, nth, cyc_wait), stamp_value(p, EV_CYC_PROD_ISSUE, nth, cyc_issue);
-      ++nth;
-    }
-    // every stage this CTA filled has been released before it leaves
-    for (int i = 0; ok && i < depth; ++i) {
-      ok = wait_bar(p, abort_addr, empty_bar(stage), phase ^ 1u, ST_WAIT_EMPTY, 0x100u + uint32_t(stage));
-      if (++stage == depth) stage = 0, phase ^= 1u;
-    }
-  } else if (warp == 1) {
-    // ===== MMA issuer: the pair leader's warp 1 issues for both CTAs
-    if (leader) {
-      Walker<C> walk(p, ctrl, rank, lane);
+    // ===== producer: TMA loads into this CTA's ring, counted on the leader's barrier.  One lane
+    // runs the role; a tile's k-steps are one asm loop (load_k_loop), re-entered after the bounded,
+    // timed wait whenever a slot stayed taken beyond the loop's own poll limit.
+    if (lane == 0) {
+      Walker<C, false> walk(p, ctrl, rank, lane);
       Work w;
-      int stage = 0, acc = 0, nth = 0;
-      uint32_t phase = 0, acc_phase = 0;
+      uint32_t stage = 0, phase = 0;
+      int nth = 0;
       bool ok = true;
-      const bool prof = p.stamps != nullptr;
+      const uint32_t full_leader0 = (CG == 2) ? mapa(full_bar(0), 0) : full_bar(0);
+      while (ok && walk.next(w)) {
+        int row, col;
+        tile_origin<C>(p, w.tile, row, col);
+        // a pair's CTAs sit side by side: same rows, so they split the A tile between them
+        const int a_row = row + int(rank) * C::A_ROWS;
+        uint32_t kleft = uint32_t(w.ke - w.kb);
+        int x = w.kb * C::TK;
+        stamp(p, EV_LOAD_FIRST, nth);
+        while (kleft != 0u) {
+          if (load_k_loop<CG>(1u, kleft, uint32_t(depth), stage, phase, x, empty_bar(0), full_bar(0), full_leader0, leader ? 1u : 0u,
+                              C::TX_BYTES, ring, uint32_t(C::STAGE_BYTES), uint32_t(C::A_BYTES), &map_a, a_row, &map_b, col, 1u << 14, p.debug) != 0u &&
+              !wait_bar<false, false>(p, abort_addr, empty_bar(int(stage)), phase ^ 1u, ST_WAIT_EMPTY, stage)) {
+            ok = false;
+            break;
+          }
+        }
+        stamp(p, EV_LOAD_LAST, nth);
+        ++nth;
+      }
+      // every stage this CTA filled has been released before it leaves
+      for (int i = 0; ok && i < depth; ++i) {
+        ok = wait_bar<false, false>(p, abort_addr, empty_bar(int(stage)), phase ^ 1u, ST_WAIT_EMPTY, 0x100u + stage);
+        if (++stage == uint32_t(depth)) stage = 0, phase ^= 1u;
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ===== MMA issuer: one lane of the pair leader's warp 1 issues for both CTAs; a tile's
+    // k-steps are one asm loop (mma_k_loop): wait full[s], REPS x 4 MMAs, commit to empty[s].
+    if (leader && lane == 0) {
+      Walker<C, false> walk(p, ctrl, rank, lane);
+      Work w;
+      uint32_t stage = 0, phase = 0, acc_phase = 0;
+      int acc = 0, nth = 0;
+      bool ok = true;
       constexpr uint16_t mask = (CG == 2) ? 0x3 : 0x1;
       // shared-memory descriptors: the high word is fixed (SBO 1024 B, version 1, 128-byte swizzle);
       // the low word is (address >> 4) | LBO field, so a stage, an atom or a 16-element k-step on
       // is a plain add to it
       constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
       constexpr uint32_t STAGE16 = C::STAGE_BYTES >> 4, ATOM16 = uint32_t((C::MMA_M / CG) * 128) >> 4;
-      const uint32_t a_lo0 = ((ring & 0x3FFFFu) >> 4) | (1u << 16);  // the stage's A tile (the MMA's B operand)
-      const uint32_t b_lo0 = a_lo0 + (C::A_BYTES >> 4);              // the stage's B^T tile (the MMA's A operand)
-      uint32_t stage16 = 0;
+      const uint32_t a_lo0 = ((ring & 0x3FFFFu) >> 4) | (1u << 16);  // stage 0's A tile (the MMA's B operand)
+      const uint32_t b_lo0 = a_lo0 + (C::A_BYTES >> 4);              // stage 0's B^T tile (the MMA's A operand)
       while (ok && walk.next(w)) {
-        if (!wait_bar(p, abort_addr, acc_empty_bar(acc), acc_phase ^ 1u, ST_WAIT_ACC_EMPTY, uint32_t(acc))) {
+        if (!wait_bar<false, false>(p, abort_addr, acc_empty_bar(acc), acc_phase ^ 1u, ST_WAIT_ACC_EMPTY, uint32_t(acc))) {
           ok = false;
           break;
         }
         tc_fence_after();
-        if (prof && lane == 0) stamp(p, EV_ACC_FREE, nth);
+        stamp(p, EV_ACC_FREE, nth);
         const uint32_t d = tmem_base + uint32_t(acc * C::NCOLS);
-        uint32_t accumulate = 0;
-        bool landed = false;
-        long long cyc_wait = 0, cyc_issue = 0, c0 = 0;
-        for (int kk = w.kb; kk < w.ke; ++kk) {
-          if (prof) c0 = clock64();
-          if (!landed && !wait_bar(p, abort_addr, full_bar(stage), phase, ST_WAIT_FULL, uint32_t(stage))) {
+        uint32_t kleft = uint32_t(w.ke - w.kb), accumulate = 0;
+        stamp(p, EV_MMA_FIRST, nth);
+        while (kleft != 0u) {
+          if (mma_k_loop<CG, C::REPS>(1u, kleft, uint32_t(depth), stage, phase, accumulate, full_bar(0), empty_bar(0), d, uint32_t(C::SPAN),
+                                      b_lo0, ATOM16, a_lo0, STAGE16, DESC_HI, C::IDESC, 1u << 14, p.debug) != 0u &&
+              !wait_bar<false, false>(p, abort_addr, full_bar(int(stage)), phase, ST_WAIT_FULL, stage)) {
             ok = false;
             break;
           }
-          tc_fence_after();
-          if (prof) {
-            cyc_wait += clock64() - c0, c0 = clock64();
-            if (kk == w.kb && lane == 0) stamp(p, EV_MMA_FIRST, nth);
-          }
-          const uint32_t a_lo = a_lo0 + stage16, b_lo = b_lo0 + stage16;
-#pragma unroll
-          for (int r = 0; r < C::REPS; ++r) {
-#pragma unroll
-            for (int j = 0; j < C::TK / 16; ++j) {
-              // MMA "A" = B^T rows of atom r; MMA "B" = the tile of A; 16 K-elements = 32 bytes on
-              const uint64_t adesc = (uint64_t(DESC_HI) << 32) | uint64_t(b_lo + uint32_t(r) * ATOM16 + uint32_t(j) * 2u);
-              const uint64_t bdesc = (uint64_t(DESC_HI) << 32) | uint64_t(a_lo + uint32_t(j) * 2u);
-              umma_f16_if<CG>(issuer, d + uint32_t(r * C::SPAN), adesc, bdesc, C::IDESC, (j == 0) ? accumulate : 1u);
-            }
-          }
-          accumulate = 1;
-          int nstage = stage + 1;
-          uint32_t nphase = phase, nstage16 = stage16 + STAGE16;
-          if (nstage == depth) nstage = 0, nphase ^= 1u, nstage16 = 0;
-          // asking a stage ahead: has the next stage landed already?
-          landed = (p.ask_ahead && kk + 1 < w.ke) ? (__all_sync(0xffffffffu, mbar_test_wait(full_bar(nstage), nphase)) != 0) : false;
-          umma_commit_if<CG>(issuer, empty_bar(stage), mask);  // the stage is free once these MMAs have read it
-          if (prof) cyc_issue += clock64() - c0;
-          stage = nstage, phase = nphase, stage16 = nstage16;
         }
         if (!ok) break;
-        umma_commit_if<CG>(issuer, acc_full_bar(acc), mask);  // the accumulator is complete in both CTAs
-        if (prof && lane == 0)
-          stamp(p, EV_MMA_LAST, nth), stamp_value(p, EV_CYC_MMA_WAIT, nth, cyc_wait), stamp_value(p, EV_CYC_MMA_ISSUE, nth, cyc_issue);
+        umma_commit<CG>(acc_full_bar(acc), mask);  // the accumulator is complete in both CTAs
+        stamp(p, EV_MMA_LAST, nth);
         if (++acc == nbuf) acc = 0, acc_phase ^= 1u;
         ++nth;
       }
       // every accumulator has been read out in both CTAs before leaving
       for (int i = 0; ok && i < nbuf; ++i) {
-        ok = wait_bar(p, abort_addr, acc_empty_bar(acc), acc_phase ^ 1u, ST_WAIT_ACC_EMPTY, 0x100u + uint32_t(acc));
+        ok = wait_bar<false, false>(p, abort_addr, acc_empty_bar(acc), acc_phase ^ 1u, ST_WAIT_ACC_EMPTY, 0x100u + uint32_t(acc));
         if (++acc == nbuf) acc = 0, acc_phase ^= 1u;
       }
     }
+    __syncwarp();
   } else if (warp == 2) {
     // ===== scheduler (cluster launch control): the cluster's first CTA asks for one more
     // cluster's tiles at a time and hands the answer to every taker of both CTAs
@@ -613,7 +593,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         tc_fence_after();
         if (first_warp && lane == 0) stamp(p, EV_ACC_READY, nth);
         // timing runs: the first warp's cycles in each part of the tile's store, events 11-14
-        unsigned long long* prof = (p.stamps != nullptr && first_warp && nth < 4) ? p.stamps + (size_t(blockIdx.x) * 32 + 11) * 4 + nth : nullptr;
+        unsigned long long* prof = (p.stamps != nullptr && first_warp && nth < 4) ? p.stamps + (size_t(blockIdx.x) * 64 + 11) * 4 + nth : nullptr;
         epi_staged_tile<C>(&map_c, tbase, my_staging, row, col, q, lane, false, acc_empty_addr, prof);
       } else if (p.sched == SCHED_SPLITK) {
         // ---- split-K over the grid, adding in the L2 (gemm_swapped.ml:660-710).  The S runs

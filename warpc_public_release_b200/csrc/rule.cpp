@@ -230,6 +230,7 @@ extern "C" int wg_choose(int m, int n, int k, int sm, wg_variant* out) {
   }
   const int r = wg_derive(m, n, k, &v);
   if (r != WG_OK) return r == WG_E_VARIANT ? WG_E_SHAPE : r;
+  v.retile = 1;
   *out = v;
   return WG_OK;
 }
@@ -264,10 +265,25 @@ extern "C" int wg_realise(const wg_variant* v, int M, int N, int K, wg_launch_in
     li.cg = 2, li.tile_m = v->tile_m, li.tile_n = v->tile_n, li.direct = v->direct && v->split == 1;
     li.cluster = 2;
     li.nbuf = v->nbuf;
-    li.cl_n = v->tiles_n / 2;
-    li.group = effective_group(v->group, v->tiles_m, li.cl_n);
+    int group = v->group, clc = v->clc;
+    const bool plain = !v->streamk && v->split_grid <= 1 && v->split <= 1;
+    if (v->retile && plain) {
+      // Measured on a B200 (no TMA multicast): one tcgen05.mma costs 55-90 cycles to issue whatever
+      // its N, so MMAs narrower than N = 256 (tile_m < 256) cannot keep the tensor pipe full; the
+      // store through staging copies and TMA beats the store from the registers at every size; and
+      // a fixed grid walking tiles by stride beats cluster launch control until tiles are 256 x 256.
+      li.direct = 0;
+      const int pair_tiles_256 = (M % 256 == 0 && N % 256 == 0) ? (M / 256) * (N / 256) : 0;
+      if (v->tile_m < 256 && v->tile_n == 128 && pair_tiles_256 >= 50) {
+        li.tile_m = 256, li.tile_n = 128, li.depth = 6, clc = 0, group = 8;
+        li.nbuf = (2 * pair_tiles_256 > kSms) ? 2 : 1;
+      }
+    }
+    const int tiles_m = (M + li.tile_m - 1) / li.tile_m, tiles_n = (N + li.tile_n - 1) / li.tile_n;
+    const int total = tiles_m * tiles_n;
+    li.cl_n = tiles_n / 2;
+    li.group = effective_group(group, tiles_m, li.cl_n);
     li.serpentine = v->serpentine && li.cl_n > 1 && (li.cl_n & (li.cl_n - 1)) == 0;
-    const int total = v->total_tiles;
     if (v->streamk) {
       li.sched = 4, li.grid = kSms / 2 * 2;
       li.nflags = li.grid + total;
@@ -276,7 +292,7 @@ extern "C" int wg_realise(const wg_variant* v, int M, int N, int K, wg_launch_in
       li.sched = 3, li.grid = total * li.split;
       li.nflags = li.grid;
       if (li.grid / 2 > resident_clusters(2)) return WG_E_VARIANT;
-    } else if (v->clc) {
+    } else if (clc) {
       li.sched = 2, li.grid = total;
     } else if (total <= kSms) {
       li.sched = 0, li.grid = total;
@@ -325,17 +341,17 @@ extern "C" int wg_header(const wg_variant* v, int M, int N, int K, char* buf, si
   } else {
     append(s, "# gemm_one %dx%dx%d, ring depth %d, one CTA a 128x128 tile", M, N, K, v->depth);
   }
-  append(s, "# b200 kernel %s: sched %d, cluster %d, tensor memory %d columns", wg_kernel_name(li.kernel_id), li.sched, li.cluster,
-         li.tmem_cols);
+  append(s, "# b200 kernel %s: %dx%d a CTA, ring depth %d, %d accumulator%s, sched %d, cluster %d, tensor memory %d columns",
+         wg_kernel_name(li.kernel_id), li.tile_m, li.tile_n, li.depth, li.nbuf, li.nbuf > 1 ? "s" : "", li.sched, li.cluster, li.tmem_cols);
   append(s, ".kernel %s", name);
   append(s, ".sm sm_100a");
   append(s, ".barriers 2");
   append(s, ".threads %d", li.threads);
   append(s, ".smem 0");
   append(s, ".dynsmem %d", li.dynsmem);
-  append(s, ".tile %d %d %d", v->tile_m, v->tile_n, kTileK);
+  append(s, ".tile %d %d %d", li.tile_m, li.tile_n, kTileK);
   if (li.direct) append(s, ".ptr c %d %d 4", M, N);
-  else append(s, ".tmap c %d %d 4 %d 32 128", M, N, li.c_box_rows);
+  else append(s, ".tmap c %d %d 4 %d 32 0", M, N, li.c_box_rows);
   append(s, ".tmap a %d %d 2 %d 64 128", M, K, li.a_box_rows);
   append(s, ".tmap bt %d %d 2 %d 64 128", N, K, li.bt_box_rows);
   if (li.nflags > 0) append(s, ".ptr flags 1 %d 4", li.nflags);

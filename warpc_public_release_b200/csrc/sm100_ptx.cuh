@@ -382,6 +382,146 @@ WB_DEV void umma_commit_if(uint32_t issuer, uint32_t bar, uint16_t mask) {
   }
 }
 
+// ---------------------------------------------------------------- k loops, written out
+// The two loops a tile's time is spent in -- the producer's and the MMA issuer's -- each as ONE
+// asm block: barrier wait, issue, release and ring bookkeeping are ~30 instructions per k-step
+// with nothing the compiler adds in between.  That matters because one tcgen05.mma takes
+// 65-90 cycles to issue and the tensor pipe queues little: any cycles spent between two stages'
+// MMAs are cycles the tensor cores idle.  (The reference's hand-scheduled loops are 45 and 22
+// SASS instructions; docs/warpc.md:274-275.)
+//
+// Every lane of the warp runs the loop; `issuer` is non-zero in the lane whose instructions
+// take effect.  A wait that does not complete within `limit` polls ends the loop with status 1
+// and the state (stage, phase, k-steps left, ...) as of that k-step, so the caller can run its
+// bounded, timed wait and re-enter: the asm itself never spins without limit.  The polls are
+// test_wait (they return at once) rather than try_wait: a try_wait that finds the phase open
+// suspends the thread, and the wake-up after the arrival costs several hundred cycles -- more
+// than a ring of four to eight stages can hide.
+
+// No tcgen05.fence sits between the wait and the MMAs: operand tiles arrive through the async
+// proxy and the mbarrier's completion orders them for the MMAs that read them; the tcgen05
+// fences are for hand-offs of tensor memory between threads (once per tile, around the
+// accumulator barriers), and one inside this loop would drain the tensor pipe at every k-step.
+// MMA issuer: for each of `kleft` k-steps wait full[stage], issue REPS x 4 MMAs (A operand =
+// the stage's B^T tile, low descriptor word ma_lo0 + stage * step16, atoms atom16 apart; B operand
+// = its A tile, mb_lo0 + ...; +2 per 16 K-elements; atom r accumulates at column d + r * span),
+// commit to empty[stage].  `accumulate` is 0 until the tile's first MMA has been issued.
+#define WB_KL_MMA(G, D, A, B, PRED)                                   \
+  "mov.b64 da, {" A ", %16};\n\tmov.b64 db, {" B ", %16};\n\t"        \
+  "@e tcgen05.mma.cta_group::" G ".kind::f16 [" D "], da, db, %17, " PRED ";\n\t"
+#define WB_KL_MMA_J(G, D, A0, J, PRED) \
+  "add.u32 ta, " A0 ", " J ";\n\tadd.u32 tb, mb, " J ";\n\t" WB_KL_MMA(G, D, "ta", "tb", PRED)
+// Order inside one k-step: the first MMA, then the commit that frees the stage BEFORE (issued
+// while that MMA runs, so it never sits between two stages' MMAs), the middle MMAs, a
+// non-blocking probe of the next stage's barrier (its answer is back before the loop comes
+// round), the last two MMAs.
+#define WB_KL_HEAD                                                                                   \
+  "{\n\t.reg .pred e, ec, p, q, w, pa, pt, c, pr, pv, pm;\n\t"                                       \
+  ".reg .b32 n, fb, eb, s16, ta, tb, d1, a1, ma, mb, dbg, pb, nst, nfb, neb, ns16, nph;\n\t"         \
+  ".reg .b64 da, db;\n\t.reg .b16 mk;\n\t"                                                           \
+  "setp.ne.u32 ec, %5, 0;\n\tand.b32 dbg, %15, 2;\n\tsetp.eq.and.u32 e, dbg, 0, ec;\n\t"             \
+  "setp.eq.u32 pt, 0, 0;\n\tsetp.ne.u32 pa, %4, 0;\n\tmov.b16 mk, 3;\n\t"                            \
+  "setp.eq.u32 pr, 1, 0;\n\tsetp.eq.u32 pv, 1, 0;\n\tmov.u32 pb, 0;\n\t"                             \
+  "mov.u32 %0, 0;\n\t"                                                                               \
+  "mad.lo.u32 fb, %1, 8, %7;\n\tmad.lo.u32 eb, %1, 8, %8;\n\tmul.lo.u32 s16, %1, %14;\n\t"           \
+  "add.u32 d1, %9, %10;\n"                                                                           \
+  "WB_KL_LOOP:\n\t"                                                                                  \
+  "@pr bra WB_KL_GO;\n\t"                                                                            \
+  "mov.u32 n, 0;\n"                                                                                  \
+  "WB_KL_WAIT:\n\t"                                                                                  \
+  "mbarrier.test_wait.parity.shared::cta.b64 p, [fb], %2;\n\t"                                       \
+  "@p bra WB_KL_GO;\n\t"                                                                             \
+  "add.u32 n, n, 1;\n\tsetp.lt.u32 q, n, %18;\n\t@q bra WB_KL_WAIT;\n\t"                             \
+  "mov.u32 %0, 1;\n\tbra WB_KL_OUT;\n"                                                               \
+  "WB_KL_GO:\n\t"                                                                                    \
+  "add.u32 ma, %11, s16;\n\tadd.u32 mb, %13, s16;\n\t"
+#define WB_KL_COMMIT2 "@pv tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [pb], mk;\n\t"
+#define WB_KL_COMMIT1 "@pv tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [pb];\n\t"
+// where the ring goes next, and a probe of that stage's full barrier (not past the last k-step)
+#define WB_KL_PROBE                                                                                  \
+  "add.u32 nst, %1, 1;\n\tadd.u32 nfb, fb, 8;\n\tadd.u32 neb, eb, 8;\n\tadd.u32 ns16, s16, %14;\n\tmov.u32 nph, %2;\n\t" \
+  "setp.eq.u32 w, nst, %6;\n\t"                                                                      \
+  "@w mov.u32 nst, 0;\n\t@w mov.u32 nfb, %7;\n\t@w mov.u32 neb, %8;\n\t@w mov.u32 ns16, 0;\n\t@w xor.b32 nph, nph, 1;\n\t" \
+  "setp.eq.u32 pr, 1, 0;\n\tsetp.gt.u32 pm, %3, 1;\n\t"                                              \
+  "@pm mbarrier.test_wait.parity.shared::cta.b64 pr, [nfb], nph;\n\t"
+#define WB_KL_TAIL(COMMIT)                                                                           \
+  "setp.eq.u32 pa, 0, 0;\n\tmov.u32 %4, 1;\n\t"                                                      \
+  "mov.u32 pb, eb;\n\tsetp.ne.u32 pv, %5, 0;\n\t"                                                    \
+  "mov.u32 %1, nst;\n\tmov.u32 fb, nfb;\n\tmov.u32 eb, neb;\n\tmov.u32 s16, ns16;\n\tmov.u32 %2, nph;\n\t" \
+  "sub.u32 %3, %3, 1;\n\tsetp.ne.u32 c, %3, 0;\n\t@c bra WB_KL_LOOP;\n"                              \
+  "WB_KL_OUT:\n\t"                                                                                   \
+  COMMIT                                                                                             \
+  "}"
+// one k-step's MMAs for one atom (REPS == 1) or two stacked atoms (REPS == 2)
+#define WB_KL_STEP1(G, COMMIT)                                                                       \
+  WB_KL_MMA(G, "%9", "ma", "mb", "pa") COMMIT WB_KL_MMA_J(G, "%9", "ma", "2", "pt") WB_KL_PROBE     \
+  WB_KL_MMA_J(G, "%9", "ma", "4", "pt") WB_KL_MMA_J(G, "%9", "ma", "6", "pt")
+#define WB_KL_STEP2(G, COMMIT)                                                                       \
+  WB_KL_MMA(G, "%9", "ma", "mb", "pa") COMMIT WB_KL_MMA_J(G, "%9", "ma", "2", "pt")                 \
+  WB_KL_MMA_J(G, "%9", "ma", "4", "pt") WB_KL_MMA_J(G, "%9", "ma", "6", "pt")                       \
+  "add.u32 a1, ma, %12;\n\t"                                                                         \
+  WB_KL_MMA(G, "d1", "a1", "mb", "pa") WB_KL_MMA_J(G, "d1", "a1", "2", "pt") WB_KL_PROBE            \
+  WB_KL_MMA_J(G, "d1", "a1", "4", "pt") WB_KL_MMA_J(G, "d1", "a1", "6", "pt")
+#define WB_KL_ARGS                                                                                          \
+  : "=r"(status), "+r"(stage), "+r"(phase), "+r"(kleft), "+r"(accumulate)                                   \
+  : "r"(issuer), "r"(depth), "r"(full0), "r"(empty0), "r"(d), "r"(span), "r"(ma_lo0), "r"(atom16), "r"(mb_lo0), \
+    "r"(step16), "r"(debug), "r"(hi), "r"(idesc), "r"(limit)                                                \
+  : "memory"
+
+template <int CG, int REPS>
+WB_DEV uint32_t mma_k_loop(uint32_t issuer, uint32_t& kleft, uint32_t depth, uint32_t& stage, uint32_t& phase, uint32_t& accumulate,
+                           uint32_t full0, uint32_t empty0, uint32_t d, uint32_t span, uint32_t ma_lo0, uint32_t atom16, uint32_t mb_lo0,
+                           uint32_t step16, uint32_t hi, uint32_t idesc, uint32_t limit, uint32_t debug = 0) {
+  uint32_t status;
+  if constexpr (CG == 2 && REPS == 1) asm volatile(WB_KL_HEAD WB_KL_STEP1("2", WB_KL_COMMIT2) WB_KL_TAIL(WB_KL_COMMIT2) WB_KL_ARGS);
+  if constexpr (CG == 2 && REPS == 2) asm volatile(WB_KL_HEAD WB_KL_STEP2("2", WB_KL_COMMIT2) WB_KL_TAIL(WB_KL_COMMIT2) WB_KL_ARGS);
+  if constexpr (CG == 1 && REPS == 1) asm volatile(WB_KL_HEAD WB_KL_STEP1("1", WB_KL_COMMIT1) WB_KL_TAIL(WB_KL_COMMIT1) WB_KL_ARGS);
+  if constexpr (CG == 1 && REPS == 2) asm volatile(WB_KL_HEAD WB_KL_STEP2("1", WB_KL_COMMIT1) WB_KL_TAIL(WB_KL_COMMIT1) WB_KL_ARGS);
+  return status;
+}
+
+// Producer: for each of `kleft` k-steps wait empty[stage], (pair leader) state the pair's bytes
+// on its own full[stage], then load the A half-tile and the B^T tile of k column x into the
+// stage's slot, both completing on full_remote0 + 8*stage (the pair leader's barrier).
+template <int CG>
+WB_DEV uint32_t load_k_loop(uint32_t issuer, uint32_t& kleft, uint32_t depth, uint32_t& stage, uint32_t& phase, int& x, uint32_t empty0,
+                            uint32_t full0, uint32_t full_remote0, uint32_t is_leader, uint32_t tx, uint32_t ring, uint32_t stage_bytes,
+                            uint32_t a_bytes, const void* map_a, int a_row, const void* map_b, int col, uint32_t limit, uint32_t debug = 0) {
+  uint32_t status;
+#define WB_LD_BODY(CGQ)                                                                                          \
+  "{\n\t.reg .pred e, ei, pl, pn, p, q, w, c;\n\t.reg .b32 n, eb, fl, fr, sa, sb, par, dbg;\n\t"                 \
+  "setp.ne.u32 ei, %5, 0;\n\tand.b32 dbg, %19, 1;\n\tsetp.eq.and.u32 e, dbg, 0, ei;\n\t"                          \
+  "setp.ne.and.u32 pl, %10, 0, e;\n\tsetp.ne.and.u32 pn, %10, 0, ei;\n\tsetp.ne.and.u32 pn, dbg, 0, pn;\n\tmov.u32 %0, 0;\n\t" \
+  "mad.lo.u32 eb, %1, 8, %7;\n\tmad.lo.u32 fl, %1, 8, %8;\n\tmad.lo.u32 fr, %1, 8, %9;\n\tmad.lo.u32 sa, %1, %13, %12;\n" \
+  "WB_LD_LOOP:\n\tmov.u32 n, 0;\n\txor.b32 par, %2, 1;\n"                                                        \
+  "WB_LD_WAIT:\n\t"                                                                                              \
+  "mbarrier.test_wait.parity.shared::cta.b64 p, [eb], par;\n\t"                                                  \
+  "@p bra WB_LD_GO;\n\t"                                                                                         \
+  "add.u32 n, n, 1;\n\tsetp.lt.u32 q, n, %20;\n\t@q bra WB_LD_WAIT;\n\t"                                         \
+  "mov.u32 %0, 1;\n\tbra WB_LD_OUT;\n"                                                                           \
+  "WB_LD_GO:\n\t"                                                                                                \
+  "@pl mbarrier.arrive.expect_tx.shared::cta.b64 _, [fl], %11;\n\t"                                              \
+  "@pn mbarrier.arrive.shared::cta.b64 _, [fl];\n\t"                                                             \
+  "add.u32 sb, sa, %14;\n\t"                                                                                     \
+  "@e cp.async.bulk.tensor.2d" CGQ ".shared::cluster.global.mbarrier::complete_tx::bytes [sa], [%15, {%4, %16}], [fr];\n\t" \
+  "@e cp.async.bulk.tensor.2d" CGQ ".shared::cluster.global.mbarrier::complete_tx::bytes [sb], [%17, {%4, %18}], [fr];\n\t" \
+  "add.s32 %4, %4, 64;\n\tadd.u32 %1, %1, 1;\n\tadd.u32 eb, eb, 8;\n\tadd.u32 fl, fl, 8;\n\tadd.u32 fr, fr, 8;\n\tadd.u32 sa, sa, %13;\n\t" \
+  "setp.eq.u32 w, %1, %6;\n\t"                                                                                   \
+  "@w mov.u32 %1, 0;\n\t@w mov.u32 eb, %7;\n\t@w mov.u32 fl, %8;\n\t@w mov.u32 fr, %9;\n\t@w mov.u32 sa, %12;\n\t@w xor.b32 %2, %2, 1;\n\t" \
+  "sub.u32 %3, %3, 1;\n\tsetp.ne.u32 c, %3, 0;\n\t@c bra WB_LD_LOOP;\n"                                          \
+  "WB_LD_OUT:\n\t}"
+#define WB_LD_ARGS                                                                                               \
+  : "=r"(status), "+r"(stage), "+r"(phase), "+r"(kleft), "+r"(x)                                                 \
+  : "r"(issuer), "r"(depth), "r"(empty0), "r"(full0), "r"(full_remote0), "r"(is_leader), "r"(tx), "r"(ring), "r"(stage_bytes), \
+    "r"(a_bytes), "l"(reinterpret_cast<uint64_t>(map_a)), "r"(a_row), "l"(reinterpret_cast<uint64_t>(map_b)), "r"(col), "r"(debug), "r"(limit) \
+  : "memory"
+  if constexpr (CG == 2) asm volatile(WB_LD_BODY(".cta_group::2") WB_LD_ARGS);
+  else asm volatile(WB_LD_BODY("") WB_LD_ARGS);
+#undef WB_LD_BODY
+#undef WB_LD_ARGS
+  return status;
+}
+
 // ---------------------------------------------------------------- cluster launch control
 // Ask the hardware to cancel a not-yet-launched cluster of this grid; the 16-byte
 // answer lands in this CTA's shared memory and completes 16 bytes on `bar`.

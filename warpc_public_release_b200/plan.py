@@ -49,11 +49,22 @@ class _Base:
         """Phase stamps of the last launches: array [grid, 32 events, 4 tiles]; events 11-14 and 16-20 are cycle sums of GPU-timer nanoseconds (0 = not reached)."""
         import numpy as np
         grid = self.info().grid
-        buf = (ctypes.c_ulonglong * (grid * 128))()
-        r = _lib.lib().wg_plan_read_stamps(self._h, buf, grid * 128)
+        buf = (ctypes.c_ulonglong * (grid * 256))()
+        r = _lib.lib().wg_plan_read_stamps(self._h, buf, grid * 256)
         if r < 0:
             check(r, "wg_plan_read_stamps")
-        return np.frombuffer(buf, dtype=np.uint64).reshape(grid, 32, 4).copy()
+        return np.frombuffer(buf, dtype=np.uint64).reshape(grid, 64, 4)[:, :32, :].copy()
+
+    def read_stage_traces(self):
+        """Per-stage SM-cycle traces of each CTA's first tile: array [grid, 4, 32] -- producer saw
+        the slot empty, producer issued, MMA warp saw it full, MMA warp issued (0 = not reached)."""
+        import numpy as np
+        grid = self.info().grid
+        buf = (ctypes.c_ulonglong * (grid * 256))()
+        r = _lib.lib().wg_plan_read_stamps(self._h, buf, grid * 256)
+        if r < 0:
+            check(r, "wg_plan_read_stamps")
+        return np.frombuffer(buf, dtype=np.uint64).reshape(grid, 256)[:, 128:].reshape(grid, 4, 32).copy()
 
     def status(self):
         """Synchronise and raise DeviceWaitError if any launch gave up."""
@@ -66,6 +77,9 @@ class _Base:
 
     def debug_set_flag(self, index, value):
         check(_lib.lib().wg_plan_debug_set_flag(self._h, int(index), int(value)), "wg_plan_debug_set_flag")
+
+    def debug_set_mode(self, flags):
+        check(_lib.lib().wg_plan_debug_set_mode(self._h, int(flags)), "wg_plan_debug_set_mode")
 
     def reset(self):
         check(_lib.lib().wg_plan_reset(self._h), "wg_plan_reset")

@@ -54,10 +54,10 @@ def variant_from_header(hdr, m, n, k):
     if name.startswith("pair_"):
         return programs.pair(m, n, k, int(name.rsplit("_s", 1)[1]))
     chosen = programs.choose(m, n, k)
-    tm, tn, _ = map(int, hdr["tile"].split())
+    if launch_header.parse_header(programs.header(chosen, m, n, k))["kernel"] == name:
+        return chosen  # the rule's own program for this shape
+    tm, tn = (int(x) for x in name.rsplit("_", 2)[1].split("x"))
     depth = int(name.rsplit("_s", 1)[1])
-    if (chosen.tile_m, chosen.tile_n, chosen.depth) == (tm, tn, depth):
-        return chosen
     return programs.swapped(m, n, k, tm, tn, depth, direct=launch_header.parameter(hdr, "c")["kind"] == "ptr",
                             clc=int(hdr["grid"].split()[0]) > 148)
 
