@@ -124,7 +124,9 @@ int wg_plan_read_stamps(void* plan, unsigned long long* out, size_t cap_words);
 int wg_plan_debug_set_flag(void* plan, int index, unsigned value);
 
 /* Timing experiments only (no reference counterpart): bit 0 = load nothing, bit 1 = issue no
- * MMAs; barriers and the ring still cycle, results are meaningless. */
+ * MMAs; barriers and the ring still cycle, results are meaningless.  Bits 8-11: k-steps the
+ * ring hands over per barrier round in the launches that follow (1, 2 or 4; results stay
+ * exact), 0 = the library's own choice. */
 int wg_plan_debug_set_mode(void* plan, unsigned flags);
 
 /* Where CTA tile index `tile` sits in C under a launch's tile walk (backend/tiles.ml:32-80). */

@@ -23,7 +23,7 @@ template <class C>
 wb_kernel_entry entry(int id, const char* name) {
   wb_kernel_entry e;
   e.id = id, e.cg = C::CG, e.tile_m = C::TM, e.tile_n = C::TN, e.direct = C::DIRECT ? 1 : 0;
-  e.epi_rows = C::EPI_ROWS, e.ncols = C::NCOLS, e.stage_bytes = C::STAGE_BYTES;
+  e.reps = C::REPS, e.epi_rows = C::EPI_ROWS, e.wide_rows = C::WIDE_ROWS, e.ncols = C::NCOLS, e.stage_bytes = C::STAGE_BYTES;
   e.smem_fixed = C::smem_bytes(0);
   e.name = name;
   e.fn = reinterpret_cast<const void*>(&gemm_kernel<C>);
@@ -88,12 +88,22 @@ int encode_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem, const void* pt
   return r == CUDA_SUCCESS ? WG_OK : int(r);
 }
 
+// How many k-steps the ring hands over at a time (one full and one empty barrier a round): one
+// k-step's barrier round costs the issuing thread more than four narrow MMAs take to run, so
+// the slots of the N = 128 tiles go in fours (16 KB) or pairs (24 KB); larger slots keep a round per
+// k-step, where handing over 64 KB at a time would leave the producer too little slack.
+void set_rounds(KParams& p, const wb_kernel_entry* k, int depth) {
+  int ksub = (k->reps != 1 || k->stage_bytes > 24 * 1024) ? 1 : (k->stage_bytes <= 16 * 1024 ? 4 : 2);
+  while (ksub > 1 && depth / ksub < 2) ksub /= 2;
+  p.ksub = ksub, p.rounds = depth / ksub;
+}
+
 struct Plan {
   int device = 0;
   wg_variant v;
   wg_launch_info li;
   const wb_kernel_entry* k = nullptr;
-  CUtensorMap map_a, map_b, map_c;
+  CUtensorMap map_a, map_b, map_c, map_cw;
   KParams p;
   uint32_t* d_flags = nullptr;
   uint32_t* d_status = nullptr;
@@ -122,9 +132,11 @@ int fill_plan(Plan* pl, int device, const wg_variant* v, int M, int N, int K, co
   pl->k = wb_kernel_at(li.kernel_id);
   WG_CUDA(cudaSetDevice(device));
   std::memset(&pl->map_c, 0, sizeof pl->map_c);
+  std::memset(&pl->map_cw, 0, sizeof pl->map_cw);
   if ((r = encode_2d(&pl->map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, dA, M, K, li.a_box_rows, 64)) != WG_OK) return r;
   if ((r = encode_2d(&pl->map_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, dBt, N, K, li.bt_box_rows, 64)) != WG_OK) return r;
   if (!li.direct && (r = encode_2d(&pl->map_c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dC, M, N, li.c_box_rows, 32, CU_TENSOR_MAP_SWIZZLE_NONE)) != WG_OK) return r;
+  if (!li.direct && (r = encode_2d(&pl->map_cw, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dC, M, N, pl->k->wide_rows, 32, CU_TENSOR_MAP_SWIZZLE_NONE)) != WG_OK) return r;
   pl->flag_bytes = size_t(li.nflags > 0 ? li.nflags : 1) * sizeof(uint32_t);
   WG_CUDA(cudaMalloc(&pl->d_flags, pl->flag_bytes));
   WG_CUDA(cudaMalloc(&pl->d_status, 8 * sizeof(uint32_t)));
@@ -141,6 +153,8 @@ int fill_plan(Plan* pl, int device, const wg_variant* v, int M, int N, int K, co
   p.serp = li.serpentine;
   p.depth = li.depth, p.nbuf = li.nbuf, p.sched = li.sched, p.ask_ahead = li.ask_ahead;
   p.split = li.split;
+  set_rounds(p, pl->k, li.depth);
+  p.epi_ring = (!li.direct && size_t(li.depth) * size_t(pl->k->stage_bytes) >= size_t(li.tile_m) * size_t(li.tile_n) * 4) ? 1 : 0;
   if (li.sched == SCHED_STREAMK) {
     const int clusters = li.grid / li.cluster, units = (p.ntiles / li.cluster) * p.kt;
     p.sk_clusters = clusters, p.sk_q = units / clusters, p.sk_r = units % clusters;
@@ -240,7 +254,7 @@ extern "C" int wg_launch(void* plan, void* cuda_stream) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  void* args[4] = {&pl->map_a, &pl->map_b, &pl->map_c, &pl->p};
+  void* args[5] = {&pl->map_a, &pl->map_b, &pl->map_c, &pl->map_cw, &pl->p};
   return int(cudaLaunchKernelExC(&cfg, pl->k->fn, args));
 }
 
@@ -409,17 +423,21 @@ extern "C" int wg_launch_noalloc(int device, const wg_variant* v, int M, int N, 
   if ((r = noalloc_setup(device, &scratch)) != WG_OK) return r;
   WG_CUDA(cudaSetDevice(device));
   const wb_kernel_entry* k = wb_kernel_at(li.kernel_id);
-  CUtensorMap map_a, map_b, map_c;
+  CUtensorMap map_a, map_b, map_c, map_cw;
   std::memset(&map_c, 0, sizeof map_c);
+  std::memset(&map_cw, 0, sizeof map_cw);
   if ((r = encode_2d(&map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, dA, M, K, li.a_box_rows, 64)) != WG_OK) return r;
   if ((r = encode_2d(&map_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, dBt, N, K, li.bt_box_rows, 64)) != WG_OK) return r;
   if (!li.direct && (r = encode_2d(&map_c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dC, M, N, li.c_box_rows, 32, CU_TENSOR_MAP_SWIZZLE_NONE)) != WG_OK) return r;
+  if (!li.direct && (r = encode_2d(&map_cw, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dC, M, N, k->wide_rows, 32, CU_TENSOR_MAP_SWIZZLE_NONE)) != WG_OK) return r;
   KParams p;
   std::memset(&p, 0, sizeof p);
   p.M = M, p.N = N, p.K = K, p.kt = K / 64;
   p.ntiles = ((M + li.tile_m - 1) / li.tile_m) * ((N + li.tile_n - 1) / li.tile_n);
   p.cl_n = li.cl_n > 0 ? li.cl_n : 1, p.group = li.group > 0 ? li.group : 1, p.serp = li.serpentine;
   p.depth = li.depth, p.nbuf = li.nbuf, p.sched = li.sched, p.ask_ahead = li.ask_ahead, p.split = li.split;
+  set_rounds(p, k, li.depth);
+  p.epi_ring = (!li.direct && size_t(li.depth) * size_t(k->stage_bytes) >= size_t(li.tile_m) * size_t(li.tile_n) * 4) ? 1 : 0;
   if (li.sched == SCHED_STREAMK) {
     const int clusters = li.grid / li.cluster, units = (p.ntiles / li.cluster) * p.kt;
     p.sk_clusters = clusters, p.sk_q = units / clusters, p.sk_r = units % clusters;
@@ -446,7 +464,7 @@ extern "C" int wg_launch_noalloc(int device, const wg_variant* v, int M, int N, 
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  void* args[4] = {&map_a, &map_b, &map_c, &p};
+  void* args[5] = {&map_a, &map_b, &map_c, &map_cw, &p};
   return int(cudaLaunchKernelExC(&cfg, k->fn, args));
 }
 
@@ -468,6 +486,11 @@ extern "C" int wg_noalloc_status(int device, unsigned out[4]) {
 extern "C" int wg_plan_debug_set_mode(void* plan, unsigned flags) {
   Plan* pl = static_cast<Plan*>(plan);
   if (!pl) return WG_E_ARG;
-  pl->p.debug = flags;
+  pl->p.debug = flags & 0xffu;
+  // bits 8-11: k-steps a barrier round (1, 2 or 4) for the launches that follow; 0 = the library's choice
+  const int ksub = int((flags >> 8) & 0xfu);
+  if (ksub == 0) set_rounds(pl->p, pl->k, pl->p.depth);
+  else if ((ksub == 1 || ((ksub == 2 || ksub == 4) && pl->k->reps == 1)) && pl->p.depth / ksub >= 2) pl->p.ksub = ksub, pl->p.rounds = pl->p.depth / ksub;
+  else return WG_E_ARG;
   return WG_OK;
 }

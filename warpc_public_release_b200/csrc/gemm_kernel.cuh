@@ -52,6 +52,8 @@ struct KParams {
   int ask_ahead;  // probe the next stage before releasing this one
   int split;      // SCHED_SPLITK: runs of K per tile
   int sk_q, sk_r, sk_clusters;  // SCHED_STREAMK: units = q * clusters + r
+  int ksub, rounds;             // the ring is handed over `ksub` k-steps (slots) at a time: rounds = depth / ksub barrier pairs
+  int epi_ring;                 // the ring holds a whole C tile: a CTA's last tile is staged there, one copy per block
   float* C;                     // direct store
   uint32_t* flags;              // split-K / stream-K hand-off words
   uint32_t* status;             // 8 words: [0] code, [1] site detail, [2] CTA, [3] parity/stage
@@ -82,10 +84,13 @@ struct Cfg {
   static constexpr int STAGING_BYTES = DIRECT ? 0 : 4 * EPI_COPIES * EPI_COPY_BYTES;
   static constexpr int CHUNKS = SPAN / EPI_ROWS;  // blocks per atom per warp
   static constexpr int NBLK = REPS * CHUNKS;
+  // a CTA's last tile goes out in stores of WIDE_ROWS rows, from copies side by side in the drained ring
+  static constexpr int WIDE_ROWS = DIRECT ? 32 : ((SPAN % 128 == 0) ? 128 : 64);
+  static constexpr int WIDE_BLKS = WIDE_ROWS / EPI_ROWS;
   static constexpr int MAX_DEPTH = 16;
   static constexpr int CTRL_BYTES = 512;
   static_assert(A_BYTES % 1024 == 0 && B_BYTES % 1024 == 0, "ring slots keep the 1024-byte swizzle atom alignment");
-  static_assert(SPAN % EPI_ROWS == 0, "whole epilogue blocks");
+  static_assert(SPAN % EPI_ROWS == 0 && SPAN % WIDE_ROWS == 0 && WIDE_ROWS % EPI_ROWS == 0, "whole epilogue blocks");
   static_assert((MMA_M == 128 && MMA_N % 16 == 0) || (MMA_M == 256 && MMA_N % 16 == 0), "UMMA shape");
   // kind::f16 instruction descriptor: f32 accumulator, f16 operands, both K-major
   static constexpr uint32_t IDESC = (1u << 4) | (uint32_t(MMA_N >> 3) << 17) | (uint32_t(MMA_M >> 4) << 24);
@@ -204,7 +209,7 @@ struct Work {
 };
 
 // The sequence of work units a CTA walks; every role of the CTA walks the same one.
-template <class C, bool WARP = true>
+template <class C>
 struct Walker {
   const KParams& p;
   uint32_t abort_addr, sched_full, sched_slot, sched_empty_first;  // shared addresses (the last in the first CTA)
@@ -220,6 +225,8 @@ struct Walker {
     sched_empty_first = mapa(ctrl_addr + offsetof(Ctrl, sched_empty), 0);
   }
 
+  // WARP: called by a whole converged warp, else by one lane running its role alone
+  template <bool WARP = true>
   WB_DEV bool next(Work& w) {
     const int sched = p.sched;
     if (!started) {
@@ -271,6 +278,16 @@ struct Walker {
     w.ke = (seg == t_last) ? ke_last : p.kt;
     return true;
   }
+
+  // `w` (the unit next() gave last) is known to be this CTA's final one.  Cluster launch
+  // control only learns that from the answer after it, so it never says yes.
+  WB_DEV bool is_last(const Work& w) const {
+    const int sched = p.sched;
+    if (sched == SCHED_ONE || sched == SCHED_SPLITK) return true;
+    if (sched == SCHED_STRIDE) return w.tile + int(gridDim.x) >= p.ntiles;
+    if (sched == SCHED_STREAMK) return seg == t_first;
+    return false;
+  }
 };
 
 template <class C>
@@ -304,10 +321,12 @@ WB_DEV void epi_coords(int row, int col, int q, int i, int& y, int& x) {
 // One tile's accumulator out through the staging copies: each block loaded from tensor
 // memory while the block before it is staged and handed to the copy engine.  `add` selects
 // the reducing store (C += block, performed in the L2).  The accumulator is released on the
-// leader's barrier as soon as the last block is in registers.
+// leader's barrier as soon as the last block is in registers.  When the tile is the CTA's last
+// and the operand ring (idle once the tile's accumulator is complete: every MMA that read it
+// has retired) can hold it, every block gets a copy of its own there and no store is waited for.
 template <class C>
-WB_DEV void epi_staged_tile(const CUtensorMap* map_c, uint32_t tbase, uint32_t my_staging, int row, int col, int q, uint32_t lane,
-                            bool add, uint32_t acc_empty_addr, unsigned long long* prof = nullptr) {
+WB_DEV void epi_staged_tile(const CUtensorMap* map_c, const CUtensorMap* map_cw, uint32_t tbase, uint32_t my_staging, int row, int col, int q, uint32_t lane,
+                            bool add, uint32_t acc_empty_addr, uint32_t wide = 0, unsigned long long* prof = nullptr) {
   uint32_t v[2][C::EPI_ROWS];
   long long t_ld = 0, t_copy = 0, t_sts = 0, t_tma = 0, t0 = 0;
   epi_load<C>(tbase, 0, v[0]);
@@ -326,10 +345,13 @@ WB_DEV void epi_staged_tile(const CUtensorMap* map_c, uint32_t tbase, uint32_t m
     }
     int y, x;
     epi_coords<C>(row, col, q, i, y, x);
-    const uint32_t copy = my_staging + uint32_t(i % C::EPI_COPIES) * C::EPI_COPY_BYTES;
+    // `wide` != 0: this warp's NBLK private copies in the drained ring, nothing to wait for
+    const uint32_t copy = wide != 0u ? wide + uint32_t(i) * C::EPI_COPY_BYTES : my_staging + uint32_t(i % C::EPI_COPIES) * C::EPI_COPY_BYTES;
     if (prof) t0 = clock64();
-    bulk_wait_read<C::EPI_COPIES - 1>();  // the store that last read this copy is done with it (only the issuing lane has groups)
-    __syncwarp();
+    if (wide == 0u) {
+      bulk_wait_read<C::EPI_COPIES - 1>();  // the store that last read this copy is done with it (only the issuing lane has groups)
+      __syncwarp();
+    }
     if (prof) t_copy += clock64() - t0, t0 = clock64();
     // register j is one C row: the warp's 32 lanes write its 128 bytes side by side (no bank
     // conflict, so the staging box needs no swizzle)
@@ -339,7 +361,13 @@ WB_DEV void epi_staged_tile(const CUtensorMap* map_c, uint32_t tbase, uint32_t m
     fence_proxy_async_smem();
     __syncwarp();
     if (prof) t_sts += clock64() - t0, t0 = clock64();
-    tma_store_commit_if(lane == 0 ? 1u : 0u, add ? 1u : 0u, map_c, x, y, copy);
+    if (wide == 0u) {
+      tma_store_commit_if(lane == 0 ? 1u : 0u, add ? 1u : 0u, map_c, x, y, copy);
+    } else if ((i + 1) % C::WIDE_BLKS == 0) {
+      // the last WIDE_BLKS blocks are WIDE_ROWS consecutive rows of C and of the ring: one store
+      tma_store_commit_if(lane == 0 ? 1u : 0u, add ? 1u : 0u, map_cw, x, y - (C::WIDE_BLKS - 1) * C::EPI_ROWS,
+                          copy - uint32_t(C::WIDE_BLKS - 1) * C::EPI_COPY_BYTES);
+    }
     if (prof) t_tma += clock64() - t0;
   }
   if (prof && lane == 0) prof[0] = t_ld, prof[4] = t_copy, prof[8] = t_sts, prof[12] = t_tma;
@@ -375,7 +403,8 @@ WB_DEV void epi_direct_tile(const KParams& p, uint32_t tbase, int row, int col, 
 template <class C>
 __global__ void __launch_bounds__(256, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-            const __grid_constant__ CUtensorMap map_c, const __grid_constant__ KParams p) {
+            const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_cw,
+            const __grid_constant__ KParams p) {
   constexpr int CG = C::CG;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -392,7 +421,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   const uint32_t rank = (CG == 2) ? warp_uniform(cluster_ctarank()) : 0u;
   const bool leader = (rank == 0);
   const uint32_t issuer = (lane == 0) ? 1u : 0u;  // the lane that issues its warp's single-lane instructions
-  const int depth = p.depth, nbuf = p.nbuf;
+  const int depth = p.depth, nbuf = p.nbuf, rounds = p.rounds, ksub = p.ksub;
+  const long long cycles_at_entry = clock64();
   if (threadIdx.x == 0) stamp(p, EV_ENTRY, 0);
 
   auto full_bar = [&](int s) { return ctrl_at(offsetof(Ctrl, full) + 8 * s); };
@@ -401,23 +431,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   auto acc_empty_bar = [&](int b) { return ctrl_at(offsetof(Ctrl, acc_empty) + 8 * b); };
 
   // ---------------------------------------------------------------- set-up
-  if (warp == 3 && lane == 0) {
-    prefetch_tmap(&map_a);
-    prefetch_tmap(&map_b);
-    if constexpr (!C::DIRECT) prefetch_tmap(&map_c);
-    for (int s = 0; s < depth; ++s) {
-      mbar_init(full_bar(s), 1);   // the leader's one arrival stating the pair's bytes
-      mbar_init(empty_bar(s), 1);  // one commit from the MMA warp
+  if (warp == 3) {
+    // one barrier (or pair of them) a lane, so the set-up is one instruction deep, not forty
+    if (int(lane) < rounds) {
+      mbar_init(full_bar(int(lane)), 1);   // the leader's one arrival stating the pair's bytes
+      mbar_init(empty_bar(int(lane)), 1);  // one commit from the MMA warp
+    } else if (lane == 16 || lane == 17) {
+      mbar_init(acc_full_bar(int(lane) - 16), 1);        // one commit
+      mbar_init(acc_empty_bar(int(lane) - 16), 4 * CG);  // every epilogue warp of the pair
+    } else if (lane == 18) {
+      mbar_init(ctrl_at(offsetof(Ctrl, clc_bar)), 1);
+      mbar_init(ctrl_at(offsetof(Ctrl, sched_full)), 1);
+      // takers of an answer: a producer a CTA, the leader's MMA warp, four epilogue warps a CTA
+      mbar_init(ctrl_at(offsetof(Ctrl, sched_empty)), CG + 1 + 4 * CG);
+      st_shared_u32(abort_addr, 0u);
+    } else if (lane == 19) {
+      prefetch_tmap(&map_a);
+      prefetch_tmap(&map_b);
+      if constexpr (!C::DIRECT) prefetch_tmap(&map_c), prefetch_tmap(&map_cw);
     }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(acc_full_bar(b), 1);        // one commit
-      mbar_init(acc_empty_bar(b), 4 * CG);  // every epilogue warp of the pair
-    }
-    mbar_init(ctrl_at(offsetof(Ctrl, clc_bar)), 1);
-    mbar_init(ctrl_at(offsetof(Ctrl, sched_full)), 1);
-    // takers of an answer: a producer a CTA, the leader's MMA warp, four epilogue warps a CTA
-    mbar_init(ctrl_at(offsetof(Ctrl, sched_empty)), CG + 1 + 4 * CG);
-    st_shared_u32(abort_addr, 0u);
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -425,6 +457,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     tmem_alloc<CG>(ctrl_at(offsetof(Ctrl, tmem_base)), uint32_t(C::pow2_ge(C::NCOLS * nbuf)));
     tmem_relinquish<CG>();
   }
+  // every role's first unit of work and its tile's origin, found while the barriers and the
+  // tensor memory are being set up rather than after the CTAs have met
+  Walker<C> walk(p, ctrl, rank, lane);
+  Work w;
+  bool have = walk.template next<true>(w);
+  int row = 0, col = 0;
+  if (have) tile_origin<C>(p, w.tile, row, col);
   tc_fence_before();
   if constexpr (CG == 2) {
     cluster_arrive();
@@ -437,29 +476,37 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   if (threadIdx.x == 0) stamp(p, EV_SETUP, 0);
 
   // ---------------------------------------------------------------- roles
+  bool arrived = false;  // this warp has already arrived at the teardown's cluster barrier
   if (warp == 0) {
     // ===== producer: TMA loads into this CTA's ring, counted on the leader's barrier.  One lane
     // runs the role; a tile's k-steps are one asm loop (load_k_loop), re-entered after the bounded,
     // timed wait whenever a slot stayed taken beyond the loop's own poll limit.
     if (lane == 0) {
-      Walker<C, false> walk(p, ctrl, rank, lane);
-      Work w;
       uint32_t stage = 0, phase = 0;
       int nth = 0;
       bool ok = true;
       const uint32_t full_leader0 = (CG == 2) ? mapa(full_bar(0), 0) : full_bar(0);
-      while (ok && walk.next(w)) {
-        int row, col;
-        tile_origin<C>(p, w.tile, row, col);
+      for (; ok && have; have = ok && walk.template next<false>(w)) {
+        if (nth != 0) tile_origin<C>(p, w.tile, row, col);
         // a pair's CTAs sit side by side: same rows, so they split the A tile between them
         const int a_row = row + int(rank) * C::A_ROWS;
         uint32_t kleft = uint32_t(w.ke - w.kb);
         int x = w.kb * C::TK;
         stamp(p, EV_LOAD_FIRST, nth);
         while (kleft != 0u) {
-          if (load_k_loop<CG>(1u, kleft, uint32_t(depth), stage, phase, x, empty_bar(0), full_bar(0), full_leader0, leader ? 1u : 0u,
-                              C::TX_BYTES, ring, uint32_t(C::STAGE_BYTES), uint32_t(C::A_BYTES), &map_a, a_row, &map_b, col, 1u << 14, p.debug) != 0u &&
-              !wait_bar<false, false>(p, abort_addr, empty_bar(int(stage)), phase ^ 1u, ST_WAIT_EMPTY, stage)) {
+          uint32_t gave_up;
+          if (ksub == 2)
+            gave_up = load_rounds<CG, 2>(1u, kleft, uint32_t(rounds), stage, phase, x, empty_bar(0), full_bar(0), full_leader0, leader ? 1u : 0u,
+                                         C::TX_BYTES, ring, 2u * C::STAGE_BYTES, uint32_t(C::A_BYTES), &map_a, a_row, &map_b, col, 1u << 14, p.debug,
+                                         uint32_t(C::STAGE_BYTES));
+          else if (ksub == 4)
+            gave_up = load_rounds<CG, 4>(1u, kleft, uint32_t(rounds), stage, phase, x, empty_bar(0), full_bar(0), full_leader0, leader ? 1u : 0u,
+                                         C::TX_BYTES, ring, 4u * C::STAGE_BYTES, uint32_t(C::A_BYTES), &map_a, a_row, &map_b, col, 1u << 14, p.debug,
+                                         uint32_t(C::STAGE_BYTES));
+          else
+            gave_up = load_k_loop<CG>(1u, kleft, uint32_t(rounds), stage, phase, x, empty_bar(0), full_bar(0), full_leader0, leader ? 1u : 0u,
+                                      C::TX_BYTES, ring, uint32_t(C::STAGE_BYTES), uint32_t(C::A_BYTES), &map_a, a_row, &map_b, col, 1u << 14, p.debug);
+          if (gave_up != 0u && !wait_bar<false, false>(p, abort_addr, empty_bar(int(stage)), phase ^ 1u, ST_WAIT_EMPTY, stage)) {
             ok = false;
             break;
           }
@@ -468,9 +515,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         ++nth;
       }
       // every stage this CTA filled has been released before it leaves
-      for (int i = 0; ok && i < depth; ++i) {
+      for (int i = 0; ok && i < rounds; ++i) {
         ok = wait_bar<false, false>(p, abort_addr, empty_bar(int(stage)), phase ^ 1u, ST_WAIT_EMPTY, 0x100u + stage);
-        if (++stage == uint32_t(depth)) stage = 0, phase ^= 1u;
+        if (++stage == uint32_t(rounds)) stage = 0, phase ^= 1u;
       }
     }
     __syncwarp();
@@ -478,8 +525,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     // ===== MMA issuer: one lane of the pair leader's warp 1 issues for both CTAs; a tile's
     // k-steps are one asm loop (mma_k_loop): wait full[s], REPS x 4 MMAs, commit to empty[s].
     if (leader && lane == 0) {
-      Walker<C, false> walk(p, ctrl, rank, lane);
-      Work w;
       uint32_t stage = 0, phase = 0, acc_phase = 0;
       int acc = 0, nth = 0;
       bool ok = true;
@@ -491,7 +536,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       constexpr uint32_t STAGE16 = C::STAGE_BYTES >> 4, ATOM16 = uint32_t((C::MMA_M / CG) * 128) >> 4;
       const uint32_t a_lo0 = ((ring & 0x3FFFFu) >> 4) | (1u << 16);  // stage 0's A tile (the MMA's B operand)
       const uint32_t b_lo0 = a_lo0 + (C::A_BYTES >> 4);              // stage 0's B^T tile (the MMA's A operand)
-      while (ok && walk.next(w)) {
+      for (; ok && have; have = ok && walk.template next<false>(w)) {
         if (!wait_bar<false, false>(p, abort_addr, acc_empty_bar(acc), acc_phase ^ 1u, ST_WAIT_ACC_EMPTY, uint32_t(acc))) {
           ok = false;
           break;
@@ -502,9 +547,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         uint32_t kleft = uint32_t(w.ke - w.kb), accumulate = 0;
         stamp(p, EV_MMA_FIRST, nth);
         while (kleft != 0u) {
-          if (mma_k_loop<CG, C::REPS>(1u, kleft, uint32_t(depth), stage, phase, accumulate, full_bar(0), empty_bar(0), d, uint32_t(C::SPAN),
-                                      b_lo0, ATOM16, a_lo0, STAGE16, DESC_HI, C::IDESC, 1u << 14, p.debug) != 0u &&
-              !wait_bar<false, false>(p, abort_addr, full_bar(int(stage)), phase, ST_WAIT_FULL, stage)) {
+          uint32_t gave_up;
+          if (C::REPS == 1 && ksub == 2)
+            gave_up = mma_rounds<CG, 2>(1u, kleft, uint32_t(rounds), stage, phase, accumulate, full_bar(0), empty_bar(0), d, uint32_t(C::SPAN),
+                                        b_lo0, STAGE16, a_lo0, 2u * STAGE16, DESC_HI, C::IDESC, 1u << 14, p.debug);
+          else if (C::REPS == 1 && ksub == 4)
+            gave_up = mma_rounds<CG, 4>(1u, kleft, uint32_t(rounds), stage, phase, accumulate, full_bar(0), empty_bar(0), d, uint32_t(C::SPAN),
+                                        b_lo0, STAGE16, a_lo0, 4u * STAGE16, DESC_HI, C::IDESC, 1u << 14, p.debug);
+          else
+            gave_up = mma_k_loop<CG, C::REPS>(1u, kleft, uint32_t(rounds), stage, phase, accumulate, full_bar(0), empty_bar(0), d, uint32_t(C::SPAN),
+                                              b_lo0, ATOM16, a_lo0, STAGE16, DESC_HI, C::IDESC, 1u << 14, p.debug);
+          if (gave_up != 0u && !wait_bar<false, false>(p, abort_addr, full_bar(int(stage)), phase, ST_WAIT_FULL, stage)) {
             ok = false;
             break;
           }
@@ -559,8 +612,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     // ===== epilogue: tensor memory -> registers -> C
     const int q = int(warp & 3u);
     const bool first_warp = (warp == 4);
-    Walker<C> walk(p, ctrl, rank, lane);
-    Work w;
     int acc = 0, nth = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -578,9 +629,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         if (first_warp && lane == 0) st_relaxed_gpu(p.flags + blockIdx.x, target);
       }
     }
-    while (walk.next(w)) {
-      int row, col;
-      tile_origin<C>(p, w.tile, row, col);
+    for (; have; have = walk.template next<true>(w)) {
+      if (nth != 0) tile_origin<C>(p, w.tile, row, col);
+      const uint32_t wide = (p.epi_ring != 0 && walk.is_last(w)) ? ring + uint32_t(q) * uint32_t(C::NBLK) * C::EPI_COPY_BYTES : 0u;
       const uint32_t tbase = tmem_base + uint32_t(acc * C::NCOLS) + (uint32_t(q * 32) << 16);
       const uint32_t acc_empty_addr = acc_empty_leader + 8u * uint32_t(acc);
       if constexpr (C::DIRECT) {
@@ -594,7 +645,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         if (first_warp && lane == 0) stamp(p, EV_ACC_READY, nth);
         // timing runs: the first warp's cycles in each part of the tile's store, events 11-14
         unsigned long long* prof = (p.stamps != nullptr && first_warp && nth < 4) ? p.stamps + (size_t(blockIdx.x) * 64 + 11) * 4 + nth : nullptr;
-        epi_staged_tile<C>(&map_c, tbase, my_staging, row, col, q, lane, false, acc_empty_addr, prof);
+        epi_staged_tile<C>(&map_c, &map_cw, tbase, my_staging, row, col, q, lane, false, acc_empty_addr, wide, prof);
       } else if (p.sched == SCHED_SPLITK) {
         // ---- split-K over the grid, adding in the L2 (gemm_swapped.ml:660-710).  The S runs
         // of a tile first zero disjoint shares of it (while their k loops run), raise their
@@ -635,7 +686,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         fence_proxy_async_global();
         named_bar_sync(2, 128);
         ok = ok && (ld_shared_u32(abort_addr) == 0u);
-        if (ok) epi_staged_tile<C>(&map_c, tbase, my_staging, row, col, q, lane, true, acc_empty_addr);
+        if (ok) epi_staged_tile<C>(&map_c, &map_cw, tbase, my_staging, row, col, q, lane, true, acc_empty_addr, wide);
       } else {
         // ---- stream-K, adding in the L2 (gemm_swapped.ml:633-659): the segment holding the
         // tile's first k-step stores and raises the tile's flag; the others wait for it and add.
@@ -643,7 +694,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         if (w.kb == 0) {
           ok = wait_bar(p, abort_addr, acc_full_bar(acc), acc_phase, ST_WAIT_ACC_FULL, uint32_t(acc));
           tc_fence_after();
-          if (ok) epi_staged_tile<C>(&map_c, tbase, my_staging, row, col, q, lane, false, acc_empty_addr);
+          if (ok) epi_staged_tile<C>(&map_c, &map_cw, tbase, my_staging, row, col, q, lane, false, acc_empty_addr, wide);
           if (lane == 0) {
             bulk_wait<0>();
             fence_proxy_async_global();
@@ -660,7 +711,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           ok = ok && (ld_shared_u32(abort_addr) == 0u);
           ok = ok && wait_bar(p, abort_addr, acc_full_bar(acc), acc_phase, ST_WAIT_ACC_FULL, uint32_t(acc));
           tc_fence_after();
-          if (ok) epi_staged_tile<C>(&map_c, tbase, my_staging, row, col, q, lane, true, acc_empty_addr);
+          if (ok) epi_staged_tile<C>(&map_c, &map_cw, tbase, my_staging, row, col, q, lane, true, acc_empty_addr, wide);
         }
       }
       if (!ok) break;
@@ -669,6 +720,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       ++nth;
     }
     if constexpr (!C::DIRECT) {
+      // this warp is done with its partner CTA (its last word there was the accumulator's
+      // release): it says so before waiting for its own stores, not after
+      if (CG == 2 && ld_shared_u32(abort_addr) == 0u) {
+        tc_fence_before();
+        cluster_arrive();
+        arrived = true;
+      }
       if (lane == 0) bulk_wait_read<0>();  // the last stores have read their staging copies
       __syncwarp();
     }
@@ -685,7 +743,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   }
   tc_fence_before();
   if constexpr (CG == 2) {
-    cluster_arrive();
+    if (!arrived) cluster_arrive();
     cluster_wait();
   } else {
     __syncthreads();
@@ -694,7 +752,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     tc_fence_after();
     tmem_dealloc<CG>(tmem_base, uint32_t(C::pow2_ge(C::NCOLS * nbuf)));
   }
-  if (threadIdx.x == 0) stamp(p, EV_EXIT, 0);
+  if (threadIdx.x == 0) stamp(p, EV_EXIT, 0), stamp_value(p, 15, 0, clock64() - cycles_at_entry);
 }
 
 }  // namespace wb

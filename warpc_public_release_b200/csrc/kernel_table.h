@@ -6,7 +6,9 @@
 struct wb_kernel_entry {
   int id;
   int cg, tile_m, tile_n, direct;
+  int reps;            // stacked MMA atoms a CTA (2 for 256-column tiles)
   int epi_rows;        // C rows per epilogue block (the C tensor map's box rows)
+  int wide_rows;       // C rows per store of a CTA's last tile, staged whole in the drained ring
   int ncols;           // tensor-memory columns of one accumulator
   int stage_bytes;     // shared memory of one ring stage
   size_t smem_fixed;   // alignment slack + staging + control block

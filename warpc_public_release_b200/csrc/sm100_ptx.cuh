@@ -522,6 +522,138 @@ WB_DEV uint32_t load_k_loop(uint32_t issuer, uint32_t& kleft, uint32_t depth, ui
   return status;
 }
 
+// ---------------------------------------------------------------- k loops in rounds
+// The same two loops with the ring handed over KSUB k-steps at a time: a ROUND is KSUB
+// consecutive slots behind one full and one empty barrier.  One k-step of four MMAs costs its
+// issuing thread about 4 x 64 cycles for the MMAs plus about 360 for the commit, the probe and
+// the ring bookkeeping -- more than the 512 cycles the tensor pipe needs for four N = 256 MMAs
+// (and far more than the 256 of N = 128), so with a barrier round per k-step the issuing thread,
+// not the tensor pipe, sets the pace.  A round of KSUB k-steps pays that overhead once.  A tile
+// (or split-K run) whose k-steps are not a multiple of KSUB ends on a partly used round: the
+// producer states and loads, and the issuer multiplies, only the k-steps that exist.
+// Operands as in mma_k_loop / load_k_loop, with `stage` the round index, `depth` the number of
+// rounds, step16 / stage_bytes the size of a ROUND and slot16 / slot_bytes that of one slot.
+#define WB_KR_MMA(G, D, A, B, PRED, GUARD)                            \
+  "mov.b64 da, {" A ", %16};\n\tmov.b64 db, {" B ", %16};\n\t"        \
+  "@" GUARD " tcgen05.mma.cta_group::" G ".kind::f16 [" D "], da, db, %17, " PRED ";\n\t"
+#define WB_KR_MMA_J(G, A0, B0, J, GUARD) \
+  "add.u32 ta, " A0 ", " J ";\n\tadd.u32 tb, " B0 ", " J ";\n\t" WB_KR_MMA(G, "%9", "ta", "tb", "pt", GUARD)
+// k-step g (>= 1) of the round: its slot's descriptors, four MMAs under the guard for "it exists"
+#define WB_KR_GROUP(G, GUARD)                                                                        \
+  "add.u32 ga, ga, %12;\n\tadd.u32 gb, gb, %12;\n\t"                                                 \
+  WB_KR_MMA(G, "%9", "ga", "gb", "pt", GUARD) WB_KR_MMA_J(G, "ga", "gb", "2", GUARD)                \
+  WB_KR_MMA_J(G, "ga", "gb", "4", GUARD) WB_KR_MMA_J(G, "ga", "gb", "6", GUARD)
+#define WB_KR_HEAD(KSUB)                                                                             \
+  "{\n\t.reg .pred e, e1, e2, e3, ec, p, q, w, pa, pt, c, pr, pv, pm;\n\t"                           \
+  ".reg .b32 n, fb, eb, s16, ta, tb, ga, gb, ma, mb, dbg, pb, nst, nfb, neb, ns16, nph, use;\n\t"    \
+  ".reg .b64 da, db;\n\t.reg .b16 mk;\n\t"                                                           \
+  "setp.ne.u32 ec, %5, 0;\n\tand.b32 dbg, %15, 2;\n\tsetp.eq.and.u32 e, dbg, 0, ec;\n\t"             \
+  "setp.eq.u32 pt, 0, 0;\n\tsetp.ne.u32 pa, %4, 0;\n\tmov.b16 mk, 3;\n\t"                            \
+  "setp.eq.u32 pr, 1, 0;\n\tsetp.eq.u32 pv, 1, 0;\n\tmov.u32 pb, 0;\n\t"                             \
+  "mov.u32 %0, 0;\n\t"                                                                               \
+  "mad.lo.u32 fb, %1, 8, %7;\n\tmad.lo.u32 eb, %1, 8, %8;\n\tmul.lo.u32 s16, %1, %14;\n"             \
+  "WB_KR_LOOP:\n\t"                                                                                  \
+  "@pr bra WB_KR_GO;\n\t"                                                                            \
+  "mov.u32 n, 0;\n"                                                                                  \
+  "WB_KR_WAIT:\n\t"                                                                                  \
+  "mbarrier.test_wait.parity.shared::cta.b64 p, [fb], %2;\n\t"                                       \
+  "@p bra WB_KR_GO;\n\t"                                                                             \
+  "add.u32 n, n, 1;\n\tsetp.lt.u32 q, n, %18;\n\t@q bra WB_KR_WAIT;\n\t"                             \
+  "mov.u32 %0, 1;\n\tbra WB_KR_OUT;\n"                                                               \
+  "WB_KR_GO:\n\t"                                                                                    \
+  "add.u32 ma, %11, s16;\n\tadd.u32 mb, %13, s16;\n\tmov.u32 ga, ma;\n\tmov.u32 gb, mb;\n\t"         \
+  "setp.gt.u32 e1, %3, 1;\n\tand.pred e1, e1, e;\n\t"                                                \
+  "setp.gt.u32 e2, %3, 2;\n\tand.pred e2, e2, e;\n\t"                                                \
+  "setp.gt.u32 e3, %3, 3;\n\tand.pred e3, e3, e;\n\t"
+// where the ring goes next, and a probe of that round's full barrier (not past the last round)
+#define WB_KR_PROBE(KSUB)                                                                            \
+  "add.u32 nst, %1, 1;\n\tadd.u32 nfb, fb, 8;\n\tadd.u32 neb, eb, 8;\n\tadd.u32 ns16, s16, %14;\n\tmov.u32 nph, %2;\n\t" \
+  "setp.eq.u32 w, nst, %6;\n\t"                                                                      \
+  "@w mov.u32 nst, 0;\n\t@w mov.u32 nfb, %7;\n\t@w mov.u32 neb, %8;\n\t@w mov.u32 ns16, 0;\n\t@w xor.b32 nph, nph, 1;\n\t" \
+  "setp.eq.u32 pr, 1, 0;\n\tsetp.gt.u32 pm, %3, " KSUB ";\n\t"                                       \
+  "@pm mbarrier.test_wait.parity.shared::cta.b64 pr, [nfb], nph;\n\t"
+#define WB_KR_TAIL(KSUB, COMMIT)                                                                     \
+  "setp.eq.u32 pa, 0, 0;\n\tmov.u32 %4, 1;\n\t"                                                      \
+  "mov.u32 pb, eb;\n\tsetp.ne.u32 pv, %5, 0;\n\t"                                                    \
+  "mov.u32 %1, nst;\n\tmov.u32 fb, nfb;\n\tmov.u32 eb, neb;\n\tmov.u32 s16, ns16;\n\tmov.u32 %2, nph;\n\t" \
+  "min.u32 use, %3, " KSUB ";\n\tsub.u32 %3, %3, use;\n\tsetp.ne.u32 c, %3, 0;\n\t@c bra WB_KR_LOOP;\n" \
+  "WB_KR_OUT:\n\t"                                                                                   \
+  COMMIT                                                                                             \
+  "}"
+// k-step 0: first MMA, the lagged commit of the round before, the rest; then the later k-steps,
+// with the probe of the next round once the first of them is under way
+#define WB_KR_STEP0(G, COMMIT)                                                                       \
+  WB_KR_MMA(G, "%9", "ma", "mb", "pa", "e") COMMIT WB_KR_MMA_J(G, "ma", "mb", "2", "e")             \
+  WB_KR_MMA_J(G, "ma", "mb", "4", "e") WB_KR_MMA_J(G, "ma", "mb", "6", "e")
+#define WB_KR_BODY2(G, COMMIT) WB_KR_STEP0(G, COMMIT) WB_KR_PROBE("2") WB_KR_GROUP(G, "e1")
+#define WB_KR_BODY4(G, COMMIT) WB_KR_STEP0(G, COMMIT) WB_KR_GROUP(G, "e1") WB_KR_PROBE("4") WB_KR_GROUP(G, "e2") WB_KR_GROUP(G, "e3")
+
+template <int CG, int KSUB>
+WB_DEV uint32_t mma_rounds(uint32_t issuer, uint32_t& kleft, uint32_t depth, uint32_t& stage, uint32_t& phase, uint32_t& accumulate,
+                           uint32_t full0, uint32_t empty0, uint32_t d, uint32_t span, uint32_t ma_lo0, uint32_t atom16, uint32_t mb_lo0,
+                           uint32_t step16, uint32_t hi, uint32_t idesc, uint32_t limit, uint32_t debug = 0) {
+  static_assert(KSUB == 2 || KSUB == 4, "rounds of two or four k-steps");
+  uint32_t status;
+  if constexpr (CG == 2 && KSUB == 2) asm volatile(WB_KR_HEAD("2") WB_KR_BODY2("2", WB_KL_COMMIT2) WB_KR_TAIL("2", WB_KL_COMMIT2) WB_KL_ARGS);
+  if constexpr (CG == 2 && KSUB == 4) asm volatile(WB_KR_HEAD("4") WB_KR_BODY4("2", WB_KL_COMMIT2) WB_KR_TAIL("4", WB_KL_COMMIT2) WB_KL_ARGS);
+  if constexpr (CG == 1 && KSUB == 2) asm volatile(WB_KR_HEAD("2") WB_KR_BODY2("1", WB_KL_COMMIT1) WB_KR_TAIL("2", WB_KL_COMMIT1) WB_KL_ARGS);
+  if constexpr (CG == 1 && KSUB == 4) asm volatile(WB_KR_HEAD("4") WB_KR_BODY4("1", WB_KL_COMMIT1) WB_KR_TAIL("4", WB_KL_COMMIT1) WB_KL_ARGS);
+  return status;
+}
+
+// Producer, a round at a time: wait empty[round], (pair leader) state the bytes of the round's
+// k-steps that exist, load each of them into its slot.
+template <int CG, int KSUB>
+WB_DEV uint32_t load_rounds(uint32_t issuer, uint32_t& kleft, uint32_t depth, uint32_t& stage, uint32_t& phase, int& x, uint32_t empty0,
+                            uint32_t full0, uint32_t full_remote0, uint32_t is_leader, uint32_t tx, uint32_t ring, uint32_t stage_bytes,
+                            uint32_t a_bytes, const void* map_a, int a_row, const void* map_b, int col, uint32_t limit, uint32_t debug,
+                            uint32_t slot_bytes) {
+  static_assert(KSUB == 2 || KSUB == 4, "rounds of two or four k-steps");
+  uint32_t status;
+#define WB_LR_LOADS(CGQ, GUARD)                                                                                  \
+  "add.u32 sb, sg, %14;\n\t"                                                                                     \
+  "@" GUARD " cp.async.bulk.tensor.2d" CGQ ".shared::cluster.global.mbarrier::complete_tx::bytes [sg], [%15, {xg, %16}], [fr];\n\t" \
+  "@" GUARD " cp.async.bulk.tensor.2d" CGQ ".shared::cluster.global.mbarrier::complete_tx::bytes [sb], [%17, {xg, %18}], [fr];\n\t" \
+  "add.u32 sg, sg, %21;\n\tadd.s32 xg, xg, 64;\n\t"
+#define WB_LR_BODY(CGQ, KSUB_S, MORE)                                                                            \
+  "{\n\t.reg .pred e, e1, e2, e3, ei, pl, pn, p, q, w, c;\n\t.reg .b32 n, eb, fl, fr, sa, sb, sg, xg, par, dbg, use, txr;\n\t" \
+  "setp.ne.u32 ei, %5, 0;\n\tand.b32 dbg, %19, 1;\n\tsetp.eq.and.u32 e, dbg, 0, ei;\n\t"                          \
+  "setp.ne.and.u32 pl, %10, 0, e;\n\tsetp.ne.and.u32 pn, %10, 0, ei;\n\tsetp.ne.and.u32 pn, dbg, 0, pn;\n\tmov.u32 %0, 0;\n\t" \
+  "mad.lo.u32 eb, %1, 8, %7;\n\tmad.lo.u32 fl, %1, 8, %8;\n\tmad.lo.u32 fr, %1, 8, %9;\n\tmad.lo.u32 sa, %1, %13, %12;\n" \
+  "WB_LR_LOOP:\n\tmov.u32 n, 0;\n\txor.b32 par, %2, 1;\n"                                                        \
+  "WB_LR_WAIT:\n\t"                                                                                              \
+  "mbarrier.test_wait.parity.shared::cta.b64 p, [eb], par;\n\t"                                                  \
+  "@p bra WB_LR_GO;\n\t"                                                                                         \
+  "add.u32 n, n, 1;\n\tsetp.lt.u32 q, n, %20;\n\t@q bra WB_LR_WAIT;\n\t"                                         \
+  "mov.u32 %0, 1;\n\tbra WB_LR_OUT;\n"                                                                           \
+  "WB_LR_GO:\n\t"                                                                                                \
+  "min.u32 use, %3, " KSUB_S ";\n\tmul.lo.u32 txr, %11, use;\n\t"                                                \
+  "setp.gt.u32 e1, %3, 1;\n\tand.pred e1, e1, e;\n\tsetp.gt.u32 e2, %3, 2;\n\tand.pred e2, e2, e;\n\tsetp.gt.u32 e3, %3, 3;\n\tand.pred e3, e3, e;\n\t" \
+  "@pl mbarrier.arrive.expect_tx.shared::cta.b64 _, [fl], txr;\n\t"                                              \
+  "@pn mbarrier.arrive.shared::cta.b64 _, [fl];\n\t"                                                             \
+  "mov.u32 sg, sa;\n\tmov.u32 xg, %4;\n\t"                                                                       \
+  WB_LR_LOADS(CGQ, "e") WB_LR_LOADS(CGQ, "e1") MORE                                                              \
+  "mad.lo.s32 %4, use, 64, %4;\n\tadd.u32 %1, %1, 1;\n\tadd.u32 eb, eb, 8;\n\tadd.u32 fl, fl, 8;\n\tadd.u32 fr, fr, 8;\n\tadd.u32 sa, sa, %13;\n\t" \
+  "setp.eq.u32 w, %1, %6;\n\t"                                                                                   \
+  "@w mov.u32 %1, 0;\n\t@w mov.u32 eb, %7;\n\t@w mov.u32 fl, %8;\n\t@w mov.u32 fr, %9;\n\t@w mov.u32 sa, %12;\n\t@w xor.b32 %2, %2, 1;\n\t" \
+  "sub.u32 %3, %3, use;\n\tsetp.ne.u32 c, %3, 0;\n\t@c bra WB_LR_LOOP;\n"                                        \
+  "WB_LR_OUT:\n\t}"
+#define WB_LR_ARGS                                                                                               \
+  : "=r"(status), "+r"(stage), "+r"(phase), "+r"(kleft), "+r"(x)                                                 \
+  : "r"(issuer), "r"(depth), "r"(empty0), "r"(full0), "r"(full_remote0), "r"(is_leader), "r"(tx), "r"(ring), "r"(stage_bytes), \
+    "r"(a_bytes), "l"(reinterpret_cast<uint64_t>(map_a)), "r"(a_row), "l"(reinterpret_cast<uint64_t>(map_b)), "r"(col), "r"(debug), "r"(limit), \
+    "r"(slot_bytes)                                                                                              \
+  : "memory"
+  if constexpr (CG == 2 && KSUB == 2) asm volatile(WB_LR_BODY(".cta_group::2", "2", "") WB_LR_ARGS);
+  if constexpr (CG == 2 && KSUB == 4) asm volatile(WB_LR_BODY(".cta_group::2", "4", WB_LR_LOADS(".cta_group::2", "e2") WB_LR_LOADS(".cta_group::2", "e3")) WB_LR_ARGS);
+  if constexpr (CG == 1 && KSUB == 2) asm volatile(WB_LR_BODY("", "2", "") WB_LR_ARGS);
+  if constexpr (CG == 1 && KSUB == 4) asm volatile(WB_LR_BODY("", "4", WB_LR_LOADS("", "e2") WB_LR_LOADS("", "e3")) WB_LR_ARGS);
+#undef WB_LR_BODY
+#undef WB_LR_LOADS
+#undef WB_LR_ARGS
+  return status;
+}
+
 // ---------------------------------------------------------------- cluster launch control
 // Ask the hardware to cancel a not-yet-launched cluster of this grid; the 16-byte
 // answer lands in this CTA's shared memory and completes 16 bytes on `bar`.

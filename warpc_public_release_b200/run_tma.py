@@ -101,6 +101,15 @@ def run(variant, m, n, k, repeat=20, seed=1, name=None, out=sys.stdout):
                 col = col[col > 0] - t0
                 cells.append("%5d:%7d/%7d/%7d" % (len(col), col.min(), np.median(col), col.max()) if len(col) else " " * 29)
             print("  %2d %-34s %s" % (ev, label, "  ".join(cells)), file=out)
+        ran = st[:, 15, 0] > 0
+        if ran.any():  # event 15: SM cycles from entry to exit, against the same interval on the GPU-wide timer
+            mhz = 1e3 * st[ran, 15, 0] / np.maximum(st[ran, 9, 0] - st[ran, 0, 0], 1)
+            print("  SM clock over the launch: %.0f MHz (median of CTAs)" % np.median(mhz), file=out)
+        # events 11-14: SM cycles the first epilogue warp spent in each part of a tile's store
+        for ev, label in zip(range(11, 15), ("waiting for tcgen05.ld", "waiting for a staging copy", "st.shared + fence", "issuing the TMA store")):
+            cells = ["%5d:%7d/%7d/%7d" % (len(c), c.min(), np.median(c), c.max()) if len(c) else " " * 29
+                     for c in (st[:, ev, t][st[:, ev, t] > 0] for t in range(4))]
+            print("  %2d %-34s %s" % (ev, "epilogue cycles: " + label, "  ".join(cells)), file=out)
     if os.environ.get("WARPC_VERIFY_LAST"):
         c2 = dc.cpu().numpy()
         print("  last launch: %d wrong" % int(np.count_nonzero(~(np.abs(c2 - ref) <= tol))), file=out)
