@@ -271,7 +271,7 @@ def ours(args, rank, world, local_rank):
         "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
                      "frac": per_gpu / peaks["bf16_tflops_sustained"], "peak_source": which + " (cuBLAS bf16 sustained)",
                      "frac_of_burst": per_gpu / peaks["bf16_tflops"], "frac_of_nominal_2250": per_gpu / NOMINAL_TFLOPS,
-                     "traffic": TRAFFIC_BYTES_PER_LAUNCH, "algorithmic_bytes": 2 * rows * k + 2 * n * k + 4 * rows * n},
+                     "traffic": TRAFFIC_BYTES_PER_LAUNCH if world == 1 else None, "algorithmic_bytes": 2 * rows * k + 2 * n * k + 4 * rows * n},
         "e2e": {"value": flops / e2e_s / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_s * 1e3, "steps": e2e_steps,
                 "h2d_bytes_per_step": world * (rows * k * 2 + n * k * 2), "d2h_bytes_per_step": world * rows * n * 4},
         "gpu_launches": args.steps * world,
@@ -298,9 +298,11 @@ def ours(args, rank, world, local_rank):
     return 0
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu
-# capture summarised under profiles/ (null until one has been taken at this size or scaled to it)
-TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel on the one-GPU
+# workload (16384^3), from the one-pass ncu capture summarised in
+# profiles/gemm_kernel_pair_256x256_16384x16384x16384_dram.md: 7.92 GB read + 1.06 GB written.
+# No capture exists for the per-GPU slabs of a sharded run, so those lines carry null.
+TRAFFIC_BYTES_PER_LAUNCH = 8.98e9
 
 
 def main():

@@ -20,11 +20,15 @@ import warpc_public_release_b200 as w  # noqa: E402
 from oracle import gemm_ref  # noqa: E402
 
 
-def run_gemm(variant, m, n, k, a, bt, launches=1, prefill=float("nan")):
+def run_gemm(variant, m, n, k, a, bt, launches=1, prefill=float("nan"), dependent=False, mode=0):
     da, db = torch.from_numpy(a).cuda(), torch.from_numpy(bt).cuda()
     dc = torch.full((m, n), prefill, dtype=torch.float32, device="cuda")
     plan = w.Plan(variant, m, n, k, da.data_ptr(), db.data_ptr(), dc.data_ptr())
     plan.set_timeout_ms(1000)
+    if dependent:
+        plan.set_dependent_launch(True)
+    if mode:
+        plan.debug_set_mode(mode)
     for _ in range(launches):
         plan.launch()
     plan.status()
@@ -33,9 +37,9 @@ def run_gemm(variant, m, n, k, a, bt, launches=1, prefill=float("nan")):
     return out
 
 
-def check(variant, m, n, k, family, launches=1):
+def check(variant, m, n, k, family, launches=1, **how):
     a, bt = gemm_ref.INPUTS[family](m, n, k)
-    c = run_gemm(variant, m, n, k, a, bt, launches)
+    c = run_gemm(variant, m, n, k, a, bt, launches, **how)
     ref = gemm_ref.gemm_ref(a, bt)
     wrong = gemm_ref.count_wrong(c, ref, gemm_ref.tolerance(family, k, a, bt))
     assert wrong == 0, "%d of %d entries wrong" % (wrong, m * n)
@@ -64,6 +68,9 @@ CASES = [
     ("split_k_more_runs_than_blocks", (256, 512, 4096), lambda s: SW(*s, 256, 256, 4, split_grid=37, split_add=True)),
     ("stream_k", (1024, 512, 1024), lambda s: SW(*s, 256, 128, 6, streamk=True, split_add=True, bufs=2, ask_ahead=True)),
     ("stream_k_long", (1024, 1024, 4096), lambda s: SW(*s, 256, 128, 6, streamk=True, split_add=True, bufs=2)),
+    ("fold_rounds_partial_last_round", (256, 256, 448), lambda s: SW(*s, 128, 64, 12, direct=True)),   # 7 k-steps in rounds of 4
+    ("pair_128x128_rounds_odd_k", (256, 512, 320), lambda s: SW(*s, 128, 128, 8)),                      # 5 k-steps in rounds of 2
+    ("stream_k_rounds", (512, 512, 1088), lambda s: SW(*s, 128, 128, 8, streamk=True, split_add=True, bufs=2)),
     ("split_in_cluster_as_grid", (256, 512, 16384), lambda s: w.choose(*s)),
     ("rule_pair_fallback", (512, 384, 256), lambda s: w.pair(*s, 8)),
     ("rule_small", (256, 384, 512), lambda s: w.choose(*s)),
@@ -81,6 +88,21 @@ def test_variant_against_oracle(name, shape, build, family):
 def test_repeated_launches_leave_the_same_answer(name, shape, build):
     # hand-off flags count launches and are never reset (gemm_swapped.ml:608-626); the 1st and the 7th launch agree
     check(build(shape), *shape, "integers", launches=7)
+
+
+@pytest.mark.parametrize("name,shape,build", [c for c in CASES if c[0] in (
+    "pair_staged", "persistent_stride_two_accumulators", "clc_many_tiles", "split_k_grid_even", "stream_k", "rule_small", "pair_256x256")],
+                         ids=lambda x: x if isinstance(x, str) else None)
+def test_dependent_launches_back_to_back(name, shape, build):
+    # each launch may begin while the one before it still runs (backend/node/clusterlaunch.py:54-74); the kernel's
+    # griddepcontrol.wait keeps its reads and writes behind the launch before it, hand-off flags included
+    check(build(shape), *shape, "integers", launches=7, dependent=True)
+
+
+@pytest.mark.parametrize("ksub", [1, 2, 4])
+def test_every_round_length_gives_the_same_product(ksub):
+    for shape, build in (((512, 512, 1088), lambda s: SW(*s, 128, 128, 8)), ((256, 256, 576), lambda s: SW(*s, 128, 64, 12, direct=True))):
+        check(build(shape), *shape, "hash", mode=ksub << 8)
 
 
 def test_golden_products_bit_exact(golden_dir):

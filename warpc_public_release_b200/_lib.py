@@ -68,6 +68,7 @@ def lib():
         "wg_host_plan_buffer": ([vp, i], vp),
         "wg_time_launches": ([vp, i, i, ctypes.POINTER(ctypes.c_float)], i),
         "wg_plan_enable_stamps": ([vp, i], i),
+        "wg_plan_set_dependent_launch": ([vp, i], i),
         "wg_plan_read_stamps": ([vp, ctypes.POINTER(ctypes.c_ulonglong), ctypes.c_size_t], i),
         "wg_plan_debug_set_flag": ([vp, i, u], i),
         "wg_plan_debug_set_mode": ([vp, u], i),

@@ -112,6 +112,7 @@ struct Plan {
   // host plans own these
   void *dA = nullptr, *dBt = nullptr, *dC = nullptr;
   bool owns_buffers = false;
+  bool dependent_launch = false;  // launches carry the programmatic stream serialization attribute
   int M = 0, N = 0, K = 0;
 };
 
@@ -154,6 +155,7 @@ int fill_plan(Plan* pl, int device, const wg_variant* v, int M, int N, int K, co
   p.depth = li.depth, p.nbuf = li.nbuf, p.sched = li.sched, p.ask_ahead = li.ask_ahead;
   p.split = li.split;
   set_rounds(p, pl->k, li.depth);
+  p.late_launch = v->late_launch;
   p.epi_ring = (!li.direct && size_t(li.depth) * size_t(pl->k->stage_bytes) >= size_t(li.tile_m) * size_t(li.tile_n) * 4) ? 1 : 0;
   if (li.sched == SCHED_STREAMK) {
     const int clusters = li.grid / li.cluster, units = (p.ntiles / li.cluster) * p.kt;
@@ -247,15 +249,24 @@ extern "C" int wg_launch(void* plan, void* cuda_stream) {
   cfg.blockDim = dim3(unsigned(pl->li.threads), 1, 1);
   cfg.dynamicSmemBytes = size_t(pl->li.dynsmem);
   cfg.stream = static_cast<cudaStream_t>(cuda_stream);
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = unsigned(pl->li.cluster);
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = pl->dependent_launch ? 2 : 1;
   void* args[5] = {&pl->map_a, &pl->map_b, &pl->map_c, &pl->map_cw, &pl->p};
   return int(cudaLaunchKernelExC(&cfg, pl->k->fn, args));
+}
+
+extern "C" int wg_plan_set_dependent_launch(void* plan, int on) {
+  Plan* pl = static_cast<Plan*>(plan);
+  if (!pl) return WG_E_ARG;
+  pl->dependent_launch = on != 0;
+  return WG_OK;
 }
 
 extern "C" int wg_last_device_status(void* plan, unsigned out[4]) {
@@ -437,6 +448,7 @@ extern "C" int wg_launch_noalloc(int device, const wg_variant* v, int M, int N, 
   p.cl_n = li.cl_n > 0 ? li.cl_n : 1, p.group = li.group > 0 ? li.group : 1, p.serp = li.serpentine;
   p.depth = li.depth, p.nbuf = li.nbuf, p.sched = li.sched, p.ask_ahead = li.ask_ahead, p.split = li.split;
   set_rounds(p, k, li.depth);
+  p.late_launch = v->late_launch;
   p.epi_ring = (!li.direct && size_t(li.depth) * size_t(k->stage_bytes) >= size_t(li.tile_m) * size_t(li.tile_n) * 4) ? 1 : 0;
   if (li.sched == SCHED_STREAMK) {
     const int clusters = li.grid / li.cluster, units = (p.ntiles / li.cluster) * p.kt;

@@ -52,6 +52,7 @@ struct KParams {
   int ask_ahead;  // probe the next stage before releasing this one
   int split;      // SCHED_SPLITK: runs of K per tile
   int sk_q, sk_r, sk_clusters;  // SCHED_STREAMK: units = q * clusters + r
+  int late_launch;              // the next grid in the stream is let go when the producer's last load is out, not at entry
   int ksub, rounds;             // the ring is handed over `ksub` k-steps (slots) at a time: rounds = depth / ksub barrier pairs
   int epi_ring;                 // the ring holds a whole C tile: a CTA's last tile is staged there, one copy per block
   float* C;                     // direct store
@@ -141,8 +142,8 @@ WB_DEV void record_failure(const KParams& p, uint32_t code, uint32_t detail, uin
 // the CTA's `slot`-th tile, on the GPU-wide nanosecond timer.
 enum : int { EV_ENTRY = 0, EV_SETUP = 1, EV_LOAD_FIRST = 2, EV_LOAD_LAST = 3, EV_MMA_FIRST = 4, EV_MMA_LAST = 5,
              EV_ACC_READY = 6, EV_STORED = 7, EV_TEARDOWN = 8, EV_EXIT = 9, EV_ACC_FREE = 10 };
-// cycle counters of a timing run: events 16.. hold sums of clock64() intervals, not times
-enum : int { EV_CYC_PROD_WAIT = 16, EV_CYC_PROD_ISSUE = 17, EV_CYC_MMA_WAIT = 18, EV_CYC_MMA_ISSUE = 19, EV_CYC_MMA_ACC_WAIT = 20 };
+// 11-14: cycle sums of the first epilogue warp, 15: cycles entry to exit; 16 barriers initialised, 17 tensor memory
+// allocated, 18 first tile found, 19 last stores have read their copies, 20 CTAs met at teardown, 21 tensor memory freed
 WB_DEV void stamp_value(const KParams& p, int ev, int slot, long long value) {
   if (p.stamps != nullptr && slot < 4) p.stamps[(size_t(blockIdx.x) * 64 + ev) * 4 + slot] = (unsigned long long)value;
 }
@@ -423,6 +424,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   const uint32_t issuer = (lane == 0) ? 1u : 0u;  // the lane that issues its warp's single-lane instructions
   const int depth = p.depth, nbuf = p.nbuf, rounds = p.rounds, ksub = p.ksub;
   const long long cycles_at_entry = clock64();
+  // Dependent launch (the reference's PREEXIT / ACQBULK, backend/sass.ml:496-502, gemm_swapped.ml:169-172, 232, 368):
+  // under the programmatic-stream-serialization launch attribute the next grid in the stream may
+  // take SMs as this grid's CTAs leave, from this instruction on -- or, "late launch", once the
+  // producer's last load is out, so its CTAs do not sit on idle SMs through this grid.  Without
+  // the attribute both instructions do nothing.
+  if (threadIdx.x == 0 && !p.late_launch) griddep_launch_dependents();
   if (threadIdx.x == 0) stamp(p, EV_ENTRY, 0);
 
   auto full_bar = [&](int s) { return ctrl_at(offsetof(Ctrl, full) + 8 * s); };
@@ -451,11 +458,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       if constexpr (!C::DIRECT) prefetch_tmap(&map_c), prefetch_tmap(&map_cw);
     }
     fence_mbar_init();
+    if (lane == 0) stamp(p, 16, 0);
   }
   if (warp == 1) {
     // both CTAs of a pair allocate, each into its own slot word
     tmem_alloc<CG>(ctrl_at(offsetof(Ctrl, tmem_base)), uint32_t(C::pow2_ge(C::NCOLS * nbuf)));
     tmem_relinquish<CG>();
+    if (lane == 0) stamp(p, 17, 0);
   }
   // every role's first unit of work and its tile's origin, found while the barriers and the
   // tensor memory are being set up rather than after the CTAs have met
@@ -464,6 +473,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   bool have = walk.template next<true>(w);
   int row = 0, col = 0;
   if (have) tile_origin<C>(p, w.tile, row, col);
+  if (threadIdx.x == 0) stamp(p, 18, 0);
   tc_fence_before();
   if constexpr (CG == 2) {
     cluster_arrive();
@@ -472,6 +482,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     __syncthreads();
   }
   tc_fence_after();
+  // nothing above touched global memory (a timing build's entry stamp aside); everything below
+  // may read what the grid before this one wrote
+  griddep_wait();
   const uint32_t tmem_base = warp_uniform(ld_shared_u32(ctrl_at(offsetof(Ctrl, tmem_base))));
   if (threadIdx.x == 0) stamp(p, EV_SETUP, 0);
 
@@ -514,6 +527,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         stamp(p, EV_LOAD_LAST, nth);
         ++nth;
       }
+      if (p.late_launch) griddep_launch_dependents();
       // every stage this CTA filled has been released before it leaves
       for (int i = 0; ok && i < rounds; ++i) {
         ok = wait_bar<false, false>(p, abort_addr, empty_bar(int(stage)), phase ^ 1u, ST_WAIT_EMPTY, 0x100u + stage);
@@ -729,6 +743,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       }
       if (lane == 0) bulk_wait_read<0>();  // the last stores have read their staging copies
       __syncwarp();
+      if (first_warp && lane == 0) stamp(p, 19, 0);
     }
   }
 
@@ -748,9 +763,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   } else {
     __syncthreads();
   }
+  if (threadIdx.x == 0) stamp(p, 20, 0);
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc<CG>(tmem_base, uint32_t(C::pow2_ge(C::NCOLS * nbuf)));
+    if (lane == 0) stamp(p, 21, 0);
   }
   if (threadIdx.x == 0) stamp(p, EV_EXIT, 0), stamp_value(p, 15, 0, clock64() - cycles_at_entry);
 }

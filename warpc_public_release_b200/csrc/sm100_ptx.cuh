@@ -28,6 +28,10 @@ WB_DEV uint64_t globaltimer() {
   return t;
 }
 
+// Dependent launch: let the next grid in the stream be scheduled / wait for the grids before this one.
+WB_DEV void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+WB_DEV void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // Address of the same shared-memory offset in CTA `rank` of this cluster.
 WB_DEV uint32_t mapa(uint32_t addr, uint32_t rank) {
   uint32_t r;

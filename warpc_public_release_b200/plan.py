@@ -42,6 +42,12 @@ class _Base:
         check(_lib.lib().wg_time_launches(self._h, int(warmup), int(repeat), ctypes.byref(ms)), "wg_time_launches")
         return ms.value
 
+    def set_dependent_launch(self, on=True):
+        """Launches that follow may begin while the one before them in the stream still runs (the
+        reference's `pdl`, backend/node/clusterlaunch.py:54-74); the kernel waits before it reads
+        or writes global memory."""
+        check(_lib.lib().wg_plan_set_dependent_launch(self._h, int(bool(on))), "wg_plan_set_dependent_launch")
+
     def enable_stamps(self, on=True):
         check(_lib.lib().wg_plan_enable_stamps(self._h, int(bool(on))), "wg_plan_enable_stamps")
 

@@ -13,7 +13,8 @@ events and the last line reads
 
     NAME MxNxK grid=(G, 1)  MATCH|MISMATCH bad=x/y  ms  TFLOP/s
 
-WARPC_NO_CHECK=1 skips the check (prints UNCHECKED), WARPC_VERIFY_LAST=1 also checks what the
+WARPC_PDL=1 lets each timed launch begin while the one before it runs (the reference's AB_PDL,
+backend/node/ab.py:95-118).  WARPC_NO_CHECK=1 skips the check (prints UNCHECKED), WARPC_VERIFY_LAST=1 also checks what the
 last timed launch left, WARPC_STAMPS=1 prints the phase stamps of one more launch.  Returns
 True when the check passed.  The numpy product is the harness's checker, exactly as in the
 reference; the kernel never runs on the CPU.
@@ -29,6 +30,8 @@ from .plan import Plan
 STAMP_NAMES = ["entry", "barriers initialised, cluster met", "producer: first stage issued", "producer: last stage issued",
                "MMA: first stage landed", "MMA: last stage issued", "epilogue: accumulator ready", "epilogue: tile's stores issued",
                "roles done", "exit", "MMA: accumulator free"]
+FINE_STAMP_NAMES = ["set-up: barriers initialised", "set-up: tensor memory allocated", "set-up: first tile found",
+                    "teardown: last stores read", "teardown: CTAs met", "teardown: tensor memory freed"]
 
 
 def make_inputs(m, n, k, seed=1):
@@ -78,6 +81,8 @@ def run(variant, m, n, k, repeat=20, seed=1, name=None, out=sys.stdout):
     grid = tuple(int(x) for x in hdr["grid"].split())
     plan.launch()
     plan.status()
+    if os.environ.get("WARPC_PDL") == "1":
+        plan.set_dependent_launch(True)
     if ref is None:
         ms = plan.time_launches(repeat, warmup=0)
         print("%-28s %dx%dx%d grid=%s  UNCHECKED  %.4f ms" % (name, m, n, k, grid, ms), file=out)
@@ -94,7 +99,7 @@ def run(variant, m, n, k, repeat=20, seed=1, name=None, out=sys.stdout):
         plan.enable_stamps(False)
         t0 = st[:, 0, 0][st[:, 0, 0] > 0].min()
         print("  %d CTAs ran; ns from the first CTA's entry: count:min/median/max per tile" % int((st[:, 0, 0] > 0).sum()), file=out)
-        for ev, label in enumerate(STAMP_NAMES):
+        for ev, label in list(enumerate(STAMP_NAMES)) + list(zip(range(16, 22), FINE_STAMP_NAMES)):
             cells = []
             for t in range(4):
                 col = st[:, ev, t]
