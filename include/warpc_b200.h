@@ -63,6 +63,9 @@ typedef struct wg_launch_info {
   int sched;               /* 0 one tile a CTA, 1 fixed grid by stride, 2 cluster launch control, 3 split-K over the grid, 4 stream-K */
   int depth, nbuf, group, cl_n, serpentine, ask_ahead, split, nflags;
   int a_box_rows, bt_box_rows, c_box_rows;
+  int ksub, rounds;        /* the ring is handed over ksub k-steps (slots) at a time: rounds = depth / ksub barrier pairs */
+  int wide_rows;           /* C rows per store of a CTA's last tile when it is staged whole in the drained ring, else 0 */
+  int stage_bytes;         /* one ring slot: this CTA's A half-tile and B^T tile of one k-step */
 } wg_launch_info;
 
 /* `warpc gemm M N K`: the program chosen for a shape (backend/programs.ml:46-80).

@@ -1,0 +1,66 @@
+"""The hand-off protocol of the kernel's roles, checked on the host (no GPU): barrier counts and
+parities, ring slots, accumulator states, coverage of every tile's k-steps, under seeded random
+interleavings -- and the same model with one rule of the protocol broken, which it has to catch.
+The reference does this by interpreting its generated kernel (backend/interp.ml:311-332, 402-417,
+454-487); here the role programs are restated over the launch geometry the library reports."""
+import pytest
+
+import warpc_public_release_b200 as w
+from warpc_public_release_b200 import protocol
+
+SW = w.swapped
+VARIANTS = [
+    ("one", (256, 384, 512), lambda s: w.one(*s, 4)),
+    ("pair_fallback", (512, 384, 256), lambda s: w.pair(*s, 8)),
+    ("fold_rounds_of_four_partial", (256, 256, 448), lambda s: SW(*s, 128, 64, 12, direct=True)),
+    ("rounds_of_two_odd_k", (256, 512, 320), lambda s: SW(*s, 128, 128, 8)),
+    ("ring_wraps", (256, 256, 1024), lambda s: SW(*s, 128, 128, 3, direct=True)),
+    ("one_tile_256x128", (512, 512, 256), lambda s: SW(*s, 256, 128, 5)),
+    ("stride_two_accumulators", (2048, 2304, 256), lambda s: SW(*s, 128, 128, 8, bufs=2, group=16)),
+    ("clc_more_clusters_than_fit", (2304, 2048, 128), lambda s: SW(*s, 192, 128, 7, clc=True)),
+    ("clc_256x256", (1024, 2048, 512), lambda s: SW(*s, 256, 256, 4, clc=True, serpentine=True)),
+    ("split_k_even", (512, 1024, 1024), lambda s: SW(*s, 256, 256, 4, split_grid=4, split_add=True)),
+    ("split_k_uneven", (512, 1024, 1088), lambda s: SW(*s, 256, 256, 4, split_grid=3, split_add=True)),
+    ("split_k_more_runs_than_blocks", (256, 512, 4096), lambda s: SW(*s, 256, 256, 4, split_grid=37, split_add=True)),
+    ("stream_k", (1024, 512, 1024), lambda s: SW(*s, 256, 128, 6, streamk=True, split_add=True, bufs=2)),
+    ("stream_k_rounds", (512, 512, 1088), lambda s: SW(*s, 128, 128, 8, streamk=True, split_add=True, bufs=2)),
+    ("rule_2048", (2048, 2048, 2048), lambda s: w.choose(*s)),
+    ("rule_4096_stream_k", (4096, 4096, 1024 * 2), lambda s: w.choose(*s)),
+    ("rule_split_k_long", (1024, 1024, 8192), lambda s: w.choose(*s)),
+]
+
+
+@pytest.mark.parametrize("name,shape,build", VARIANTS, ids=[v[0] for v in VARIANTS])
+def test_protocol_holds_under_random_interleavings(name, shape, build):
+    v = build(shape)
+    for seed in ((0, 1, 2) if shape[0] * shape[1] * shape[2] < 2 ** 31 else (0,)):
+        assert protocol.check(v, *shape, seed=seed) > 0
+
+
+@pytest.mark.parametrize("mutation,needle", [
+    ({"acc_empty_count": 7}, ""),                          # the accumulator is handed back before its last reader is done
+    ({"acc_empty_count": 9}, "nothing can move"),          # a release that never comes: the MMA warp waits for ever
+    ({"full_count": 2}, "nothing can move"),               # a second arrival the producer never makes
+    ({"producer_rounds": 3}, ""),                          # producer and MMA issuer disagree about the ring's length
+    ({"tx_short": 4096}, ""),                              # the leader states fewer bytes than land: the stage opens early
+    ({"no_acc_empty_wait": True}, ""),                     # the MMA warp starts a tile on an accumulator still being read
+])
+def test_a_broken_protocol_is_caught(mutation, needle):
+    shape = (2048, 2304, 256)  # 288 tiles on a fixed grid of 148: two tiles a CTA; one accumulator where its reuse is the point
+    v = SW(*shape, 128, 128, 8, bufs=1 if "no_acc_empty_wait" in mutation else 2, group=16)
+    assert protocol.check(v, *shape) > 0
+    with pytest.raises(protocol.Violation) as e:
+        for seed in range(4):
+            protocol.check(v, *shape, seed=seed, mutate=mutation)
+    assert needle in str(e.value)
+
+
+@pytest.mark.parametrize("shape", [(1024, 1024, 1024), (1536, 1536, 1536), (3072, 1280, 2048), (4096, 4096, 1024), (1024, 1024, 65536)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_the_rules_program_for_a_benchmark_shape(shape):
+    assert protocol.check(w.choose(*shape), *shape, seed=0) > 0
+
+
+def test_cli(capsys):
+    assert protocol.main(["1024", "1024", "1024"]) == 0
+    assert "protocol ok" in capsys.readouterr().out

@@ -88,16 +88,6 @@ int encode_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem, const void* pt
   return r == CUDA_SUCCESS ? WG_OK : int(r);
 }
 
-// How many k-steps the ring hands over at a time (one full and one empty barrier a round): one
-// k-step's barrier round costs the issuing thread more than four narrow MMAs take to run, so
-// the slots of the N = 128 tiles go in fours (16 KB) or pairs (24 KB); larger slots keep a round per
-// k-step, where handing over 64 KB at a time would leave the producer too little slack.
-void set_rounds(KParams& p, const wb_kernel_entry* k, int depth) {
-  int ksub = (k->reps != 1 || k->stage_bytes > 24 * 1024) ? 1 : (k->stage_bytes <= 16 * 1024 ? 4 : 2);
-  while (ksub > 1 && depth / ksub < 2) ksub /= 2;
-  p.ksub = ksub, p.rounds = depth / ksub;
-}
-
 struct Plan {
   int device = 0;
   wg_variant v;
@@ -154,9 +144,9 @@ int fill_plan(Plan* pl, int device, const wg_variant* v, int M, int N, int K, co
   p.serp = li.serpentine;
   p.depth = li.depth, p.nbuf = li.nbuf, p.sched = li.sched, p.ask_ahead = li.ask_ahead;
   p.split = li.split;
-  set_rounds(p, pl->k, li.depth);
+  p.ksub = li.ksub, p.rounds = li.rounds;
   p.late_launch = v->late_launch;
-  p.epi_ring = (!li.direct && size_t(li.depth) * size_t(pl->k->stage_bytes) >= size_t(li.tile_m) * size_t(li.tile_n) * 4) ? 1 : 0;
+  p.epi_ring = li.wide_rows != 0;
   if (li.sched == SCHED_STREAMK) {
     const int clusters = li.grid / li.cluster, units = (p.ntiles / li.cluster) * p.kt;
     p.sk_clusters = clusters, p.sk_q = units / clusters, p.sk_r = units % clusters;
@@ -447,9 +437,9 @@ extern "C" int wg_launch_noalloc(int device, const wg_variant* v, int M, int N, 
   p.ntiles = ((M + li.tile_m - 1) / li.tile_m) * ((N + li.tile_n - 1) / li.tile_n);
   p.cl_n = li.cl_n > 0 ? li.cl_n : 1, p.group = li.group > 0 ? li.group : 1, p.serp = li.serpentine;
   p.depth = li.depth, p.nbuf = li.nbuf, p.sched = li.sched, p.ask_ahead = li.ask_ahead, p.split = li.split;
-  set_rounds(p, k, li.depth);
+  p.ksub = li.ksub, p.rounds = li.rounds;
   p.late_launch = v->late_launch;
-  p.epi_ring = (!li.direct && size_t(li.depth) * size_t(k->stage_bytes) >= size_t(li.tile_m) * size_t(li.tile_n) * 4) ? 1 : 0;
+  p.epi_ring = li.wide_rows != 0;
   if (li.sched == SCHED_STREAMK) {
     const int clusters = li.grid / li.cluster, units = (p.ntiles / li.cluster) * p.kt;
     p.sk_clusters = clusters, p.sk_q = units / clusters, p.sk_r = units % clusters;
@@ -501,7 +491,7 @@ extern "C" int wg_plan_debug_set_mode(void* plan, unsigned flags) {
   pl->p.debug = flags & 0xffu;
   // bits 8-11: k-steps a barrier round (1, 2 or 4) for the launches that follow; 0 = the library's choice
   const int ksub = int((flags >> 8) & 0xfu);
-  if (ksub == 0) set_rounds(pl->p, pl->k, pl->p.depth);
+  if (ksub == 0) pl->p.ksub = pl->li.ksub, pl->p.rounds = pl->li.rounds;
   else if ((ksub == 1 || ((ksub == 2 || ksub == 4) && pl->k->reps == 1)) && pl->p.depth / ksub >= 2) pl->p.ksub = ksub, pl->p.rounds = pl->p.depth / ksub;
   else return WG_E_ARG;
   return WG_OK;

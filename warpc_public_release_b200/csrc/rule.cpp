@@ -316,12 +316,26 @@ extern "C" int wg_realise(const wg_variant* v, int M, int N, int K, wg_launch_in
   // this kernel's staging copies and control block are larger than the reference's: where the
   // reference's ring depth no longer fits beside them, the ring is one or two stages shorter
   while (li.depth > 2 && e->smem_fixed + size_t(li.depth) * e->stage_bytes > 232448) li.depth -= 1;
+  // the rule's own programs take the deepest ring that fits: ring slack against L2 latency is what the
+  // k loop's pace depends on most (256 x 128: 560 cycles a k-step at depth 6, 620 at 5, 750 at 4)
+  if (v->retile && v->prog == WG_PROG_SWAPPED)
+    while (li.depth < 16 && e->smem_fixed + size_t(li.depth + 1) * e->stage_bytes <= 232448) li.depth += 1;
   li.dynsmem = int(e->smem_fixed + size_t(li.depth) * e->stage_bytes);
   if (li.dynsmem > 232448 || li.depth > 16) return WG_E_VARIANT;
-  li.mbarriers = 2 * li.depth + 4 + 3;
   li.a_box_rows = li.tile_m / li.cg;
   li.bt_box_rows = li.tile_n;
   li.c_box_rows = li.direct ? 0 : li.epi_rows;
+  // How many k-steps the ring hands over at a time (one full and one empty barrier a round): one
+  // k-step's barrier round costs the issuing thread more than four narrow MMAs take to run, so
+  // the slots of the N = 128 tiles go in fours (16 KB) or pairs (24 KB); larger slots keep a round per
+  // k-step, where handing over 64 KB at a time would leave the producer too little slack.
+  li.stage_bytes = e->stage_bytes;
+  li.ksub = (e->reps != 1 || e->stage_bytes > 24 * 1024) ? 1 : (e->stage_bytes <= 16 * 1024 ? 4 : 2);
+  while (li.ksub > 1 && li.depth / li.ksub < 2) li.ksub /= 2;
+  li.rounds = li.depth / li.ksub;
+  li.mbarriers = 2 * li.rounds + 4 + 3;  // full + empty a round, two accumulators' full + empty, scheduler's three
+  // a CTA's last tile is staged whole in the ring when the ring can hold it
+  li.wide_rows = (!li.direct && size_t(li.depth) * size_t(e->stage_bytes) >= size_t(li.tile_m) * size_t(li.tile_n) * 4) ? e->wide_rows : 0;
   (void)K;
   return WG_OK;
 }
