@@ -88,6 +88,18 @@ int encode_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem, const void* pt
   return r == CUDA_SUCCESS ? WG_OK : int(r);
 }
 
+// L2 hints, from measurements on the benchmark shapes (isolated calls on L2-warm operands): operand
+// lines marked evict-last pay where every CTA has one tile or the tiles' K is short and A and B^T
+// together are well inside the L2 (2048^3 -8 %, 3072x1280x2048 -9 %, 4096x4096x1024 -5 %) and cost
+// where they are not (8192x2048x4096 +6 %); C marked evict-first pays on the persistent walks, whose
+// stores run beside the next tile's loads (4096^3 -2 %, 2048x2048x16384 -2 %), and never costs.
+int l2_hints_for(const wg_launch_info& li, int M, int N, int K) {
+  const bool small_operands = 2.0 * double(K) * (double(M) + double(N)) <= 48.0 * 1024 * 1024;
+  const bool loads_last = (li.sched == SCHED_ONE || li.sched == SCHED_STRIDE) && small_operands;
+  const bool stores_first = li.sched == SCHED_STRIDE || li.sched == SCHED_STREAMK || loads_last;
+  return (stores_first ? 1 : 0) | (loads_last ? 2 : 0);
+}
+
 struct Plan {
   int device = 0;
   wg_variant v;
@@ -145,6 +157,7 @@ int fill_plan(Plan* pl, int device, const wg_variant* v, int M, int N, int K, co
   p.depth = li.depth, p.nbuf = li.nbuf, p.sched = li.sched, p.ask_ahead = li.ask_ahead;
   p.split = li.split;
   p.ksub = li.ksub, p.rounds = li.rounds;
+  p.l2_hints = l2_hints_for(li, M, N, K);
   p.late_launch = v->late_launch;
   p.epi_ring = li.wide_rows != 0;
   if (li.sched == SCHED_STREAMK) {
@@ -438,6 +451,7 @@ extern "C" int wg_launch_noalloc(int device, const wg_variant* v, int M, int N, 
   p.cl_n = li.cl_n > 0 ? li.cl_n : 1, p.group = li.group > 0 ? li.group : 1, p.serp = li.serpentine;
   p.depth = li.depth, p.nbuf = li.nbuf, p.sched = li.sched, p.ask_ahead = li.ask_ahead, p.split = li.split;
   p.ksub = li.ksub, p.rounds = li.rounds;
+  p.l2_hints = l2_hints_for(li, M, N, K);
   p.late_launch = v->late_launch;
   p.epi_ring = li.wide_rows != 0;
   if (li.sched == SCHED_STREAMK) {

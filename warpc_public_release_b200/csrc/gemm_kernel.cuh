@@ -52,6 +52,7 @@ struct KParams {
   int ask_ahead;  // probe the next stage before releasing this one
   int split;      // SCHED_SPLITK: runs of K per tile
   int sk_q, sk_r, sk_clusters;  // SCHED_STREAMK: units = q * clusters + r
+  int l2_hints;                 // bit 0: C's lines leave the L2 first; bit 1: operand lines leave it last
   int late_launch;              // the next grid in the stream is let go when the producer's last load is out, not at entry
   int ksub, rounds;             // the ring is handed over `ksub` k-steps (slots) at a time: rounds = depth / ksub barrier pairs
   int epi_ring;                 // the ring holds a whole C tile: a CTA's last tile is staged there, one copy per block
@@ -327,7 +328,7 @@ WB_DEV void epi_coords(int row, int col, int q, int i, int& y, int& x) {
 // has retired) can hold it, every block gets a copy of its own there and no store is waited for.
 template <class C>
 WB_DEV void epi_staged_tile(const CUtensorMap* map_c, const CUtensorMap* map_cw, uint32_t tbase, uint32_t my_staging, int row, int col, int q, uint32_t lane,
-                            bool add, uint32_t acc_empty_addr, uint32_t wide = 0, unsigned long long* prof = nullptr) {
+                            bool add, uint32_t acc_empty_addr, uint64_t policy, uint32_t wide = 0, unsigned long long* prof = nullptr) {
   uint32_t v[2][C::EPI_ROWS];
   long long t_ld = 0, t_copy = 0, t_sts = 0, t_tma = 0, t0 = 0;
   epi_load<C>(tbase, 0, v[0]);
@@ -363,11 +364,11 @@ WB_DEV void epi_staged_tile(const CUtensorMap* map_c, const CUtensorMap* map_cw,
     __syncwarp();
     if (prof) t_sts += clock64() - t0, t0 = clock64();
     if (wide == 0u) {
-      tma_store_commit_if(lane == 0 ? 1u : 0u, add ? 1u : 0u, map_c, x, y, copy);
+      tma_store_commit_if(lane == 0 ? 1u : 0u, add ? 1u : 0u, map_c, x, y, copy, policy);
     } else if ((i + 1) % C::WIDE_BLKS == 0) {
       // the last WIDE_BLKS blocks are WIDE_ROWS consecutive rows of C and of the ring: one store
       tma_store_commit_if(lane == 0 ? 1u : 0u, add ? 1u : 0u, map_cw, x, y - (C::WIDE_BLKS - 1) * C::EPI_ROWS,
-                          copy - uint32_t(C::WIDE_BLKS - 1) * C::EPI_COPY_BYTES);
+                          copy - uint32_t(C::WIDE_BLKS - 1) * C::EPI_COPY_BYTES, policy);
     }
     if (prof) t_tma += clock64() - t0;
   }
@@ -394,10 +395,10 @@ WB_DEV void epi_direct_tile(const KParams& p, uint32_t tbase, int row, int col, 
     int y, x;
     epi_coords<C>(row, col, q, i, y, x);
     float* dst = p.C + size_t(y) * size_t(p.N) + size_t(x) + lane;
-    const bool col_ok = (x + int(lane)) < p.N;
+    // whole tiles only (the host refuses the store from the registers otherwise): no bounds to test
+    const size_t ld = size_t(p.N);
 #pragma unroll
-    for (int j = 0; j < C::EPI_ROWS; ++j)
-      if (col_ok && (y + j) < p.M) dst[size_t(j) * size_t(p.N)] = __uint_as_float(v[i & 1][j]);
+    for (int j = 0; j < C::EPI_ROWS; ++j) dst[size_t(j) * ld] = __uint_as_float(v[i & 1][j]);
   }
 }
 
@@ -498,6 +499,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       uint32_t stage = 0, phase = 0;
       int nth = 0;
       bool ok = true;
+      const uint64_t load_policy = (((p.debug >> 4) ^ uint32_t(p.l2_hints)) & 2u) ? l2_policy_evict_last() : l2_policy_evict_normal();
       const uint32_t full_leader0 = (CG == 2) ? mapa(full_bar(0), 0) : full_bar(0);
       for (; ok && have; have = ok && walk.template next<false>(w)) {
         if (nth != 0) tile_origin<C>(p, w.tile, row, col);
@@ -511,14 +513,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           if (ksub == 2)
             gave_up = load_rounds<CG, 2>(1u, kleft, uint32_t(rounds), stage, phase, x, empty_bar(0), full_bar(0), full_leader0, leader ? 1u : 0u,
                                          C::TX_BYTES, ring, 2u * C::STAGE_BYTES, uint32_t(C::A_BYTES), &map_a, a_row, &map_b, col, 1u << 14, p.debug,
-                                         uint32_t(C::STAGE_BYTES));
+                                         uint32_t(C::STAGE_BYTES), load_policy);
           else if (ksub == 4)
             gave_up = load_rounds<CG, 4>(1u, kleft, uint32_t(rounds), stage, phase, x, empty_bar(0), full_bar(0), full_leader0, leader ? 1u : 0u,
                                          C::TX_BYTES, ring, 4u * C::STAGE_BYTES, uint32_t(C::A_BYTES), &map_a, a_row, &map_b, col, 1u << 14, p.debug,
-                                         uint32_t(C::STAGE_BYTES));
+                                         uint32_t(C::STAGE_BYTES), load_policy);
           else
             gave_up = load_k_loop<CG>(1u, kleft, uint32_t(rounds), stage, phase, x, empty_bar(0), full_bar(0), full_leader0, leader ? 1u : 0u,
-                                      C::TX_BYTES, ring, uint32_t(C::STAGE_BYTES), uint32_t(C::A_BYTES), &map_a, a_row, &map_b, col, 1u << 14, p.debug);
+                                      C::TX_BYTES, ring, uint32_t(C::STAGE_BYTES), uint32_t(C::A_BYTES), &map_a, a_row, &map_b, col, 1u << 14, p.debug, load_policy);
           if (gave_up != 0u && !wait_bar<false, false>(p, abort_addr, empty_bar(int(stage)), phase ^ 1u, ST_WAIT_EMPTY, stage)) {
             ok = false;
             break;
@@ -630,6 +632,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     uint32_t acc_phase = 0;
     bool ok = true;
     const uint32_t acc_empty_leader = (CG == 2) ? mapa(acc_empty_bar(0), 0) : acc_empty_bar(0);
+    // (timing experiments: debug bits 4 and 5 flip the plan's two L2 hints)
+    const uint64_t store_policy = (((p.debug >> 4) ^ uint32_t(p.l2_hints)) & 1u) ? l2_policy_evict_first() : l2_policy_evict_normal();
     const uint32_t my_staging = staging + uint32_t(q) * uint32_t(C::EPI_COPIES) * C::EPI_COPY_BYTES;
     // K split between CTAs (split-K over the grid, stream-K): hand-off words count launches,
     // never reset: every CTA's own word holds how many launches have gone by, so one past it
@@ -659,7 +663,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         if (first_warp && lane == 0) stamp(p, EV_ACC_READY, nth);
         // timing runs: the first warp's cycles in each part of the tile's store, events 11-14
         unsigned long long* prof = (p.stamps != nullptr && first_warp && nth < 4) ? p.stamps + (size_t(blockIdx.x) * 64 + 11) * 4 + nth : nullptr;
-        epi_staged_tile<C>(&map_c, &map_cw, tbase, my_staging, row, col, q, lane, false, acc_empty_addr, wide, prof);
+        epi_staged_tile<C>(&map_c, &map_cw, tbase, my_staging, row, col, q, lane, false, acc_empty_addr, store_policy, wide, prof);
       } else if (p.sched == SCHED_SPLITK) {
         // ---- split-K over the grid, adding in the L2 (gemm_swapped.ml:660-710).  The S runs
         // of a tile first zero disjoint shares of it (while their k loops run), raise their
@@ -700,7 +704,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         fence_proxy_async_global();
         named_bar_sync(2, 128);
         ok = ok && (ld_shared_u32(abort_addr) == 0u);
-        if (ok) epi_staged_tile<C>(&map_c, &map_cw, tbase, my_staging, row, col, q, lane, true, acc_empty_addr, wide);
+        if (ok) epi_staged_tile<C>(&map_c, &map_cw, tbase, my_staging, row, col, q, lane, true, acc_empty_addr, store_policy, wide);
       } else {
         // ---- stream-K, adding in the L2 (gemm_swapped.ml:633-659): the segment holding the
         // tile's first k-step stores and raises the tile's flag; the others wait for it and add.
@@ -708,7 +712,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         if (w.kb == 0) {
           ok = wait_bar(p, abort_addr, acc_full_bar(acc), acc_phase, ST_WAIT_ACC_FULL, uint32_t(acc));
           tc_fence_after();
-          if (ok) epi_staged_tile<C>(&map_c, &map_cw, tbase, my_staging, row, col, q, lane, false, acc_empty_addr, wide);
+          if (ok) epi_staged_tile<C>(&map_c, &map_cw, tbase, my_staging, row, col, q, lane, false, acc_empty_addr, store_policy, wide);
           if (lane == 0) {
             bulk_wait<0>();
             fence_proxy_async_global();
@@ -725,7 +729,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           ok = ok && (ld_shared_u32(abort_addr) == 0u);
           ok = ok && wait_bar(p, abort_addr, acc_full_bar(acc), acc_phase, ST_WAIT_ACC_FULL, uint32_t(acc));
           tc_fence_after();
-          if (ok) epi_staged_tile<C>(&map_c, &map_cw, tbase, my_staging, row, col, q, lane, true, acc_empty_addr, wide);
+          if (ok) epi_staged_tile<C>(&map_c, &map_cw, tbase, my_staging, row, col, q, lane, true, acc_empty_addr, store_policy, wide);
         }
       }
       if (!ok) break;

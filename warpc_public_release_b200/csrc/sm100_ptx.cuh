@@ -339,17 +339,34 @@ WB_DEV void tma_load_2d_if(uint32_t issuer, uint32_t dst, const void* map, int x
   }
 }
 // store (add == 0) or reducing store (add != 0) of one staged box, then close the bulk group
-WB_DEV void tma_store_commit_if(uint32_t issuer, uint32_t add, const void* map, int x, int y, uint32_t src) {
+// `policy`: an L2 cache policy (l2_policy_*): C is written once and not read again by this
+// kernel, so its lines are the first the L2 should give up.
+WB_DEV void tma_store_commit_if(uint32_t issuer, uint32_t add, const void* map, int x, int y, uint32_t src, uint64_t policy) {
   asm volatile(
       "{\n\t.reg .pred e, s, r;\n\t"
       "setp.ne.u32 e, %0, 0;\n\t"
       "setp.eq.and.u32 s, %1, 0, e;\n\t"
       "setp.ne.and.u32 r, %1, 0, e;\n\t"
-      "@s cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%2, {%3, %4}], [%5];\n\t"
-      "@r cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%2, {%3, %4}], [%5];\n\t"
+      "@s cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%2, {%3, %4}], [%5], %6;\n\t"
+      "@r cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group.L2::cache_hint [%2, {%3, %4}], [%5], %6;\n\t"
       "@e cp.async.bulk.commit_group;\n\t}" ::"r"(issuer),
-      "r"(add), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(src)
+      "r"(add), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(src), "l"(policy)
       : "memory");
+}
+WB_DEV uint64_t l2_policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+WB_DEV uint64_t l2_policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+WB_DEV uint64_t l2_policy_evict_normal() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
+  return p;
 }
 template <int CG>
 WB_DEV void umma_f16_if(uint32_t issuer, uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
@@ -490,7 +507,7 @@ WB_DEV uint32_t mma_k_loop(uint32_t issuer, uint32_t& kleft, uint32_t depth, uin
 template <int CG>
 WB_DEV uint32_t load_k_loop(uint32_t issuer, uint32_t& kleft, uint32_t depth, uint32_t& stage, uint32_t& phase, int& x, uint32_t empty0,
                             uint32_t full0, uint32_t full_remote0, uint32_t is_leader, uint32_t tx, uint32_t ring, uint32_t stage_bytes,
-                            uint32_t a_bytes, const void* map_a, int a_row, const void* map_b, int col, uint32_t limit, uint32_t debug = 0) {
+                            uint32_t a_bytes, const void* map_a, int a_row, const void* map_b, int col, uint32_t limit, uint32_t debug, uint64_t policy) {
   uint32_t status;
 #define WB_LD_BODY(CGQ)                                                                                          \
   "{\n\t.reg .pred e, ei, pl, pn, p, q, w, c;\n\t.reg .b32 n, eb, fl, fr, sa, sb, par, dbg;\n\t"                 \
@@ -507,8 +524,8 @@ WB_DEV uint32_t load_k_loop(uint32_t issuer, uint32_t& kleft, uint32_t depth, ui
   "@pl mbarrier.arrive.expect_tx.shared::cta.b64 _, [fl], %11;\n\t"                                              \
   "@pn mbarrier.arrive.shared::cta.b64 _, [fl];\n\t"                                                             \
   "add.u32 sb, sa, %14;\n\t"                                                                                     \
-  "@e cp.async.bulk.tensor.2d" CGQ ".shared::cluster.global.mbarrier::complete_tx::bytes [sa], [%15, {%4, %16}], [fr];\n\t" \
-  "@e cp.async.bulk.tensor.2d" CGQ ".shared::cluster.global.mbarrier::complete_tx::bytes [sb], [%17, {%4, %18}], [fr];\n\t" \
+  "@e cp.async.bulk.tensor.2d" CGQ ".shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [sa], [%15, {%4, %16}], [fr], %21;\n\t" \
+  "@e cp.async.bulk.tensor.2d" CGQ ".shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [sb], [%17, {%4, %18}], [fr], %21;\n\t" \
   "add.s32 %4, %4, 64;\n\tadd.u32 %1, %1, 1;\n\tadd.u32 eb, eb, 8;\n\tadd.u32 fl, fl, 8;\n\tadd.u32 fr, fr, 8;\n\tadd.u32 sa, sa, %13;\n\t" \
   "setp.eq.u32 w, %1, %6;\n\t"                                                                                   \
   "@w mov.u32 %1, 0;\n\t@w mov.u32 eb, %7;\n\t@w mov.u32 fl, %8;\n\t@w mov.u32 fr, %9;\n\t@w mov.u32 sa, %12;\n\t@w xor.b32 %2, %2, 1;\n\t" \
@@ -517,7 +534,8 @@ WB_DEV uint32_t load_k_loop(uint32_t issuer, uint32_t& kleft, uint32_t depth, ui
 #define WB_LD_ARGS                                                                                               \
   : "=r"(status), "+r"(stage), "+r"(phase), "+r"(kleft), "+r"(x)                                                 \
   : "r"(issuer), "r"(depth), "r"(empty0), "r"(full0), "r"(full_remote0), "r"(is_leader), "r"(tx), "r"(ring), "r"(stage_bytes), \
-    "r"(a_bytes), "l"(reinterpret_cast<uint64_t>(map_a)), "r"(a_row), "l"(reinterpret_cast<uint64_t>(map_b)), "r"(col), "r"(debug), "r"(limit) \
+    "r"(a_bytes), "l"(reinterpret_cast<uint64_t>(map_a)), "r"(a_row), "l"(reinterpret_cast<uint64_t>(map_b)), "r"(col), "r"(debug), "r"(limit), \
+    "l"(policy)                                                                                                  \
   : "memory"
   if constexpr (CG == 2) asm volatile(WB_LD_BODY(".cta_group::2") WB_LD_ARGS);
   else asm volatile(WB_LD_BODY("") WB_LD_ARGS);
@@ -611,13 +629,13 @@ template <int CG, int KSUB>
 WB_DEV uint32_t load_rounds(uint32_t issuer, uint32_t& kleft, uint32_t depth, uint32_t& stage, uint32_t& phase, int& x, uint32_t empty0,
                             uint32_t full0, uint32_t full_remote0, uint32_t is_leader, uint32_t tx, uint32_t ring, uint32_t stage_bytes,
                             uint32_t a_bytes, const void* map_a, int a_row, const void* map_b, int col, uint32_t limit, uint32_t debug,
-                            uint32_t slot_bytes) {
+                            uint32_t slot_bytes, uint64_t policy) {
   static_assert(KSUB == 2 || KSUB == 4, "rounds of two or four k-steps");
   uint32_t status;
 #define WB_LR_LOADS(CGQ, GUARD)                                                                                  \
   "add.u32 sb, sg, %14;\n\t"                                                                                     \
-  "@" GUARD " cp.async.bulk.tensor.2d" CGQ ".shared::cluster.global.mbarrier::complete_tx::bytes [sg], [%15, {xg, %16}], [fr];\n\t" \
-  "@" GUARD " cp.async.bulk.tensor.2d" CGQ ".shared::cluster.global.mbarrier::complete_tx::bytes [sb], [%17, {xg, %18}], [fr];\n\t" \
+  "@" GUARD " cp.async.bulk.tensor.2d" CGQ ".shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [sg], [%15, {xg, %16}], [fr], %22;\n\t" \
+  "@" GUARD " cp.async.bulk.tensor.2d" CGQ ".shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [sb], [%17, {xg, %18}], [fr], %22;\n\t" \
   "add.u32 sg, sg, %21;\n\tadd.s32 xg, xg, 64;\n\t"
 #define WB_LR_BODY(CGQ, KSUB_S, MORE)                                                                            \
   "{\n\t.reg .pred e, e1, e2, e3, ei, pl, pn, p, q, w, c;\n\t.reg .b32 n, eb, fl, fr, sa, sb, sg, xg, par, dbg, use, txr;\n\t" \
@@ -646,7 +664,7 @@ WB_DEV uint32_t load_rounds(uint32_t issuer, uint32_t& kleft, uint32_t depth, ui
   : "=r"(status), "+r"(stage), "+r"(phase), "+r"(kleft), "+r"(x)                                                 \
   : "r"(issuer), "r"(depth), "r"(empty0), "r"(full0), "r"(full_remote0), "r"(is_leader), "r"(tx), "r"(ring), "r"(stage_bytes), \
     "r"(a_bytes), "l"(reinterpret_cast<uint64_t>(map_a)), "r"(a_row), "l"(reinterpret_cast<uint64_t>(map_b)), "r"(col), "r"(debug), "r"(limit), \
-    "r"(slot_bytes)                                                                                              \
+    "r"(slot_bytes), "l"(policy)                                                                                 \
   : "memory"
   if constexpr (CG == 2 && KSUB == 2) asm volatile(WB_LR_BODY(".cta_group::2", "2", "") WB_LR_ARGS);
   if constexpr (CG == 2 && KSUB == 4) asm volatile(WB_LR_BODY(".cta_group::2", "4", WB_LR_LOADS(".cta_group::2", "e2") WB_LR_LOADS(".cta_group::2", "e3")) WB_LR_ARGS);
