@@ -66,6 +66,7 @@ typedef struct wg_launch_info {
   int ksub, rounds;        /* the ring is handed over ksub k-steps (slots) at a time: rounds = depth / ksub barrier pairs */
   int wide_rows;           /* C rows per store of a CTA's last tile when it is staged whole in the drained ring, else 0 */
   int stage_bytes;         /* one ring slot: this CTA's A half-tile and B^T tile of one k-step */
+  int staging_bytes;       /* the epilogue's cycling staging copies; 0 where every tile is staged in the drained ring */
 } wg_launch_info;
 
 /* `warpc gemm M N K`: the program chosen for a shape (backend/programs.ml:46-80).

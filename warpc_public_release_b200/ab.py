@@ -178,7 +178,10 @@ def ab_shape(torch, timer, m, n, k, inputs="hash", rounds=2, variant=None, busy_
     err = float((c_lib - c_ours).abs().max().item())
     flops = 2.0 * m * n * k
     mid = lambda xs: (min(xs) + max(xs)) / 2
-    row = {"shape": [m, n, k], "inputs": inputs, "program": "%dx%d d%d" % (v.tile_m, v.tile_n, v.depth), "calls_in_median": last,
+    li = programs.realise(v, m, n, k)
+    sched = ("one tile a CTA", "fixed grid", "launch control", "split-K", "stream-K")[li.sched]
+    row = {"shape": [m, n, k], "inputs": inputs, "program": "%dx%d d%d" % (v.tile_m, v.tile_n, v.depth),
+           "runs_as": "%dx%d d%d %s" % (li.tile_m, li.tile_n, li.depth, sched), "calls_in_median": last,
            "ours_us": [min(ours), max(ours)], "cublaslt_us": [min(lib), max(lib)], "cublaslt_algo": best,
            "cublaslt_correct_algos": "%d of %d" % (correct, lt.n_algos), "cublaslt_version": lt.version,
            "cublaslt_kernels": lib_kernels, "ours_tflops": flops / mid(ours) / 1e6, "cublaslt_tflops": flops / mid(lib) / 1e6,
@@ -202,12 +205,12 @@ def main(argv=None):
     shapes = [tuple(args.dims[i:i + 3]) for i in range(0, len(args.dims), 3)] or [s for s in SHAPES if s != (16384, 16384, 16384)]
     timer = KernelTimer()
     rows = []
-    print("%-18s %-12s %17s %17s %8s   %s" % ("M x N x K", "program", "ours us", "cuBLASLt us", "vs lib", "published warpc / cuBLAS 13.8 us"))
+    print("%-18s %-12s %-28s %17s %17s %8s   %s" % ("M x N x K", "rule's program", "runs as", "ours us", "cuBLASLt us", "vs lib", "published warpc / cuBLAS 13.8 us"))
     for (m, n, k) in shapes:
         row = ab_shape(torch, timer, m, n, k, inputs=args.inputs, rounds=args.rounds)
         rows.append(row)
-        print("%-18s %-12s %8.2f-%-8.2f %8.2f-%-8.2f %+7.1f%%   %s / %s" % (
-            "%dx%dx%d" % (m, n, k), row["program"], *row["ours_us"], *row["cublaslt_us"], row["ours_vs_cublaslt_pct"],
+        print("%-18s %-12s %-28s %8.2f-%-8.2f %8.2f-%-8.2f %+7.1f%%   %s / %s" % (
+            "%dx%dx%d" % (m, n, k), row["program"], row["runs_as"], *row["ours_us"], *row["cublaslt_us"], row["ours_vs_cublaslt_pct"],
             row["published_warpc_us"], row["published_cublas138_us"]), flush=True)
         if args.json:
             json.dump({"method": "CUPTI kernel start-to-end, each call alone, median of the last N, ours/lib/lib/ours x %d" % args.rounds,

@@ -25,6 +25,7 @@ wb_kernel_entry entry(int id, const char* name) {
   e.id = id, e.cg = C::CG, e.tile_m = C::TM, e.tile_n = C::TN, e.direct = C::DIRECT ? 1 : 0;
   e.reps = C::REPS, e.epi_rows = C::EPI_ROWS, e.wide_rows = C::WIDE_ROWS, e.ncols = C::NCOLS, e.stage_bytes = C::STAGE_BYTES;
   e.smem_fixed = C::smem_bytes(0);
+  e.staging_bytes = C::STAGING_BYTES;
   e.name = name;
   e.fn = reinterpret_cast<const void*>(&gemm_kernel<C>);
   return e;
@@ -158,6 +159,7 @@ int fill_plan(Plan* pl, int device, const wg_variant* v, int M, int N, int K, co
   p.split = li.split;
   p.ksub = li.ksub, p.rounds = li.rounds;
   p.l2_hints = l2_hints_for(li, M, N, K);
+  p.staging_bytes = li.staging_bytes;
   p.late_launch = v->late_launch;
   p.epi_ring = li.wide_rows != 0;
   if (li.sched == SCHED_STREAMK) {
@@ -452,6 +454,7 @@ extern "C" int wg_launch_noalloc(int device, const wg_variant* v, int M, int N, 
   p.depth = li.depth, p.nbuf = li.nbuf, p.sched = li.sched, p.ask_ahead = li.ask_ahead, p.split = li.split;
   p.ksub = li.ksub, p.rounds = li.rounds;
   p.l2_hints = l2_hints_for(li, M, N, K);
+  p.staging_bytes = li.staging_bytes;
   p.late_launch = v->late_launch;
   p.epi_ring = li.wide_rows != 0;
   if (li.sched == SCHED_STREAMK) {

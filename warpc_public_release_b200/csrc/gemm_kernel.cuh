@@ -52,6 +52,7 @@ struct KParams {
   int ask_ahead;  // probe the next stage before releasing this one
   int split;      // SCHED_SPLITK: runs of K per tile
   int sk_q, sk_r, sk_clusters;  // SCHED_STREAMK: units = q * clusters + r
+  int staging_bytes;            // the cycling staging copies (0: every tile is a CTA's last and is staged in the ring)
   int l2_hints;                 // bit 0: C's lines leave the L2 first; bit 1: operand lines leave it last
   int late_launch;              // the next grid in the stream is let go when the producer's last load is out, not at entry
   int ksub, rounds;             // the ring is handed over `ksub` k-steps (slots) at a time: rounds = depth / ksub barrier pairs
@@ -412,7 +413,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t ring = smem_base;
   const uint32_t staging = ring + uint32_t(p.depth) * C::STAGE_BYTES;
-  const uint32_t ctrl = staging + C::STAGING_BYTES;
+  const uint32_t ctrl = staging + uint32_t(p.staging_bytes);
   auto ctrl_at = [&](size_t off) { return ctrl + uint32_t(off); };
   const uint32_t abort_addr = ctrl_at(offsetof(Ctrl, abort));
 

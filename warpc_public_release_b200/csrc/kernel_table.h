@@ -12,6 +12,7 @@ struct wb_kernel_entry {
   int ncols;           // tensor-memory columns of one accumulator
   int stage_bytes;     // shared memory of one ring stage
   size_t smem_fixed;   // alignment slack + staging + control block
+  int staging_bytes;   // the epilogue warps' cycling staging copies (part of smem_fixed)
   const char* name;
   const void* fn;      // the __global__ function
 };

@@ -314,13 +314,27 @@ extern "C" int wg_realise(const wg_variant* v, int M, int N, int K, wg_launch_in
   li.tmem_cols = e->ncols * li.nbuf > 32 ? pow2_cols(e->ncols * li.nbuf) : 32;
   if (e->ncols * li.nbuf > 512) return WG_E_VARIANT;
   // this kernel's staging copies and control block are larger than the reference's: where the
-  // reference's ring depth no longer fits beside them, the ring is one or two stages shorter
-  while (li.depth > 2 && e->smem_fixed + size_t(li.depth) * e->stage_bytes > 232448) li.depth -= 1;
-  // the rule's own programs take the deepest ring that fits: ring slack against L2 latency is what the
-  // k loop's pace depends on most (256 x 128: 560 cycles a k-step at depth 6, 620 at 5, 750 at 4)
-  if (v->retile && v->prog == WG_PROG_SWAPPED)
-    while (li.depth < 16 && e->smem_fixed + size_t(li.depth + 1) * e->stage_bytes <= 232448) li.depth += 1;
-  li.dynsmem = int(e->smem_fixed + size_t(li.depth) * e->stage_bytes);
+  // reference's ring depth no longer fits beside them, the ring is one or two stages shorter.
+  // Shared memory beside the ring: alignment slack, control block and the epilogue's cycling staging
+  // copies -- which a launch of one tile a CTA never uses when the ring can hold the tile (every tile is
+  // then its CTA's last and is staged in the drained ring), so there the ring gets their room as well
+  auto fit_depth = [&](size_t fixed, int depth) {
+    while (depth > 2 && fixed + size_t(depth) * e->stage_bytes > 232448) depth -= 1;
+    // the rule's own programs take the deepest ring that fits: ring slack against L2 latency is what the
+    // k loop's pace depends on most (256 x 128: 560 cycles a k-step at depth 6, 620 at 5, 750 at 4)
+    if (v->retile && v->prog == WG_PROG_SWAPPED)
+      while (depth < 16 && fixed + size_t(depth + 1) * e->stage_bytes <= 232448) depth += 1;
+    return depth;
+  };
+  size_t fixed = e->smem_fixed;
+  li.staging_bytes = e->staging_bytes;
+  if (!li.direct && li.sched == 0 && e->staging_bytes > 0) {
+    const size_t without = e->smem_fixed - size_t(e->staging_bytes);
+    const int d = fit_depth(without, li.depth);
+    if (size_t(d) * size_t(e->stage_bytes) >= size_t(li.tile_m) * size_t(li.tile_n) * 4) fixed = without, li.staging_bytes = 0;
+  }
+  li.depth = fit_depth(fixed, li.depth);
+  li.dynsmem = int(fixed + size_t(li.depth) * e->stage_bytes);
   if (li.dynsmem > 232448 || li.depth > 16) return WG_E_VARIANT;
   li.a_box_rows = li.tile_m / li.cg;
   li.bt_box_rows = li.tile_n;
