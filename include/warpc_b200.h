@@ -116,14 +116,17 @@ void* wg_host_plan_buffer(void* plan, int which);
  * stream after `warmup` untimed ones (backend/node/run_tma.py:171-175, backend/node/cuda.py:79-92). */
 int wg_time_launches(void* plan, int warmup, int repeat, float* ms_mean);
 
-/* Timing builds (the reference's: backend/stamp.ml:9-16, decoded in run_tma.py:176-192): turn
- * per-phase stamps on or off for the launches that follow, and read them back: 32 events x
- * 4 tiles per CTA (GPU nanosecond timer; events 11-14 and 16-20 are cycle sums), grid*256 words (the second half: four 32-entry per-stage cycle traces of the first tile); returns the words written. */
 /* Dependent launch (backend/node/clusterlaunch.py:54-74 `pdl`, the AB_PDL mode of backend/node/ab.py:95-118): launches
  * that follow carry the programmatic-stream-serialization attribute, so a launch may begin while the one before it
  * in the stream runs; the kernel waits (griddepcontrol.wait) before it touches global memory. Off by default. */
 int wg_plan_set_dependent_launch(void* plan, int on);
 
+/* Timing builds (the reference's: backend/stamp.ml:9-16, decoded in run_tma.py:176-192): turn per-phase stamps on or
+ * off for the launches that follow, and read them back: grid * 256 words, 64 events x 4 tiles per CTA. Events 0-10
+ * and 16-21 are times on the GPU nanosecond timer (entry, set-up, first/last load, first/last MMA, accumulator ready,
+ * stored, roles done, exit, accumulator free; barriers initialised, tensor memory allocated, first tile found, last
+ * stores read, CTAs met, tensor memory freed); 11-14 cycle sums of the first epilogue warp; 15 cycles entry to exit.
+ * wg_plan_read_stamps synchronises and returns the words written. */
 int wg_plan_enable_stamps(void* plan, int on);
 int wg_plan_read_stamps(void* plan, unsigned long long* out, size_t cap_words);
 

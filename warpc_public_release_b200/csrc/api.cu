@@ -342,7 +342,7 @@ extern "C" int wg_time_launches(void* plan, int warmup, int repeat, float* ms_me
   return r;
 }
 
-// Timing runs: phase stamps (per CTA: 32 events x 4 tiles on the GPU nanosecond timer or as cycle sums, then four 32-entry per-stage cycle traces of the first tile) of the
+// Timing runs: phase stamps (per CTA 64 events x 4 tiles, times on the GPU nanosecond timer or cycle sums) of the
 // launches that follow; wg_plan_read_stamps synchronises and copies grid*256 words out.
 extern "C" int wg_plan_enable_stamps(void* plan, int on) {
   Plan* pl = static_cast<Plan*>(plan);

@@ -149,11 +149,6 @@ enum : int { EV_ENTRY = 0, EV_SETUP = 1, EV_LOAD_FIRST = 2, EV_LOAD_LAST = 3, EV
 WB_DEV void stamp_value(const KParams& p, int ev, int slot, long long value) {
   if (p.stamps != nullptr && slot < 4) p.stamps[(size_t(blockIdx.x) * 64 + ev) * 4 + slot] = (unsigned long long)value;
 }
-// per-stage trace of a CTA's first tile: SM cycle counter at k-step `kk` (< 32) of trace `which`
-// (0 producer saw the slot empty, 1 producer issued, 2 MMA warp saw it full, 3 MMA warp issued)
-WB_DEV void trace(const KParams& p, int which, int kk) {
-  if (p.stamps != nullptr && kk < 32) p.stamps[size_t(blockIdx.x) * 256 + 128 + which * 32 + kk] = (unsigned long long)clock64();
-}
 WB_DEV void stamp(const KParams& p, int ev, int slot) {
   if (p.stamps != nullptr && slot < 4) p.stamps[(size_t(blockIdx.x) * 64 + ev) * 4 + slot] = globaltimer();
 }
@@ -423,8 +418,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   const uint32_t warp = warp_uniform(threadIdx.x >> 5), lane = threadIdx.x & 31;
   const uint32_t rank = (CG == 2) ? warp_uniform(cluster_ctarank()) : 0u;
   const bool leader = (rank == 0);
-  const uint32_t issuer = (lane == 0) ? 1u : 0u;  // the lane that issues its warp's single-lane instructions
-  const int depth = p.depth, nbuf = p.nbuf, rounds = p.rounds, ksub = p.ksub;
+  const int nbuf = p.nbuf, rounds = p.rounds, ksub = p.ksub;
   const long long cycles_at_entry = clock64();
   // Dependent launch (the reference's PREEXIT / ACQBULK, backend/sass.ml:496-502, gemm_swapped.ml:169-172, 232, 368):
   // under the programmatic-stream-serialization launch attribute the next grid in the stream may

@@ -61,17 +61,6 @@ class _Base:
             check(r, "wg_plan_read_stamps")
         return np.frombuffer(buf, dtype=np.uint64).reshape(grid, 64, 4)[:, :32, :].copy()
 
-    def read_stage_traces(self):
-        """Per-stage SM-cycle traces of each CTA's first tile: array [grid, 4, 32] -- producer saw
-        the slot empty, producer issued, MMA warp saw it full, MMA warp issued (0 = not reached)."""
-        import numpy as np
-        grid = self.info().grid
-        buf = (ctypes.c_ulonglong * (grid * 256))()
-        r = _lib.lib().wg_plan_read_stamps(self._h, buf, grid * 256)
-        if r < 0:
-            check(r, "wg_plan_read_stamps")
-        return np.frombuffer(buf, dtype=np.uint64).reshape(grid, 256)[:, 128:].reshape(grid, 4, 32).copy()
-
     def status(self):
         """Synchronise and raise DeviceWaitError if any launch gave up."""
         st = (ctypes.c_uint * 4)()
