@@ -22,15 +22,12 @@ def slab_rows(m, world, rank):
 def slab_variant(m_local, n, k, pin_large=True):
     """The program for one GPU's (M/g) x N x K share.  The rule falls back to 192 x 128 tiles
     once min(M/g, N, K) < 8192; a slab that still holds whole 256 x 256 pair tiles keeps the
-    large-shape program (cluster launch control, serpentine walk, asking ahead)."""
+    large-shape program (cluster launch control, serpentine walk, asking ahead).  (Dealing a poorly
+    filled last wave's k-steps out stream-K does not pay at this tile: 2048 x 16384 x 16384, 3.46 waves,
+    measured 965 us against 757 us -- the partial tiles' 256 KB stores are exposed and clusters stop
+    sharing operand panels in step.)"""
     if pin_large and m_local % 256 == 0 and n % 512 == 0 and k % 64 == 0 and min(n, k) >= 8192 and \
             (m_local // 256) * (n // 256) >= 148:
-        # 74 pairs fit the machine: when the slab's pair tiles leave the last wave under 93 % full and K is long,
-        # the tiles' k-steps are dealt evenly to the pairs instead (stream-K), e.g. 2048 x 16384 x 16384 = 3.46 waves
-        tiles = (m_local // 256) * (n // 512)
-        waves = -(-tiles // 74)
-        if tiles > 74 and tiles < 0.93 * waves * 74 and k // 64 >= 64:
-            return programs.swapped(m_local, n, k, 256, 256, 4, streamk=True, split_add=True)
         return programs.swapped(m_local, n, k, 256, 256, 4, clc=True, ask_ahead=True, serpentine=True)
     return programs.choose(m_local, n, k)
 
