@@ -145,7 +145,8 @@ WB_DEV void record_failure(const KParams& p, uint32_t code, uint32_t detail, uin
 enum : int { EV_ENTRY = 0, EV_SETUP = 1, EV_LOAD_FIRST = 2, EV_LOAD_LAST = 3, EV_MMA_FIRST = 4, EV_MMA_LAST = 5,
              EV_ACC_READY = 6, EV_STORED = 7, EV_TEARDOWN = 8, EV_EXIT = 9, EV_ACC_FREE = 10 };
 // 11-14: cycle sums of the first epilogue warp, 15: cycles entry to exit; 16 barriers initialised, 17 tensor memory
-// allocated, 18 first tile found, 19 last stores have read their copies, 20 CTAs met at teardown, 21 tensor memory freed
+// allocated, 18 first tile found, 19 last stores have read their copies, 20 CTAs met at teardown, 21 tensor memory freed; 22: cycles issuing the tcgen05.ld
+// of the next block and releasing the accumulator (first epilogue warp)
 WB_DEV void stamp_value(const KParams& p, int ev, int slot, long long value) {
   if (p.stamps != nullptr && slot < 4) p.stamps[(size_t(blockIdx.x) * 64 + ev) * 4 + slot] = (unsigned long long)value;
 }
@@ -326,13 +327,16 @@ template <class C>
 WB_DEV void epi_staged_tile(const CUtensorMap* map_c, const CUtensorMap* map_cw, uint32_t tbase, uint32_t my_staging, int row, int col, int q, uint32_t lane,
                             bool add, uint32_t acc_empty_addr, uint64_t policy, uint32_t wide = 0, unsigned long long* prof = nullptr) {
   uint32_t v[2][C::EPI_ROWS];
-  long long t_ld = 0, t_copy = 0, t_sts = 0, t_tma = 0, t0 = 0;
+  long long t_ld = 0, t_copy = 0, t_sts = 0, t_tma = 0, t_issue = 0, t0 = 0;
+  if (prof) t0 = clock64();
   epi_load<C>(tbase, 0, v[0]);
+  if (prof) t_issue += clock64() - t0;
 #pragma unroll
   for (int i = 0; i < C::NBLK; ++i) {
     if (prof) t0 = clock64();
     tmem_wait_ld();
     if (prof) t_ld += clock64() - t0;
+    if (prof) t0 = clock64();
     if (i + 1 < C::NBLK) {
       epi_load<C>(tbase, i + 1, v[(i + 1) & 1]);
     } else {
@@ -341,6 +345,7 @@ WB_DEV void epi_staged_tile(const CUtensorMap* map_c, const CUtensorMap* map_cw,
       if constexpr (C::CG == 2) mbar_arrive_cluster_if(lane == 0 ? 1u : 0u, acc_empty_addr);
       else mbar_arrive_if(lane == 0 ? 1u : 0u, acc_empty_addr);
     }
+    if (prof) t_issue += clock64() - t0;
     int y, x;
     epi_coords<C>(row, col, q, i, y, x);
     // `wide` != 0: this warp's NBLK private copies in the drained ring, nothing to wait for
@@ -368,7 +373,7 @@ WB_DEV void epi_staged_tile(const CUtensorMap* map_c, const CUtensorMap* map_cw,
     }
     if (prof) t_tma += clock64() - t0;
   }
-  if (prof && lane == 0) prof[0] = t_ld, prof[4] = t_copy, prof[8] = t_sts, prof[12] = t_tma;
+  if (prof && lane == 0) prof[0] = t_ld, prof[4] = t_copy, prof[8] = t_sts, prof[12] = t_tma, prof[44] = t_issue;  // events 11-14 and 22
 }
 
 // Straight from the registers: register j of a block is row y + j, the warp's lanes are 32
@@ -556,6 +561,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         stamp(p, EV_ACC_FREE, nth);
         const uint32_t d = tmem_base + uint32_t(acc * C::NCOLS);
         uint32_t kleft = uint32_t(w.ke - w.kb), accumulate = 0;
+        // timing runs: when the tile's first round of operands has landed (the loop's own first poll then passes at once)
+        if (p.stamps != nullptr && !wait_bar<false, false>(p, abort_addr, full_bar(int(stage)), phase, ST_WAIT_FULL, stage)) {
+          ok = false;
+          break;
+        }
         stamp(p, EV_MMA_FIRST, nth);
         while (kleft != 0u) {
           uint32_t gave_up;

@@ -111,7 +111,7 @@ def run(variant, m, n, k, repeat=20, seed=1, name=None, out=sys.stdout):
             mhz = 1e3 * st[ran, 15, 0] / np.maximum(st[ran, 9, 0] - st[ran, 0, 0], 1)
             print("  SM clock over the launch: %.0f MHz (median of CTAs)" % np.median(mhz), file=out)
         # events 11-14: SM cycles the first epilogue warp spent in each part of a tile's store
-        for ev, label in zip(range(11, 15), ("waiting for tcgen05.ld", "waiting for a staging copy", "st.shared + fence", "issuing the TMA store")):
+        for ev, label in zip((11, 12, 13, 14, 22), ("waiting for tcgen05.ld", "waiting for a staging copy", "st.shared + fence", "issuing the TMA store", "issuing tcgen05.ld / release")):
             cells = ["%5d:%7d/%7d/%7d" % (len(c), c.min(), np.median(c), c.max()) if len(c) else " " * 29
                      for c in (st[:, ev, t][st[:, ev, t] > 0] for t in range(4))]
             print("  %2d %-34s %s" % (ev, "epilogue cycles: " + label, "  ".join(cells)), file=out)
