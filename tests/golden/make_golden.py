@@ -1,6 +1,6 @@
 """Generates the golden fixtures in this folder.  Run where the reference is present:
 
-    python tests/golden/make_golden.py [/root/reference]
+    python tests/golden/make_golden.py [REFERENCE_ROOT]
 
 It executes the reference's OWN code, not a restatement of it:
   * inputs_and_products.json -- the input-generation and numpy-check statements of

@@ -137,6 +137,12 @@ def test_realisation_invariants():
         if li.sched == 1:
             assert li.grid == 148
         assert li.group & (li.group - 1) == 0
+        # the ring: rounds of ksub slots, all of it inside the 227 KB a CTA may have
+        assert li.ksub in (1, 2, 4) and li.rounds >= 2 and li.rounds * li.ksub <= li.depth
+        assert li.mbarriers == 2 * li.rounds + 7
+        assert li.dynsmem == 1024 + li.depth * li.stage_bytes + li.staging_bytes + 512 and li.dynsmem <= 232448
+        if li.staging_bytes == 0 and not li.direct:            # no cycling copies: only where every tile is staged in the ring
+            assert li.sched == 0 and li.wide_rows > 0 and li.depth * li.stage_bytes >= li.tile_m * li.tile_n * 4
         if v.prog == 0 and not (v.streamk or v.split_grid > 1 or v.split > 1):
             assert li.direct == 0                                  # the rule's programs run through the staged store
     # an explicitly named tile is the tile run; the rule's choice may be re-tiled for this machine

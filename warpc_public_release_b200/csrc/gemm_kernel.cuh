@@ -145,7 +145,7 @@ WB_DEV void record_failure(const KParams& p, uint32_t code, uint32_t detail, uin
 enum : int { EV_ENTRY = 0, EV_SETUP = 1, EV_LOAD_FIRST = 2, EV_LOAD_LAST = 3, EV_MMA_FIRST = 4, EV_MMA_LAST = 5,
              EV_ACC_READY = 6, EV_STORED = 7, EV_TEARDOWN = 8, EV_EXIT = 9, EV_ACC_FREE = 10 };
 // 11-14: cycle sums of the first epilogue warp, 15: cycles entry to exit; 16 barriers initialised, 17 tensor memory
-// allocated, 18 first tile found, 19 last stores have read their copies, 20 CTAs met at teardown, 21 tensor memory freed; 22: cycles issuing the tcgen05.ld
+// allocated, 18 first tile found, 19 last stores have read their copies, 20 CTAs met at teardown, 21 tensor memory freed; 23 CTAs met at set-up, before the wait on the grid before; 22: cycles issuing the tcgen05.ld
 // of the next block and releasing the accumulator (first epilogue warp)
 WB_DEV void stamp_value(const KParams& p, int ev, int slot, long long value) {
   if (p.stamps != nullptr && slot < 4) p.stamps[(size_t(blockIdx.x) * 64 + ev) * 4 + slot] = (unsigned long long)value;
@@ -483,6 +483,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     __syncthreads();
   }
   tc_fence_after();
+  if (threadIdx.x == 0) stamp(p, 23, 0);
   // nothing above touched global memory (a timing build's entry stamp aside); everything below
   // may read what the grid before this one wrote
   griddep_wait();

@@ -31,7 +31,7 @@ STAMP_NAMES = ["entry", "barriers initialised, cluster met", "producer: first st
                "MMA: first stage landed", "MMA: last stage issued", "epilogue: accumulator ready", "epilogue: tile's stores issued",
                "roles done", "exit", "MMA: accumulator free"]
 FINE_STAMP_NAMES = ["set-up: barriers initialised", "set-up: tensor memory allocated", "set-up: first tile found",
-                    "teardown: last stores read", "teardown: CTAs met", "teardown: tensor memory freed"]
+                    "teardown: last stores read", "teardown: CTAs met", "teardown: tensor memory freed", "set-up: CTAs met"]
 
 
 def make_inputs(m, n, k, seed=1):
@@ -99,7 +99,7 @@ def run(variant, m, n, k, repeat=20, seed=1, name=None, out=sys.stdout):
         plan.enable_stamps(False)
         t0 = st[:, 0, 0][st[:, 0, 0] > 0].min()
         print("  %d CTAs ran; ns from the first CTA's entry: count:min/median/max per tile" % int((st[:, 0, 0] > 0).sum()), file=out)
-        for ev, label in list(enumerate(STAMP_NAMES)) + list(zip(range(16, 22), FINE_STAMP_NAMES)):
+        for ev, label in list(enumerate(STAMP_NAMES)) + list(zip(list(range(16, 22)) + [23], FINE_STAMP_NAMES)):
             cells = []
             for t in range(4):
                 col = st[:, ev, t]
