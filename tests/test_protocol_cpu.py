@@ -61,6 +61,35 @@ def test_the_rules_program_for_a_benchmark_shape(shape):
     assert protocol.check(w.choose(*shape), *shape, seed=0) > 0
 
 
+def test_random_variants_small_shapes():
+    """Tiles, ring depths, accumulator counts and schedules drawn at random (seeded) on small shapes: whatever
+    the geometry functions accept has to run through the model clean."""
+    import random
+    rng = random.Random(7)
+    ran = 0
+    for _ in range(200):
+        tm, tn = rng.choice([(128, 64), (128, 128), (192, 128), (256, 128), (256, 256), (256, 64), (128, 256)])
+        m = tm * rng.randint(1, 5) - rng.choice([0, 0, 0, 64])
+        n = 2 * tn * rng.randint(1, 4)
+        k = 64 * rng.randint(1, 24)
+        kind = rng.choice(["plain", "plain", "clc", "split", "stream"])
+        kw = dict(bufs=rng.choice([None, 1, 2]), group=rng.choice([1, 2, 8]), serpentine=rng.random() < 0.3)
+        if kind == "clc":
+            kw.update(clc=True)
+        elif kind == "split":
+            kw.update(split_grid=rng.randint(2, 5), split_add=True)
+        elif kind == "stream":
+            kw.update(streamk=True, split_add=True, bufs=2)
+        try:
+            v = SW(m, n, k, tm, tn, rng.randint(2, 12), **kw)
+            w.realise(v, m, n, k)
+        except Exception:
+            continue  # a combination the builder refuses
+        assert protocol.check(v, m, n, k, seed=rng.randint(0, 99)) > 0, (m, n, k, tm, tn, kind, kw)
+        ran += 1
+    assert ran >= 40
+
+
 def test_cli(capsys):
     assert protocol.main(["1024", "1024", "1024"]) == 0
     assert "protocol ok" in capsys.readouterr().out
