@@ -95,6 +95,13 @@ def cpu_numpy_sample(m, n, k, rows, repeats=1):
     rng = np.random.default_rng(1)
     a = rng.uniform(-1.0, 1.0, size=(rows, k)).astype(np.float16)
     bt = rng.uniform(-1.0, 1.0, size=(n, k)).astype(np.float16)
+    # every host core the process may use, whatever OMP_NUM_THREADS says (torchrun sets it to 1 for its ranks)
+    want = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    try:
+        from threadpoolctl import threadpool_info, threadpool_limits
+        limit = threadpool_limits(limits=want, user_api="blas")
+    except Exception:
+        threadpool_info, limit = None, None
     best = None
     for _ in range(repeats):
         t0 = time.perf_counter()
@@ -102,14 +109,13 @@ def cpu_numpy_sample(m, n, k, rows, repeats=1):
         dt = time.perf_counter() - t0
         best = dt if best is None else min(best, dt)
     del c
-    threads = os.cpu_count() or 1
-    try:
-        from threadpoolctl import threadpool_info
+    threads = want
+    if threadpool_info is not None:
         blas = [p for p in threadpool_info() if p.get("user_api") == "blas"]
         if blas:
             threads = max(p.get("num_threads", 1) for p in blas)
-    except Exception:
-        pass
+    if limit is not None:
+        limit.restore_original_limits()
     return best, threads
 
 

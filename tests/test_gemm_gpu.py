@@ -66,6 +66,7 @@ CASES = [
     ("split_k_grid_even", (512, 1024, 1024), lambda s: SW(*s, 256, 256, 4, split_grid=4, split_add=True)),
     ("split_k_grid_uneven", (512, 1024, 1088), lambda s: SW(*s, 256, 256, 4, split_grid=3, split_add=True, ask_ahead=True)),
     ("split_k_more_runs_than_blocks", (256, 512, 4096), lambda s: SW(*s, 256, 256, 4, split_grid=37, split_add=True)),
+    ("split_k_workspace_variant", (512, 1024, 4096), lambda s: SW(*s, 256, 256, 4, split_grid=4, direct=True)),  # the reference's ws + FADD form
     ("stream_k", (1024, 512, 1024), lambda s: SW(*s, 256, 128, 6, streamk=True, split_add=True, bufs=2, ask_ahead=True)),
     ("stream_k_long", (1024, 1024, 4096), lambda s: SW(*s, 256, 128, 6, streamk=True, split_add=True, bufs=2)),
     ("fold_rounds_partial_last_round", (256, 256, 448), lambda s: SW(*s, 128, 64, 12, direct=True)),   # 7 k-steps in rounds of 4

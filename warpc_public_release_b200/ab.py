@@ -101,7 +101,7 @@ def make_inputs(torch, kind, m, n, k):
     return a, bt
 
 
-def ab_shape(torch, timer, m, n, k, inputs="hash", rounds=2, variant=None, busy_ms=30.0):
+def ab_shape(torch, timer, m, n, k, inputs="hash", rounds=2, variant=None, busy_ms=30.0, series=0):
     a, bt = make_inputs(torch, inputs, m, n, k)
     c_ours = torch.zeros((m, n), dtype=torch.float32, device="cuda")
     c_lib = torch.zeros((m, n), dtype=torch.float32, device="cuda")
@@ -176,6 +176,25 @@ def ab_shape(torch, timer, m, n, k, inputs="hash", rounds=2, variant=None, busy_
                 lib.append(sum(timer.median(nm, last)[0] for nm in names))
     plan.status()
     err = float((c_lib - c_ours).abs().max().item())
+    steady = None
+    if series > 0:
+        # the reference's other timing (backend/node/clusterlaunch.py:54-96, ab.py AB_SERIES / AB_PDL): mean of `series`
+        # launches back to back between two events, warmed by launches of the same kind; ours also with dependent launch
+        def back_to_back(run):
+            for _ in range(max(3, series // 4)):
+                run()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(series):
+                run()
+            e1.record()
+            torch.cuda.synchronize()
+            return 1e3 * e0.elapsed_time(e1) / series
+        steady = {"launches": series, "ours_us": back_to_back(plan.launch), "cublaslt_us": back_to_back(lambda: lt.run(best))}
+        plan.set_dependent_launch(True)
+        steady["ours_dependent_launch_us"] = back_to_back(plan.launch)
+        plan.set_dependent_launch(False)
+        plan.status()
     flops = 2.0 * m * n * k
     mid = lambda xs: (min(xs) + max(xs)) / 2
     li = programs.realise(v, m, n, k)
@@ -187,6 +206,8 @@ def ab_shape(torch, timer, m, n, k, inputs="hash", rounds=2, variant=None, busy_
            "cublaslt_kernels": lib_kernels, "ours_tflops": flops / mid(ours) / 1e6, "cublaslt_tflops": flops / mid(lib) / 1e6,
            "ours_vs_cublaslt_pct": 100.0 * (min(lib) / mid(ours) - 1.0), "max_abs_diff_vs_cublaslt": err,
            "published_warpc_us": PUBLISHED.get((m, n, k), (None, None))[0], "published_cublas138_us": PUBLISHED.get((m, n, k), (None, None))[1]}
+    if steady is not None:
+        row["back_to_back"] = steady
     plan.close()
     lt.close()
     return row
@@ -197,6 +218,7 @@ def main(argv=None):
     ap.add_argument("--inputs", default="hash", choices=["hash", "uniform"])
     ap.add_argument("--json", default=None)
     ap.add_argument("--rounds", type=int, default=2)
+    ap.add_argument("--series", type=int, default=0, help="also time this many launches back to back between events (ours, ours with dependent launch, cuBLASLt)")
     ap.add_argument("dims", nargs="*", type=int)
     args = ap.parse_args(argv)
     import torch
@@ -207,11 +229,15 @@ def main(argv=None):
     rows = []
     print("%-18s %-12s %-28s %17s %17s %8s   %s" % ("M x N x K", "rule's program", "runs as", "ours us", "cuBLASLt us", "vs lib", "published warpc / cuBLAS 13.8 us"))
     for (m, n, k) in shapes:
-        row = ab_shape(torch, timer, m, n, k, inputs=args.inputs, rounds=args.rounds)
+        row = ab_shape(torch, timer, m, n, k, inputs=args.inputs, rounds=args.rounds, series=args.series)
         rows.append(row)
         print("%-18s %-12s %-28s %8.2f-%-8.2f %8.2f-%-8.2f %+7.1f%%   %s / %s" % (
             "%dx%dx%d" % (m, n, k), row["program"], row["runs_as"], *row["ours_us"], *row["cublaslt_us"], row["ours_vs_cublaslt_pct"],
             row["published_warpc_us"], row["published_cublas138_us"]), flush=True)
+        if "back_to_back" in row:
+            b = row["back_to_back"]
+            print("%-18s back to back x%d: ours %.2f us, ours with dependent launch %.2f us, cuBLASLt %.2f us" % (
+                "", b["launches"], b["ours_us"], b["ours_dependent_launch_us"], b["cublaslt_us"]), flush=True)
         if args.json:
             json.dump({"method": "CUPTI kernel start-to-end, each call alone, median of the last N, ours/lib/lib/ours x %d" % args.rounds,
                        "rows": rows}, open(args.json, "w"), indent=1)

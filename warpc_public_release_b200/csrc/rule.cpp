@@ -262,7 +262,10 @@ extern "C" int wg_realise(const wg_variant* v, int M, int N, int K, wg_launch_in
     li.cl_n = tiles_n / 2;
     li.group = effective_group(8, tiles_m, li.cl_n);
   } else {
-    li.cg = 2, li.tile_m = v->tile_m, li.tile_n = v->tile_n, li.direct = v->direct && v->split == 1;
+    // K shared between CTAs (split in the cluster, split over the grid, stream-K) always adds in the L2 here, the
+    // reference's workspace variants included (backend/gemm_swapped.ml:716-832: partial sums in a workspace, FADD by
+    // the last run): same sums, no workspace; so none of them stores from the registers
+    li.cg = 2, li.tile_m = v->tile_m, li.tile_n = v->tile_n, li.direct = v->direct && v->split == 1 && v->split_grid <= 1 && !v->streamk;
     li.cluster = 2;
     li.nbuf = v->nbuf;
     int group = v->group, clc = v->clc, streamk = v->streamk;
