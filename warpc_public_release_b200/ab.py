@@ -18,6 +18,7 @@ import os
 import sys
 
 from . import _lib, programs
+from .clocks import ClockSampler
 from .plan import Plan
 
 HERE = os.path.dirname(os.path.abspath(__file__))
@@ -160,6 +161,9 @@ def ab_shape(torch, timer, m, n, k, inputs="hash", rounds=2, variant=None, busy_
         return timer.median(tag, last)
 
     ours, lib, lib_kernels = [], [], None
+    sampler = ClockSampler(torch.cuda.current_device())
+    sampler.start()
+    sampler.timed = True
     for _ in range(rounds):
         for side in ("ours", "lib", "lib", "ours"):
             if side == "ours":
@@ -175,6 +179,8 @@ def ab_shape(torch, timer, m, n, k, inputs="hash", rounds=2, variant=None, busy_
                 lib_kernels = names
                 lib.append(sum(timer.median(nm, last)[0] for nm in names))
     plan.status()
+    sampler.timed = False
+    clocks = sampler.stop()
     err = float((c_lib - c_ours).abs().max().item())
     steady = None
     if series > 0:
@@ -206,6 +212,7 @@ def ab_shape(torch, timer, m, n, k, inputs="hash", rounds=2, variant=None, busy_
            "cublaslt_kernels": lib_kernels, "ours_tflops": flops / mid(ours) / 1e6, "cublaslt_tflops": flops / mid(lib) / 1e6,
            "ours_vs_cublaslt_pct": 100.0 * (min(lib) / mid(ours) - 1.0), "max_abs_diff_vs_cublaslt": err,
            "published_warpc_us": PUBLISHED.get((m, n, k), (None, None))[0], "published_cublas138_us": PUBLISHED.get((m, n, k), (None, None))[1]}
+    row["clocks"] = clocks  # over both sides' isolated calls: SM MHz (median), power (max), throttle reasons seen
     if steady is not None:
         row["back_to_back"] = steady
     plan.close()
