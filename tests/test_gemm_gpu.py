@@ -106,6 +106,39 @@ def test_every_round_length_gives_the_same_product(ksub):
         check(build(shape), *shape, "hash", mode=ksub << 8)
 
 
+def test_random_variants_bit_exact():
+    """Tiles, ring depths, accumulator counts, schedules and launch counts drawn at random (seeded): whatever the
+    geometry functions accept has to give the oracle's product exactly on integer inputs."""
+    import random
+    rng = random.Random(5)
+    ran = 0
+    for _ in range(160):
+        tm, tn = rng.choice([(128, 64), (128, 128), (192, 128), (256, 128), (256, 256), (256, 64), (128, 256)])
+        m = tm * rng.randint(1, 4) - rng.choice([0, 0, 0, 64])
+        n = 2 * tn * rng.randint(1, 3)
+        k = 64 * rng.randint(1, 20)
+        kind = rng.choice(["plain", "plain", "direct", "clc", "split", "stream", "rule"])
+        kw = dict(bufs=rng.choice([None, 1, 2]), group=rng.choice([1, 2, 8]), serpentine=rng.random() < 0.3)
+        if kind == "clc":
+            kw.update(clc=True)
+        elif kind == "direct":
+            kw.update(direct=True)
+        elif kind == "split":
+            kw.update(split_grid=rng.randint(2, 5), split_add=True)
+        elif kind == "stream":
+            kw.update(streamk=True, split_add=True, bufs=2)
+        try:
+            v = w.choose(m, n, k) if kind == "rule" else SW(m, n, k, tm, tn, rng.randint(2, 12), **kw)
+            w.realise(v, m, n, k)
+        except Exception:
+            continue  # a combination the builder refuses
+        a, bt = gemm_ref.inputs_integers(m, n, k, seed=ran + 1)
+        c = run_gemm(v, m, n, k, a, bt, launches=rng.choice([1, 1, 3]), dependent=rng.random() < 0.3)
+        assert np.array_equal(c, gemm_ref.gemm_ref(a, bt)), (m, n, k, tm, tn, kind, kw)
+        ran += 1
+    assert ran >= 40
+
+
 def test_golden_products_bit_exact(golden_dir):
     recs = json.load(open(os.path.join(golden_dir, "inputs_and_products.json")))["records"]
     for r in recs:
