@@ -106,7 +106,10 @@ int wg_plan_destroy(void* plan);
 
 /* Host-buffer entry: a plan that owns device copies of A, Bt and C.  wg_host_run copies
  * hA, hBt in, launches, copies C out to hC and synchronises -- the call the reference's
- * harness makes around a launch (backend/node/run_tma.py:68-70, 142). */
+ * harness makes around a launch (backend/node/run_tma.py:68-70, 142).  A large problem (>= 256 MB moved, M and N
+ * multiples of 2048) runs as a pipeline instead of copy / launch / copy: C in blocks of 2048 x 2048, each the rule's
+ * program for 2048 x 2048 x K, launched as its row panels of A and Bt land and copied out as it completes (pinned host
+ * buffers make the three overlap; pageable ones still give the right C).  `v` then names only the one-shot program. */
 int wg_host_plan_create(int device, const wg_variant* v, int M, int N, int K, void** plan);
 int wg_host_run(void* plan, const void* hA, const void* hBt, void* hC);
 /* device pointers of a host plan: which = 0 A, 1 Bt, 2 C */

@@ -203,6 +203,31 @@ def test_host_buffer_entry_matches_device_entry():
     hp.close()
 
 
+def test_host_buffer_entry_pipelined_blocks():
+    # a problem large enough (>= 256 MB moved, 2048-row and -column blocks) runs as a pipeline of block products:
+    # the same C as one launch on device buffers, twice over (the second run re-uses every event and flag)
+    m, n, k = 4096, 6144, 8192
+    a, bt = gemm_ref.inputs_hash(m, n, k)
+    v = w.choose(m, n, k)
+    da, db = torch.from_numpy(a).cuda(), torch.from_numpy(bt).cuda()
+    dc = torch.zeros((m, n), dtype=torch.float32, device="cuda")
+    plan = w.Plan(v, m, n, k, da.data_ptr(), db.data_ptr(), dc.data_ptr())
+    plan.launch()
+    plan.status()
+    want = dc.cpu().numpy()
+    plan.close()
+    assert gemm_ref.sampled_exact(want, m, n, k) == 0
+    ha, hb = torch.from_numpy(a).pin_memory(), torch.from_numpy(bt).pin_memory()
+    hc = torch.full((m, n), float("nan"), dtype=torch.float32).pin_memory()
+    hp = w.HostPlan(v, m, n, k)
+    for _ in range(2):
+        hc.fill_(float("nan"))
+        hp.run(ha.data_ptr(), hb.data_ptr(), hc.data_ptr())
+        hp.status()
+        assert np.array_equal(hc.numpy(), want)
+    hp.close()
+
+
 def test_edges_and_errors():
     with pytest.raises(Exception):
         w.Plan(w.choose(256, 256, 64), 256, 256, 64, 0, 0, 0)             # null pointers

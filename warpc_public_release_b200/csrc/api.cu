@@ -9,6 +9,7 @@
 #include <cstring>
 #include <mutex>
 #include <new>
+#include <vector>
 
 #include "../../include/warpc_b200.h"
 #include "gemm_kernel.cuh"
@@ -77,11 +78,11 @@ EncodeTiledFn encode_tiled() {
 // (the C staging boxes), zero fill
 // out of bounds -- the map backend/node/run_tma.py:32-45 encodes from a `.tmap` line.
 int encode_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem, const void* ptr, int rows, int cols, int box_rows, int box_cols,
-              CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
+              CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B, int ld = 0) {
   EncodeTiledFn enc = encode_tiled();
   if (!enc) return WG_E_NODRIVER;
   cuuint64_t dims[2] = {cuuint64_t(cols), cuuint64_t(rows)};
-  cuuint64_t strides[1] = {cuuint64_t(cols) * cuuint64_t(elem)};
+  cuuint64_t strides[1] = {cuuint64_t(ld > 0 ? ld : cols) * cuuint64_t(elem)};  // ld: elements between rows, when the matrix is a block of a wider one
   cuuint32_t box[2] = {cuuint32_t(box_cols), cuuint32_t(box_rows)};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -115,7 +116,13 @@ struct Plan {
   // host plans own these
   void *dA = nullptr, *dBt = nullptr, *dC = nullptr;
   bool owns_buffers = false;
-  bool dependent_launch = false;  // launches carry the programmatic stream serialization attribute
+  bool dependent_launch = false;
+  // host plans of large problems: the product as a grid of blocks, each with a plan of its own, so that the copies in,
+  // the launches and the copies out run as a pipeline (see wg_host_run)
+  std::vector<Plan*> blocks;
+  int block_rows = 0, block_cols = 0;
+  cudaStream_t s_in = nullptr, s_mm = nullptr, s_out = nullptr;
+  std::vector<cudaEvent_t> ev_a, ev_b, ev_mm;  // launches carry the programmatic stream serialization attribute
   int M = 0, N = 0, K = 0;
 };
 
@@ -125,7 +132,7 @@ struct Plan {
     if (e_ != cudaSuccess) return int(e_);     \
   } while (0)
 
-int fill_plan(Plan* pl, int device, const wg_variant* v, int M, int N, int K, const void* dA, const void* dBt, void* dC) {
+int fill_plan(Plan* pl, int device, const wg_variant* v, int M, int N, int K, const void* dA, const void* dBt, void* dC, int ldc = 0) {
   if (!v || !dA || !dBt || !dC) return WG_E_ARG;
   if ((reinterpret_cast<uintptr_t>(dA) | reinterpret_cast<uintptr_t>(dBt) | reinterpret_cast<uintptr_t>(dC)) & 15u) return WG_E_ARG;
   if (M <= 0 || N <= 0 || K <= 0 || K % 64 != 0 || N % 4 != 0) return WG_E_ARG;
@@ -139,8 +146,9 @@ int fill_plan(Plan* pl, int device, const wg_variant* v, int M, int N, int K, co
   std::memset(&pl->map_cw, 0, sizeof pl->map_cw);
   if ((r = encode_2d(&pl->map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, dA, M, K, li.a_box_rows, 64)) != WG_OK) return r;
   if ((r = encode_2d(&pl->map_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, dBt, N, K, li.bt_box_rows, 64)) != WG_OK) return r;
-  if (!li.direct && (r = encode_2d(&pl->map_c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dC, M, N, li.c_box_rows, 32, CU_TENSOR_MAP_SWIZZLE_NONE)) != WG_OK) return r;
-  if (!li.direct && (r = encode_2d(&pl->map_cw, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dC, M, N, pl->k->wide_rows, 32, CU_TENSOR_MAP_SWIZZLE_NONE)) != WG_OK) return r;
+  if (!li.direct && (r = encode_2d(&pl->map_c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dC, M, N, li.c_box_rows, 32, CU_TENSOR_MAP_SWIZZLE_NONE, ldc)) != WG_OK) return r;
+  if (!li.direct && (r = encode_2d(&pl->map_cw, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dC, M, N, pl->k->wide_rows, 32, CU_TENSOR_MAP_SWIZZLE_NONE, ldc)) != WG_OK) return r;
+  if (li.direct && ldc > 0 && ldc != N) return WG_E_VARIANT;  // the store from the registers takes C's rows N apart
   pl->flag_bytes = size_t(li.nflags > 0 ? li.nflags : 1) * sizeof(uint32_t);
   WG_CUDA(cudaMalloc(&pl->d_flags, pl->flag_bytes));
   WG_CUDA(cudaMalloc(&pl->d_status, 8 * sizeof(uint32_t)));
@@ -171,6 +179,82 @@ int fill_plan(Plan* pl, int device, const wg_variant* v, int M, int N, int K, co
   p.status = pl->d_status;
   p.timeout_ns = 2000ull * 1000ull * 1000ull;
   WG_CUDA(cudaFuncSetAttribute(pl->k->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, li.dynsmem));
+  return WG_OK;
+}
+
+// A host plan of a large problem runs as a pipeline: C is cut into blocks of 2048 x 2048, block (i, j) = rows i of A
+// times rows j of B^T, each with the rule's own program for a 2048 x 2048 x K product.  The row panels of A and B^T
+// go to the device alternately (A0, B0, A1, B1, ...); a block is launched when its two panels have landed and copied
+// out when it is done, so the copies in, the tensor cores and the copies out overlap instead of following each other.
+// Only for problems that cut evenly and are worth it (>= 256 MB moved); otherwise one shot with the plan's own
+// variant.  (The variant a host plan was made with names the one-shot program; the blocks run the rule's.)
+int make_blocks(Plan* pl, int device) {
+  constexpr int B = 2048;
+  const int M = pl->M, N = pl->N, K = pl->K;
+  const double moved = 2.0 * K * (double(M) + N) + 4.0 * M * N;
+  if (M % B != 0 || N % B != 0 || M / B * (N / B) < 4 || M / B * (N / B) > 1024 || moved < 256e6) return WG_OK;
+  wg_variant bv;
+  if (wg_choose(B, B, K, WG_SM_100A, &bv) != WG_OK) return WG_OK;
+  const int nr = M / B, nc = N / B;
+  for (int i = 0; i < nr; ++i)
+    for (int j = 0; j < nc; ++j) {
+      Plan* b = new (std::nothrow) Plan();
+      if (!b) return WG_E_ARG;
+      pl->blocks.push_back(b);
+      const int r = fill_plan(b, device, &bv, B, B, K, static_cast<const char*>(pl->dA) + size_t(i) * B * K * 2,
+                              static_cast<const char*>(pl->dBt) + size_t(j) * B * K * 2,
+                              static_cast<char*>(pl->dC) + (size_t(i) * B * N + size_t(j) * B) * 4, N);
+      if (r != WG_OK) return r;
+    }
+  pl->block_rows = nr, pl->block_cols = nc;
+  WG_CUDA(cudaStreamCreateWithFlags(&pl->s_in, cudaStreamNonBlocking));
+  WG_CUDA(cudaStreamCreateWithFlags(&pl->s_mm, cudaStreamNonBlocking));
+  WG_CUDA(cudaStreamCreateWithFlags(&pl->s_out, cudaStreamNonBlocking));
+  pl->ev_a.resize(nr), pl->ev_b.resize(nc), pl->ev_mm.resize(size_t(nr) * nc);
+  for (auto* list : {&pl->ev_a, &pl->ev_b, &pl->ev_mm})
+    for (auto& e : *list) WG_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+  return WG_OK;
+}
+
+// The pipelined form of wg_host_run (see make_blocks).  Panels go in on one stream in the order A0 B0 A1 B1 ...;
+// block (i, j) waits for panels i and j on the compute stream, blocks are launched in the order their panels
+// complete (all blocks with max(i, j) = d after panel pair d), and each goes out on a third stream once computed.
+int host_run_blocks(Plan* pl, const void* hA, const void* hBt, void* hC) {
+  constexpr int B = 2048;
+  const int nr = pl->block_rows, nc = pl->block_cols, N = pl->N, K = pl->K;
+  const size_t panel = size_t(B) * K * 2;
+  WG_CUDA(cudaSetDevice(pl->device));
+  for (int d = 0; d < (nr > nc ? nr : nc); ++d) {
+    if (d < nr) {
+      WG_CUDA(cudaMemcpyAsync(static_cast<char*>(pl->dA) + d * panel, static_cast<const char*>(hA) + d * panel, panel, cudaMemcpyHostToDevice, pl->s_in));
+      WG_CUDA(cudaEventRecord(pl->ev_a[d], pl->s_in));
+    }
+    if (d < nc) {
+      WG_CUDA(cudaMemcpyAsync(static_cast<char*>(pl->dBt) + d * panel, static_cast<const char*>(hBt) + d * panel, panel, cudaMemcpyHostToDevice, pl->s_in));
+      WG_CUDA(cudaEventRecord(pl->ev_b[d], pl->s_in));
+    }
+    auto run_block = [&](int i, int j) -> int {
+      WG_CUDA(cudaStreamWaitEvent(pl->s_mm, pl->ev_a[i], 0));
+      WG_CUDA(cudaStreamWaitEvent(pl->s_mm, pl->ev_b[j], 0));
+      const int r = wg_launch(pl->blocks[size_t(i) * nc + j], pl->s_mm);
+      if (r != WG_OK) return r;
+      cudaEvent_t done = pl->ev_mm[size_t(i) * nc + j];
+      WG_CUDA(cudaEventRecord(done, pl->s_mm));
+      WG_CUDA(cudaStreamWaitEvent(pl->s_out, done, 0));
+      const size_t off = (size_t(i) * B * N + size_t(j) * B) * 4;
+      WG_CUDA(cudaMemcpy2DAsync(static_cast<char*>(hC) + off, size_t(N) * 4, static_cast<const char*>(pl->dC) + off, size_t(N) * 4, size_t(B) * 4, B,
+                                cudaMemcpyDeviceToHost, pl->s_out));
+      return WG_OK;
+    };
+    int r = WG_OK;
+    for (int j = 0; j <= d && j < nc && r == WG_OK; ++j)
+      if (d < nr) r = run_block(d, j);          // the new row of blocks
+    for (int i = 0; i < d && i < nr && r == WG_OK; ++i)
+      if (d < nc) r = run_block(i, d);          // the new column of blocks
+    if (r != WG_OK) return r;
+  }
+  WG_CUDA(cudaStreamSynchronize(pl->s_out));
+  WG_CUDA(cudaStreamSynchronize(pl->s_mm));
   return WG_OK;
 }
 
@@ -217,6 +301,7 @@ extern "C" int wg_host_plan_create(int device, const wg_variant* v, int M, int N
   if (r == 0) r = int(cudaMalloc(&pl->dBt, size_t(N) * K * 2));
   if (r == 0) r = int(cudaMalloc(&pl->dC, size_t(M) * N * 4));
   if (r == 0) r = fill_plan(pl, device, v, M, N, K, pl->dA, pl->dBt, pl->dC);
+  if (r == 0) r = make_blocks(pl, device);
   if (r != WG_OK) {
     wg_plan_destroy(pl);
     return r;
@@ -299,6 +384,12 @@ extern "C" int wg_plan_destroy(void* plan) {
   if (pl->d_flags) cudaFree(pl->d_flags);
   if (pl->d_status) cudaFree(pl->d_status);
   if (pl->d_stamps) cudaFree(pl->d_stamps);
+  for (Plan* b : pl->blocks) wg_plan_destroy(b);
+  for (auto* list : {&pl->ev_a, &pl->ev_b, &pl->ev_mm})
+    for (auto& e : *list)
+      if (e) cudaEventDestroy(e);
+  for (cudaStream_t s : {pl->s_in, pl->s_mm, pl->s_out})
+    if (s) cudaStreamDestroy(s);
   if (pl->owns_buffers) {
     if (pl->dA) cudaFree(pl->dA);
     if (pl->dBt) cudaFree(pl->dBt);
@@ -311,6 +402,7 @@ extern "C" int wg_plan_destroy(void* plan) {
 extern "C" int wg_host_run(void* plan, const void* hA, const void* hBt, void* hC) {
   Plan* pl = static_cast<Plan*>(plan);
   if (!pl || !pl->owns_buffers || !hA || !hBt || !hC) return WG_E_ARG;
+  if (!pl->blocks.empty()) return host_run_blocks(pl, hA, hBt, hC);
   WG_CUDA(cudaMemcpyAsync(pl->dA, hA, size_t(pl->M) * pl->K * 2, cudaMemcpyHostToDevice, 0));
   WG_CUDA(cudaMemcpyAsync(pl->dBt, hBt, size_t(pl->N) * pl->K * 2, cudaMemcpyHostToDevice, 0));
   const int r = wg_launch(pl, nullptr);
