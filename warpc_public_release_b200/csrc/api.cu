@@ -236,21 +236,29 @@ int host_run_blocks(Plan* pl, const void* hA, const void* hBt, void* hC) {
     auto run_block = [&](int i, int j) -> int {
       WG_CUDA(cudaStreamWaitEvent(pl->s_mm, pl->ev_a[i], 0));
       WG_CUDA(cudaStreamWaitEvent(pl->s_mm, pl->ev_b[j], 0));
-      const int r = wg_launch(pl->blocks[size_t(i) * nc + j], pl->s_mm);
-      if (r != WG_OK) return r;
-      cudaEvent_t done = pl->ev_mm[size_t(i) * nc + j];
+      return wg_launch(pl->blocks[size_t(i) * nc + j], pl->s_mm);
+    };
+    // rows [r0, r0 + rows) x columns [c0, c0 + cols) of C out, once everything launched so far is done
+    auto copy_out = [&](cudaEvent_t done, int r0, int rows, int c0, int cols) -> int {
       WG_CUDA(cudaEventRecord(done, pl->s_mm));
       WG_CUDA(cudaStreamWaitEvent(pl->s_out, done, 0));
-      const size_t off = (size_t(i) * B * N + size_t(j) * B) * 4;
-      WG_CUDA(cudaMemcpy2DAsync(static_cast<char*>(hC) + off, size_t(N) * 4, static_cast<const char*>(pl->dC) + off, size_t(N) * 4, size_t(B) * 4, B,
-                                cudaMemcpyDeviceToHost, pl->s_out));
+      const size_t off = (size_t(r0) * N + size_t(c0)) * 4;
+      WG_CUDA(cudaMemcpy2DAsync(static_cast<char*>(hC) + off, size_t(N) * 4, static_cast<const char*>(pl->dC) + off, size_t(N) * 4, size_t(cols) * 4,
+                                size_t(rows), cudaMemcpyDeviceToHost, pl->s_out));
       return WG_OK;
     };
     int r = WG_OK;
-    for (int j = 0; j <= d && j < nc && r == WG_OK; ++j)
-      if (d < nr) r = run_block(d, j);          // the new row of blocks
-    for (int i = 0; i < d && i < nr && r == WG_OK; ++i)
-      if (d < nc) r = run_block(i, d);          // the new column of blocks
+    // the new row of blocks (d, 0..d) leaves as one copy of long rows, the new column (0..d-1, d) as one of many rows
+    if (d < nr) {
+      const int last = d < nc ? d : nc - 1;
+      for (int j = 0; j <= last && r == WG_OK; ++j) r = run_block(d, j);
+      if (r == WG_OK) r = copy_out(pl->ev_mm[size_t(d) * nc], d * B, B, 0, (last + 1) * B);
+    }
+    if (d < nc && d > 0 && r == WG_OK) {
+      const int rows = d < nr ? d : nr;
+      for (int i = 0; i < rows && r == WG_OK; ++i) r = run_block(i, d);
+      if (r == WG_OK) r = copy_out(pl->ev_mm[size_t(0) * nc + d], 0, rows * B, d * B, B);
+    }
     if (r != WG_OK) return r;
   }
   WG_CUDA(cudaStreamSynchronize(pl->s_out));
