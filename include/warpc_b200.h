@@ -9,7 +9,9 @@
  * Conventions: every function returns 0 on success, > 0 a cudaError_t / CUresult value,
  * < 0 a library error (WG_E_*).  Callers own A, Bt and C; a plan owns its tensor maps,
  * hand-off flags and status words.  A plan is used from one host thread and one stream at a
- * time.  Nothing synchronises unless stated.  There is no CPU fallback: without a CUDA device
+ * time.  Every entry point that touches the GPU makes the plan's (or the named) device current
+ * for the call and restores the caller's current device before it returns, so one thread may
+ * drive plans on several GPUs.  Nothing synchronises unless stated.  There is no CPU fallback: without a CUDA device
  * every function that touches the GPU returns an error.
  */
 #ifndef WARPC_B200_H
@@ -138,10 +140,10 @@ int wg_plan_read_stamps(void* plan, unsigned long long* out, size_t cap_words);
  * backend/node/run_tma.py:129-137): overwrite hand-off word `index` of a split-K / stream-K plan. */
 int wg_plan_debug_set_flag(void* plan, int index, unsigned value);
 
-/* Timing experiments only (no reference counterpart): bit 0 = load nothing, bit 1 = issue no
- * MMAs; barriers and the ring still cycle, results are meaningless.  Bits 8-11: k-steps the
- * ring hands over per barrier round in the launches that follow (1, 2 or 4; results stay
- * exact), 0 = the library's own choice. */
+/* Tuning hook (no reference counterpart).  Bits 8-11: k-steps the ring hands over per barrier
+ * round in the launches that follow (1, 2 or 4; results stay exact), 0 = the library's own
+ * choice.  Bits 0-7 must be zero: they select modes that skip loads or MMAs to time one role
+ * alone, and exist only in builds made with -DWB_TIMING_EXPERIMENTS. */
 int wg_plan_debug_set_mode(void* plan, unsigned flags);
 
 /* Where CTA tile index `tile` sits in C under a launch's tile walk (backend/tiles.ml:32-80). */
@@ -162,7 +164,10 @@ int wg_tile_origin(const wg_launch_info* li, int tile, int* row, int* col);
  *     ahead of its kernel, so calls on one stream are safe back to back, but two calls that
  *     overlap on the GPU (different streams, no dependency) race on it.
  *   - No cudaMalloc / cudaFree / allocating library routine is called.
- * wg_noalloc_status synchronises the device and reports the status words like wg_last_device_status. */
+ * wg_noalloc_status synchronises the device and reports the status words of the MOST RECENT call
+ * only: each wg_launch_noalloc clears them on its stream (its waits read them), so a give-up must
+ * be read before the next wg_launch_noalloc on that device -- unlike wg_last_device_status, which
+ * is sticky across a plan's launches. */
 int wg_launch_noalloc(int device, const wg_variant* v, int M, int N, int K, const void* dA, const void* dBt, void* dC,
                       void* cuda_stream);
 int wg_noalloc_status(int device, unsigned out[4]);

@@ -1,6 +1,6 @@
 """Generates the golden fixtures in this folder.  Run where the reference is present:
 
-    python tests/golden/make_golden.py [REFERENCE_ROOT]
+    python tests/golden/make_golden.py REFERENCE_ROOT        (or WARPC_REFERENCE=REFERENCE_ROOT)
 
 It executes the reference's OWN code, not a restatement of it:
   * inputs_and_products.json -- the input-generation and numpy-check statements of
@@ -46,7 +46,9 @@ def reference_inputs_snippet(ref_root):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("WARPC_REFERENCE")
+    if not ref_root or not os.path.isdir(os.path.join(ref_root, "backend", "node")):
+        raise SystemExit("usage: make_golden.py REFERENCE_ROOT  (the checkout of the reference; or set WARPC_REFERENCE)")
     snippet = reference_inputs_snippet(ref_root)
     records = []
     for family, env_inputs in (("integers", None), ("hash", "hash")):

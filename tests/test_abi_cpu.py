@@ -163,6 +163,32 @@ def test_gemm_command_line():
     assert sw.returncode == 0 and ".ptr flags 1 144 4" in sw.stdout
 
 
+def test_a_header_text_rebuilds_the_exact_program():
+    """gemm -> header text -> run_tma's variant_from_header gives back the same program (same launch geometry), for
+    the rule's choices and for explicitly named split-K, stream-K, launch-control and serpentine programs; a header
+    whose directives were edited, or that carries no variant line, is refused rather than run as something else."""
+    from warpc_public_release_b200 import run_tma
+    cases = [(s, w.choose(*s)) for s in BENCH_SHAPES]
+    cases += [((512, 1024, 1088), w.swapped(512, 1024, 1088, 256, 256, 4, split_grid=3, split_add=True, ask_ahead=True)),
+              ((1024, 512, 1024), w.swapped(1024, 512, 1024, 256, 128, 6, streamk=True, split_add=True, bufs=2, ask_ahead=True)),
+              ((384, 512, 256), w.swapped(384, 512, 256, 192, 128, 7, clc=True)),              # launch control with <= 148 tiles
+              ((1024, 2048, 512), w.swapped(1024, 2048, 512, 256, 256, 4, clc=True, serpentine=True, ask_ahead=True)),
+              ((2048, 2304, 256), w.swapped(2048, 2304, 256, 128, 128, 8, bufs=2, group=16)),
+              ((512, 1024, 4096), w.swapped(512, 1024, 4096, 256, 256, 4, split_grid=4, direct=True)),
+              ((256, 512, 16384), w.swapped(256, 512, 16384, 128, 128, 9, split=2, cluster_n=2, direct=True)),
+              ((512, 384, 256), w.pair(512, 384, 256, 8)), ((256, 384, 512), w.one(256, 384, 512, 4))]
+    for s, v in cases:
+        text = w.header(v, *s)
+        back = run_tma.variant_from_header(text, *s)
+        assert w.realise(back, *s).as_dict() == w.realise(v, *s).as_dict(), s
+        assert w.header(back, *s) == text
+    text = w.header(cases[-4][1], *cases[-4][0])
+    with pytest.raises(RuntimeError):
+        run_tma.variant_from_header(text.replace(".grid ", ".grid 1"), *cases[-4][0])
+    with pytest.raises(RuntimeError):
+        run_tma.variant_from_header("\n".join(l for l in text.splitlines() if not l.startswith("# variant")), *cases[-4][0])
+
+
 def test_no_cpu_fallback_without_a_device():
     import torch
     if torch.cuda.is_available():

@@ -132,6 +132,58 @@ struct Plan {
     if (e_ != cudaSuccess) return int(e_);     \
   } while (0)
 
+// Makes `device` current for the length of an entry point and gives the caller's device back on
+// the way out, so one host thread can drive plans on several GPUs in turn.
+struct DeviceGuard {
+  int prev = -1;
+  bool changed = false;
+  cudaError_t err = cudaSuccess;
+  explicit DeviceGuard(int device) {
+    err = cudaGetDevice(&prev);
+    if (err == cudaSuccess && prev != device) {
+      err = cudaSetDevice(device);
+      changed = err == cudaSuccess;
+    }
+  }
+  ~DeviceGuard() {
+    if (changed) cudaSetDevice(prev);
+  }
+  DeviceGuard(const DeviceGuard&) = delete;
+  DeviceGuard& operator=(const DeviceGuard&) = delete;
+};
+#define WG_ON_DEVICE(device)        \
+  DeviceGuard guard_(device);       \
+  if (guard_.err != cudaSuccess) return int(guard_.err)
+
+void launch_config(const wg_launch_info& li, cudaStream_t stream, bool dependent, cudaLaunchConfig_t* cfg, cudaLaunchAttribute attr[2]) {
+  std::memset(cfg, 0, sizeof *cfg);
+  cfg->gridDim = dim3(unsigned(li.grid), 1, 1);
+  cfg->blockDim = dim3(unsigned(li.threads), 1, 1);
+  cfg->dynamicSmemBytes = size_t(li.dynsmem);
+  cfg->stream = stream;
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = unsigned(li.cluster);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg->attrs = attr;
+  cfg->numAttrs = dependent ? 2 : 1;
+}
+
+// Split-K and stream-K CTAs wait for each other's flags, so every cluster of the grid has to be
+// resident at once.  The rule's tables assume a whole B200 (148 SMs, 74 resident pairs); a device
+// or context that offers fewer is refused here rather than found out by a wait that runs out.
+int check_coresident(const wb_kernel_entry* k, const wg_launch_info& li) {
+  if (li.sched != SCHED_SPLITK && li.sched != SCHED_STREAMK) return WG_OK;
+  cudaLaunchConfig_t cfg;
+  cudaLaunchAttribute attr[2];
+  launch_config(li, nullptr, false, &cfg, attr);
+  int clusters = 0;
+  WG_CUDA(cudaOccupancyMaxActiveClusters(&clusters, k->fn, &cfg));
+  return li.grid / li.cluster <= clusters ? WG_OK : WG_E_VARIANT;
+}
+
 int fill_plan(Plan* pl, int device, const wg_variant* v, int M, int N, int K, const void* dA, const void* dBt, void* dC, int ldc = 0) {
   if (!v || !dA || !dBt || !dC) return WG_E_ARG;
   if ((reinterpret_cast<uintptr_t>(dA) | reinterpret_cast<uintptr_t>(dBt) | reinterpret_cast<uintptr_t>(dC)) & 15u) return WG_E_ARG;
@@ -141,7 +193,7 @@ int fill_plan(Plan* pl, int device, const wg_variant* v, int M, int N, int K, co
   if (r != WG_OK) return r;
   const wg_launch_info& li = pl->li;
   pl->k = wb_kernel_at(li.kernel_id);
-  WG_CUDA(cudaSetDevice(device));
+  WG_ON_DEVICE(device);
   std::memset(&pl->map_c, 0, sizeof pl->map_c);
   std::memset(&pl->map_cw, 0, sizeof pl->map_cw);
   if ((r = encode_2d(&pl->map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, dA, M, K, li.a_box_rows, 64)) != WG_OK) return r;
@@ -152,8 +204,9 @@ int fill_plan(Plan* pl, int device, const wg_variant* v, int M, int N, int K, co
   pl->flag_bytes = size_t(li.nflags > 0 ? li.nflags : 1) * sizeof(uint32_t);
   WG_CUDA(cudaMalloc(&pl->d_flags, pl->flag_bytes));
   WG_CUDA(cudaMalloc(&pl->d_status, 8 * sizeof(uint32_t)));
-  WG_CUDA(cudaMemset(pl->d_flags, 0, pl->flag_bytes));
-  WG_CUDA(cudaMemset(pl->d_status, 0, 8 * sizeof(uint32_t)));
+  WG_CUDA(cudaMemsetAsync(pl->d_flags, 0, pl->flag_bytes, 0));
+  WG_CUDA(cudaMemsetAsync(pl->d_status, 0, 8 * sizeof(uint32_t), 0));
+  WG_CUDA(cudaStreamSynchronize(0));  // the words are zero before any stream, blocking or not, can launch on the plan
   KParams& p = pl->p;
   std::memset(&p, 0, sizeof p);
   p.M = M, p.N = N, p.K = K;
@@ -179,7 +232,7 @@ int fill_plan(Plan* pl, int device, const wg_variant* v, int M, int N, int K, co
   p.status = pl->d_status;
   p.timeout_ns = 2000ull * 1000ull * 1000ull;
   WG_CUDA(cudaFuncSetAttribute(pl->k->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, li.dynsmem));
-  return WG_OK;
+  return check_coresident(pl->k, li);
 }
 
 // A host plan of a large problem runs as a pipeline: C is cut into blocks of 2048 x 2048, block (i, j) = rows i of A
@@ -223,7 +276,6 @@ int host_run_blocks(Plan* pl, const void* hA, const void* hBt, void* hC) {
   constexpr int B = 2048;
   const int nr = pl->block_rows, nc = pl->block_cols, N = pl->N, K = pl->K;
   const size_t panel = size_t(B) * K * 2;
-  WG_CUDA(cudaSetDevice(pl->device));
   for (int d = 0; d < (nr > nc ? nr : nc); ++d) {
     if (d < nr) {
       WG_CUDA(cudaMemcpyAsync(static_cast<char*>(pl->dA) + d * panel, static_cast<const char*>(hA) + d * panel, panel, cudaMemcpyHostToDevice, pl->s_in));
@@ -304,7 +356,9 @@ extern "C" int wg_host_plan_create(int device, const wg_variant* v, int M, int N
   Plan* pl = new (std::nothrow) Plan();
   if (!pl) return WG_E_ARG;
   pl->owns_buffers = true;
-  int r = int(cudaSetDevice(device));
+  pl->device = device;
+  DeviceGuard guard(device);
+  int r = int(guard.err);
   if (r == 0) r = int(cudaMalloc(&pl->dA, size_t(M) * K * 2));
   if (r == 0) r = int(cudaMalloc(&pl->dBt, size_t(N) * K * 2));
   if (r == 0) r = int(cudaMalloc(&pl->dC, size_t(M) * N * 4));
@@ -341,21 +395,10 @@ extern "C" int wg_plan_info(void* plan, wg_launch_info* out) {
 extern "C" int wg_launch(void* plan, void* cuda_stream) {
   Plan* pl = static_cast<Plan*>(plan);
   if (!pl || !pl->k) return WG_E_ARG;
+  WG_ON_DEVICE(pl->device);
   cudaLaunchConfig_t cfg;
-  std::memset(&cfg, 0, sizeof cfg);
-  cfg.gridDim = dim3(unsigned(pl->li.grid), 1, 1);
-  cfg.blockDim = dim3(unsigned(pl->li.threads), 1, 1);
-  cfg.dynamicSmemBytes = size_t(pl->li.dynsmem);
-  cfg.stream = static_cast<cudaStream_t>(cuda_stream);
   cudaLaunchAttribute attr[2];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = unsigned(pl->li.cluster);
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[1].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = pl->dependent_launch ? 2 : 1;
+  launch_config(pl->li, static_cast<cudaStream_t>(cuda_stream), pl->dependent_launch, &cfg, attr);
   void* args[5] = {&pl->map_a, &pl->map_b, &pl->map_c, &pl->map_cw, &pl->p};
   return int(cudaLaunchKernelExC(&cfg, pl->k->fn, args));
 }
@@ -370,6 +413,7 @@ extern "C" int wg_plan_set_dependent_launch(void* plan, int on) {
 extern "C" int wg_last_device_status(void* plan, unsigned out[4]) {
   Plan* pl = static_cast<Plan*>(plan);
   if (!pl || !out) return WG_E_ARG;
+  WG_ON_DEVICE(pl->device);
   uint32_t st[8];
   WG_CUDA(cudaDeviceSynchronize());
   WG_CUDA(cudaMemcpy(st, pl->d_status, sizeof st, cudaMemcpyDeviceToHost));
@@ -380,15 +424,18 @@ extern "C" int wg_last_device_status(void* plan, unsigned out[4]) {
 extern "C" int wg_plan_reset(void* plan) {
   Plan* pl = static_cast<Plan*>(plan);
   if (!pl) return WG_E_ARG;
+  WG_ON_DEVICE(pl->device);
   WG_CUDA(cudaDeviceSynchronize());
-  WG_CUDA(cudaMemset(pl->d_flags, 0, pl->flag_bytes));
-  WG_CUDA(cudaMemset(pl->d_status, 0, 8 * sizeof(uint32_t)));
+  WG_CUDA(cudaMemsetAsync(pl->d_flags, 0, pl->flag_bytes, 0));
+  WG_CUDA(cudaMemsetAsync(pl->d_status, 0, 8 * sizeof(uint32_t), 0));
+  WG_CUDA(cudaStreamSynchronize(0));
   return WG_OK;
 }
 
 extern "C" int wg_plan_destroy(void* plan) {
   Plan* pl = static_cast<Plan*>(plan);
   if (!pl) return WG_OK;
+  DeviceGuard guard(pl->device);
   if (pl->d_flags) cudaFree(pl->d_flags);
   if (pl->d_status) cudaFree(pl->d_status);
   if (pl->d_stamps) cudaFree(pl->d_stamps);
@@ -410,6 +457,7 @@ extern "C" int wg_plan_destroy(void* plan) {
 extern "C" int wg_host_run(void* plan, const void* hA, const void* hBt, void* hC) {
   Plan* pl = static_cast<Plan*>(plan);
   if (!pl || !pl->owns_buffers || !hA || !hBt || !hC) return WG_E_ARG;
+  WG_ON_DEVICE(pl->device);
   if (!pl->blocks.empty()) return host_run_blocks(pl, hA, hBt, hC);
   WG_CUDA(cudaMemcpyAsync(pl->dA, hA, size_t(pl->M) * pl->K * 2, cudaMemcpyHostToDevice, 0));
   WG_CUDA(cudaMemcpyAsync(pl->dBt, hBt, size_t(pl->N) * pl->K * 2, cudaMemcpyHostToDevice, 0));
@@ -425,6 +473,7 @@ extern "C" int wg_host_run(void* plan, const void* hA, const void* hBt, void* hC
 extern "C" int wg_time_launches(void* plan, int warmup, int repeat, float* ms_mean) {
   Plan* pl = static_cast<Plan*>(plan);
   if (!pl || !ms_mean || repeat < 1) return WG_E_ARG;
+  WG_ON_DEVICE(pl->device);
   cudaEvent_t e0, e1;
   WG_CUDA(cudaEventCreate(&e0));
   WG_CUDA(cudaEventCreate(&e1));
@@ -447,6 +496,7 @@ extern "C" int wg_time_launches(void* plan, int warmup, int repeat, float* ms_me
 extern "C" int wg_plan_enable_stamps(void* plan, int on) {
   Plan* pl = static_cast<Plan*>(plan);
   if (!pl) return WG_E_ARG;
+  WG_ON_DEVICE(pl->device);
   const size_t bytes = size_t(pl->li.grid) * 256 * sizeof(unsigned long long);
   if (on && !pl->d_stamps) {
     WG_CUDA(cudaMalloc(&pl->d_stamps, bytes));
@@ -461,6 +511,7 @@ extern "C" int wg_plan_read_stamps(void* plan, unsigned long long* out, size_t c
   if (!pl || !out || !pl->d_stamps) return WG_E_ARG;
   const size_t words = size_t(pl->li.grid) * 256;
   if (cap_words < words) return WG_E_ARG;
+  WG_ON_DEVICE(pl->device);
   WG_CUDA(cudaDeviceSynchronize());
   WG_CUDA(cudaMemcpy(out, pl->d_stamps, words * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
   return int(words);
@@ -478,6 +529,7 @@ extern "C" int wg_tile_origin(const wg_launch_info* li, int tile, int* row, int*
 extern "C" int wg_plan_debug_set_flag(void* plan, int index, unsigned value) {
   Plan* pl = static_cast<Plan*>(plan);
   if (!pl || index < 0 || size_t(index) * sizeof(uint32_t) >= pl->flag_bytes) return WG_E_ARG;
+  WG_ON_DEVICE(pl->device);
   WG_CUDA(cudaDeviceSynchronize());
   WG_CUDA(cudaMemcpy(pl->d_flags + index, &value, sizeof value, cudaMemcpyHostToDevice));
   return WG_OK;
@@ -506,7 +558,7 @@ int noalloc_setup(int device, uint32_t** out) {
   if (device < 0 || device >= kMaxDevices) return WG_E_ARG;
   std::lock_guard<std::mutex> lock(g_noalloc_mutex);
   if (!g_noalloc_ptr[device]) {
-    WG_CUDA(cudaSetDevice(device));
+    WG_ON_DEVICE(device);
     void* p = nullptr;
     cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
     if (e != cudaSuccess) return int(e);
@@ -537,7 +589,7 @@ extern "C" int wg_launch_noalloc(int device, const wg_variant* v, int M, int N, 
   if (li.nflags > kNoAllocMaxFlags) return WG_E_LIMIT;  // the shape needs more hand-off words than the array holds
   uint32_t* scratch = nullptr;
   if ((r = noalloc_setup(device, &scratch)) != WG_OK) return r;
-  WG_CUDA(cudaSetDevice(device));
+  WG_ON_DEVICE(device);
   const wb_kernel_entry* k = wb_kernel_at(li.kernel_id);
   CUtensorMap map_a, map_b, map_c, map_cw;
   std::memset(&map_c, 0, sizeof map_c);
@@ -570,19 +622,10 @@ extern "C" int wg_launch_noalloc(int device, const wg_variant* v, int M, int N, 
   // clear the words this launch uses (and the status) on the stream, ahead of the kernel
   WG_CUDA(cudaMemsetAsync(scratch, 0, size_t(8 + (li.nflags > 0 ? li.nflags : 0)) * sizeof(uint32_t), stream));
   WG_CUDA(cudaFuncSetAttribute(k->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, li.dynsmem));
+  if ((r = check_coresident(k, li)) != WG_OK) return r;
   cudaLaunchConfig_t cfg;
-  std::memset(&cfg, 0, sizeof cfg);
-  cfg.gridDim = dim3(unsigned(li.grid), 1, 1);
-  cfg.blockDim = dim3(unsigned(li.threads), 1, 1);
-  cfg.dynamicSmemBytes = size_t(li.dynsmem);
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = unsigned(li.cluster);
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cudaLaunchAttribute attr[2];
+  launch_config(li, stream, false, &cfg, attr);
   void* args[5] = {&map_a, &map_b, &map_c, &map_cw, &p};
   return int(cudaLaunchKernelExC(&cfg, k->fn, args));
 }
@@ -593,19 +636,25 @@ extern "C" int wg_noalloc_status(int device, unsigned out[4]) {
   const int r = noalloc_setup(device, &scratch);
   if (r != WG_OK) return r;
   uint32_t st[4];
-  WG_CUDA(cudaSetDevice(device));
+  WG_ON_DEVICE(device);
   WG_CUDA(cudaDeviceSynchronize());
   WG_CUDA(cudaMemcpy(st, scratch, sizeof st, cudaMemcpyDeviceToHost));
   for (int i = 0; i < 4; ++i) out[i] = st[i];
   return st[0] == 0 ? WG_OK : WG_E_DEVICE_WAIT;
 }
 
-// Timing experiments: bit 0 = the producer loads nothing (barriers still cycle), bit 1 = no MMAs
-// are issued (commits still are).  Results are then meaningless; only the time is of interest.
+// Bits 8-11 choose how many k-steps the ring hands over per barrier round (results stay exact).
+// Bits 0-7 exist only in builds with -DWB_TIMING_EXPERIMENTS (bit 0: the producer loads nothing,
+// bit 1: no MMAs are issued, bits 4-5: flip the L2 hints; results are then meaningless); the
+// library as shipped refuses them.
 extern "C" int wg_plan_debug_set_mode(void* plan, unsigned flags) {
   Plan* pl = static_cast<Plan*>(plan);
   if (!pl) return WG_E_ARG;
+#ifdef WB_TIMING_EXPERIMENTS
   pl->p.debug = flags & 0xffu;
+#else
+  if (flags & 0xffu) return WG_E_ARG;
+#endif
   // bits 8-11: k-steps a barrier round (1, 2 or 4) for the launches that follow; 0 = the library's choice
   const int ksub = int((flags >> 8) & 0xfu);
   if (ksub == 0) pl->p.ksub = pl->li.ksub, pl->p.rounds = pl->li.rounds;

@@ -61,9 +61,19 @@ struct KParams {
   uint32_t* flags;              // split-K / stream-K hand-off words
   uint32_t* status;             // 8 words: [0] code, [1] site detail, [2] CTA, [3] parity/stage
   unsigned long long timeout_ns;
-  unsigned int debug;           // timing experiments only: bit 0 the producer loads nothing, bit 1 no MMAs are issued
+#ifdef WB_TIMING_EXPERIMENTS
+  unsigned int debug;           // bit 0 the producer loads nothing, bit 1 no MMAs are issued, bits 4-5 flip the L2 hints
+#endif
   unsigned long long* stamps;   // timing builds: 32 events x 4 tiles per CTA, or null
 };
+
+// Builds with -DWB_TIMING_EXPERIMENTS carry a word of switches that make a launch skip its loads or
+// its MMAs (wrong results, for timing one role alone); the library as shipped has no such switch.
+#ifdef WB_TIMING_EXPERIMENTS
+#define WB_DEBUG_WORD(p) ((p).debug)
+#else
+#define WB_DEBUG_WORD(p) 0u
+#endif
 
 template <int CG_, int TM_, int TN_, bool DIRECT_, int EPI_ROWS_ = 32, int EPI_COPIES_ = 2>
 struct Cfg {
@@ -500,7 +510,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       uint32_t stage = 0, phase = 0;
       int nth = 0;
       bool ok = true;
-      const uint64_t load_policy = (((p.debug >> 4) ^ uint32_t(p.l2_hints)) & 2u) ? l2_policy_evict_last() : l2_policy_evict_normal();
+      const uint64_t load_policy = (((WB_DEBUG_WORD(p) >> 4) ^ uint32_t(p.l2_hints)) & 2u) ? l2_policy_evict_last() : l2_policy_evict_normal();
       const uint32_t full_leader0 = (CG == 2) ? mapa(full_bar(0), 0) : full_bar(0);
       for (; ok && have; have = ok && walk.template next<false>(w)) {
         if (nth != 0) tile_origin<C>(p, w.tile, row, col);
@@ -513,15 +523,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           uint32_t gave_up;
           if (ksub == 2)
             gave_up = load_rounds<CG, 2>(1u, kleft, uint32_t(rounds), stage, phase, x, empty_bar(0), full_bar(0), full_leader0, leader ? 1u : 0u,
-                                         C::TX_BYTES, ring, 2u * C::STAGE_BYTES, uint32_t(C::A_BYTES), &map_a, a_row, &map_b, col, 1u << 14, p.debug,
+                                         C::TX_BYTES, ring, 2u * C::STAGE_BYTES, uint32_t(C::A_BYTES), &map_a, a_row, &map_b, col, 1u << 14, WB_DEBUG_WORD(p),
                                          uint32_t(C::STAGE_BYTES), load_policy);
           else if (ksub == 4)
             gave_up = load_rounds<CG, 4>(1u, kleft, uint32_t(rounds), stage, phase, x, empty_bar(0), full_bar(0), full_leader0, leader ? 1u : 0u,
-                                         C::TX_BYTES, ring, 4u * C::STAGE_BYTES, uint32_t(C::A_BYTES), &map_a, a_row, &map_b, col, 1u << 14, p.debug,
+                                         C::TX_BYTES, ring, 4u * C::STAGE_BYTES, uint32_t(C::A_BYTES), &map_a, a_row, &map_b, col, 1u << 14, WB_DEBUG_WORD(p),
                                          uint32_t(C::STAGE_BYTES), load_policy);
           else
             gave_up = load_k_loop<CG>(1u, kleft, uint32_t(rounds), stage, phase, x, empty_bar(0), full_bar(0), full_leader0, leader ? 1u : 0u,
-                                      C::TX_BYTES, ring, uint32_t(C::STAGE_BYTES), uint32_t(C::A_BYTES), &map_a, a_row, &map_b, col, 1u << 14, p.debug, load_policy);
+                                      C::TX_BYTES, ring, uint32_t(C::STAGE_BYTES), uint32_t(C::A_BYTES), &map_a, a_row, &map_b, col, 1u << 14, WB_DEBUG_WORD(p), load_policy);
           if (gave_up != 0u && !wait_bar<false, false>(p, abort_addr, empty_bar(int(stage)), phase ^ 1u, ST_WAIT_EMPTY, stage)) {
             ok = false;
             break;
@@ -572,13 +582,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           uint32_t gave_up;
           if (C::REPS == 1 && ksub == 2)
             gave_up = mma_rounds<CG, 2>(1u, kleft, uint32_t(rounds), stage, phase, accumulate, full_bar(0), empty_bar(0), d, uint32_t(C::SPAN),
-                                        b_lo0, STAGE16, a_lo0, 2u * STAGE16, DESC_HI, C::IDESC, 1u << 14, p.debug);
+                                        b_lo0, STAGE16, a_lo0, 2u * STAGE16, DESC_HI, C::IDESC, 1u << 14, WB_DEBUG_WORD(p));
           else if (C::REPS == 1 && ksub == 4)
             gave_up = mma_rounds<CG, 4>(1u, kleft, uint32_t(rounds), stage, phase, accumulate, full_bar(0), empty_bar(0), d, uint32_t(C::SPAN),
-                                        b_lo0, STAGE16, a_lo0, 4u * STAGE16, DESC_HI, C::IDESC, 1u << 14, p.debug);
+                                        b_lo0, STAGE16, a_lo0, 4u * STAGE16, DESC_HI, C::IDESC, 1u << 14, WB_DEBUG_WORD(p));
           else
             gave_up = mma_k_loop<CG, C::REPS>(1u, kleft, uint32_t(rounds), stage, phase, accumulate, full_bar(0), empty_bar(0), d, uint32_t(C::SPAN),
-                                              b_lo0, ATOM16, a_lo0, STAGE16, DESC_HI, C::IDESC, 1u << 14, p.debug);
+                                              b_lo0, ATOM16, a_lo0, STAGE16, DESC_HI, C::IDESC, 1u << 14, WB_DEBUG_WORD(p));
           if (gave_up != 0u && !wait_bar<false, false>(p, abort_addr, full_bar(int(stage)), phase, ST_WAIT_FULL, stage)) {
             ok = false;
             break;
@@ -638,8 +648,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     uint32_t acc_phase = 0;
     bool ok = true;
     const uint32_t acc_empty_leader = (CG == 2) ? mapa(acc_empty_bar(0), 0) : acc_empty_bar(0);
-    // (timing experiments: debug bits 4 and 5 flip the plan's two L2 hints)
-    const uint64_t store_policy = (((p.debug >> 4) ^ uint32_t(p.l2_hints)) & 1u) ? l2_policy_evict_first() : l2_policy_evict_normal();
+    const uint64_t store_policy = (((WB_DEBUG_WORD(p) >> 4) ^ uint32_t(p.l2_hints)) & 1u) ? l2_policy_evict_first() : l2_policy_evict_normal();
     const uint32_t my_staging = staging + uint32_t(q) * uint32_t(C::EPI_COPIES) * C::EPI_COPY_BYTES;
     // K split between CTAs (split-K over the grid, stream-K): hand-off words count launches,
     // never reset: every CTA's own word holds how many launches have gone by, so one past it

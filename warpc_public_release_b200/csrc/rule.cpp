@@ -157,7 +157,7 @@ int effective_group(int group, int walked, int other) {
 }
 
 void append(std::string& s, const char* fmt, ...) {
-  char line[256];
+  char line[512];
   va_list ap;
   va_start(ap, fmt);
   vsnprintf(line, sizeof line, fmt, ap);
@@ -381,6 +381,11 @@ extern "C" int wg_header(const wg_variant* v, int M, int N, int K, char* buf, si
   }
   append(s, "# b200 kernel %s: %dx%d a CTA, ring depth %d, %d accumulator%s, sched %d, cluster %d, tensor memory %d columns",
          wg_kernel_name(li.kernel_id), li.tile_m, li.tile_n, li.depth, li.nbuf, li.nbuf > 1 ? "s" : "", li.sched, li.cluster, li.tmem_cols);
+  // every rule field, so a runner given only this text can rebuild the exact program (a comment to the reference's reader)
+  append(s, "# variant prog=%d tile_m=%d tile_n=%d depth=%d cluster_n=%d clc=%d ask_ahead=%d direct=%d serpentine=%d group=%d streamk=%d "
+            "split=%d split_grid=%d split_add=%d late_launch=%d bufs=%d retile=%d",
+         v->prog, v->tile_m, v->tile_n, v->depth, v->cluster_n, v->clc, v->ask_ahead, v->direct, v->serpentine, v->group, v->streamk, v->split,
+         v->split_grid, v->split_add, v->late_launch, v->bufs, v->retile);
   append(s, ".kernel %s", name);
   append(s, ".sm sm_100a");
   append(s, ".barriers 2");

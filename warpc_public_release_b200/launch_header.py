@@ -56,6 +56,16 @@ def parse_header(text):
     return out
 
 
+def variant_fields(text):
+    """The rule fields wg_header records in its `# variant key=value ...` comment line (a comment, so
+    the reference's reader skips it), as a dict of ints; None when the text has no such line."""
+    for line in text.splitlines():
+        words = line.split()
+        if words[:2] == ["#", "variant"]:
+            return {key: int(value) for key, value in (w.split("=", 1) for w in words[2:])}
+    return None
+
+
 def read_header(path):
     with open(path) as handle:
         return parse_header(handle.read())

@@ -49,20 +49,28 @@ def make_inputs(m, n, k, seed=1):
     return a, rng.integers(-3, 4, size=(n, k)).astype(np.float16), 1e-3
 
 
-def variant_from_header(hdr, m, n, k):
-    """The program a header names: `.kernel swapped_M_N_K_TMxTN_sD` plus the flags in its note line."""
-    name = hdr["kernel"]
-    if name.startswith("one_"):
-        return programs.one(m, n, k, int(name.rsplit("_s", 1)[1]))
-    if name.startswith("pair_"):
-        return programs.pair(m, n, k, int(name.rsplit("_s", 1)[1]))
-    chosen = programs.choose(m, n, k)
-    if launch_header.parse_header(programs.header(chosen, m, n, k))["kernel"] == name:
-        return chosen  # the rule's own program for this shape
-    tm, tn = (int(x) for x in name.rsplit("_", 2)[1].split("x"))
-    depth = int(name.rsplit("_s", 1)[1])
-    return programs.swapped(m, n, k, tm, tn, depth, direct=launch_header.parameter(hdr, "c")["kind"] == "ptr",
-                            clc=int(hdr["grid"].split()[0]) > 148)
+def variant_from_header(text, m, n, k):
+    """The exact program a header text names, rebuilt from its `# variant key=value ...` line (every
+    rule field: tile, depth, cluster launch control, split-K, stream-K, serpentine, accumulators ...).
+    Fails loudly when the line is missing or when the header derived from the rebuilt program is not
+    the text given: a header is never run as some other program under the same kernel name."""
+    f = launch_header.variant_fields(text)
+    if f is None:
+        raise RuntimeError("the header has no '# variant' line: it was not written by this library's gemm command")
+    if f["prog"] == programs._lib.PROG_ONE:
+        v = programs.one(m, n, k, f["depth"])
+    elif f["prog"] == programs._lib.PROG_PAIR:
+        v = programs.pair(m, n, k, f["depth"])
+    elif f["retile"]:
+        v = programs.choose(m, n, k)  # the rule's own program: only wg_choose marks a variant for re-tiling
+    else:
+        v = programs.swapped(m, n, k, f["tile_m"], f["tile_n"], f["depth"], clc=f["clc"], ask_ahead=f["ask_ahead"], direct=f["direct"],
+                             serpentine=f["serpentine"], cluster_n=f["cluster_n"], bufs=f["bufs"], group=f["group"], streamk=f["streamk"],
+                             split=f["split"], split_grid=f["split_grid"], split_add=f["split_add"], late_launch=f["late_launch"])
+    again = programs.header(v, m, n, k)
+    if again != text:
+        raise RuntimeError("the header does not describe a program of this library for %dx%dx%d (re-derived header differs)" % (m, n, k))
+    return v
 
 
 def run(variant, m, n, k, repeat=20, seed=1, name=None, out=sys.stdout):
@@ -134,9 +142,9 @@ def main(argv=None):
         print(__doc__, file=sys.stderr)
         return 2
     if os.path.exists(args[0]):
-        hdr = launch_header.read_header(args[0])
-        m, n, k = launch_header.shape_of(hdr)
-        variant, rest = variant_from_header(hdr, m, n, k), args[1:]
+        text = open(args[0]).read()
+        m, n, k = launch_header.shape_of(launch_header.parse_header(text))
+        variant, rest = variant_from_header(text, m, n, k), args[1:]
     else:
         m, n, k = map(int, args[:3])
         variant, rest = programs.choose(m, n, k), args[3:]
