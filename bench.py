@@ -8,8 +8,12 @@ rows of A and C, Bt is replicated, and the GEMM exchanges nothing ("strong" scal
 fixed).  A step is one call of the hot path (one kernel launch per rank).  `value` is whole-job
 TFLOP/s with inputs resident in HBM, timed with CUDA events on the launching stream, max over
 ranks; `e2e` is the same metric through the host-buffer C-ABI call (pinned host A, Bt in,
-C out, every step).  At N = 1 the line also carries `sweep`: the five mid-size shapes of the
-single-GPU configuration (1536^3 ... 4096^3) and the other benchmark shapes, us/call each.
+C out, every step; at N > 1 every rank uploads only its own rows of A and of Bt, and the Bt
+shards are gathered over NVLink).  cuBLASLt (fastest correct algorithm of its heuristic's list)
+runs on the same buffers in the same process, interleaved with ours: `cublaslt` in the line.  At
+N = 1 the line also carries `shapes`: all eleven benchmark shapes, this library and cuBLASLt,
+each call alone, GPU time from CUPTI, median of the last N calls (the reference's published
+method, README.md:504-525), plus the mean of back-to-back launches.
 
 --impl reference times the reference's own CPU path for the same config -- numpy's fp32 matmul
 of the fp16 operands (backend/node/run_tma.py:67) -- on the host cores, on a bounded sample.
@@ -17,9 +21,7 @@ of the fp16 operands (backend/node/run_tma.py:67) -- on the host cores, on a bou
 import argparse
 import json
 import os
-import subprocess
 import sys
-import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -43,14 +45,23 @@ def measured_peaks():
 from warpc_public_release_b200.clocks import ClockSampler  # noqa: E402
 
 
+_CPU_INPUTS = {}
+
+
+def cpu_inputs(n, k, rows):
+    """The CPU sample's operands, drawn once: `rows` rows of A and all of Bt, uniform[-1,1] fp16 from a seed."""
+    import numpy as np
+    if (n, k, rows) not in _CPU_INPUTS:
+        rng = np.random.default_rng(1)
+        _CPU_INPUTS[(n, k, rows)] = (rng.uniform(-1.0, 1.0, size=(rows, k)).astype(np.float16), rng.uniform(-1.0, 1.0, size=(n, k)).astype(np.float16))
+    return _CPU_INPUTS[(n, k, rows)]
+
+
 def cpu_numpy_sample(m, n, k, rows, repeats=1):
     """The reference's CPU path (numpy fp32 matmul of the fp16 operands, run_tma.py:67) on a
     row slab of the workload: `rows` rows of A against all of Bt.  Returns (seconds, threads)."""
-    import numpy as np
     from oracle import gemm_ref
-    rng = np.random.default_rng(1)
-    a = rng.uniform(-1.0, 1.0, size=(rows, k)).astype(np.float16)
-    bt = rng.uniform(-1.0, 1.0, size=(n, k)).astype(np.float16)
+    a, bt = cpu_inputs(n, k, rows)
     # every host core the process may use, whatever OMP_NUM_THREADS says (torchrun sets it to 1 for its ranks)
     want = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
     try:
@@ -80,12 +91,13 @@ def reference_arm(args, rank):
     if rank != 0:
         return 0
     m, n, k = WORKLOAD
-    rows = 256  # a 256-row slab of A per step: 2*256*16384*16384 = 0.137 TFLOP, seconds of CPU work
-    for _ in range(max(0, min(args.warmup, 1))):
+    rows = 256  # a 256-row slab of A per step: 2*256*16384*16384 = 0.137 TFLOP, about a second of CPU work
+    warmup, steps = max(0, min(args.warmup, 20)), max(1, min(args.steps, 100))   # exactly W and K (bounded: the run stays within minutes)
+    for _ in range(warmup):
         cpu_numpy_sample(m, n, k, rows)
     times = []
     threads = 1
-    for _ in range(max(1, min(args.steps, 5))):
+    for _ in range(steps):
         dt, threads = cpu_numpy_sample(m, n, k, rows)
         times.append(dt)
     sec = sum(times) / len(times)
@@ -93,9 +105,9 @@ def reference_arm(args, rank):
     sample = "rows 0..%d of A (M' = %d of %d) against all of Bt, numpy fp32 matmul incl. fp16->fp32 conversion, mean of %d" % (
         rows, rows, m, len(times))
     line = {"impl": "reference", "metric": METRIC, "value": tflops, "unit": "TFLOP/s",
-            "n_gpus": args.gpus, "steps": len(times), "warmup": min(args.warmup, 1), "ms_per_step": sec * 1e3, "ms_per_full_call_extrapolated": sec * 1e3 * (m / rows),
+            "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": sec * 1e3, "ms_per_full_call_extrapolated": sec * 1e3 * (m / rows),
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16->f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD_NAME, "sample": sample},
+            "config": {"workload": WORKLOAD_NAME},
             "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
             "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
@@ -103,36 +115,60 @@ def reference_arm(args, rank):
     return 0
 
 
-def time_shape(w, torch, m, n, k, repeat, check=True):
-    """One benchmark shape on the current device: parity on its first and last launch, then the
-    mean of `repeat` back-to-back launches between CUDA events.  Returns a dict."""
-    gen = torch.Generator(device="cuda").manual_seed(1)
-    a = (torch.rand((m, k), generator=gen, device="cuda") * 2 - 1).to(torch.float16)
-    bt = (torch.rand((n, k), generator=gen, device="cuda") * 2 - 1).to(torch.float16)
-    c = torch.zeros((m, n), dtype=torch.float32, device="cuda")
-    v = w.choose(m, n, k)
-    plan = w.Plan(v, m, n, k, a.data_ptr(), bt.data_ptr(), c.data_ptr(), device=torch.cuda.current_device())
-    plan.launch()
-    plan.status()
-    ms = plan.time_launches(repeat, warmup=3)
-    plan.status()
-    out = {"shape": [m, n, k], "program": "%dx%d d%d" % (v.tile_m, v.tile_n, v.depth), "us": ms * 1e3,
-           "tflops": 2.0 * m * n * k / ms / 1e9}
-    if check:
-        rows = min(m, 512)
-        ref = a[:rows].float() @ bt.float().T
-        err = float((c[:rows] - ref).abs().max().item())
-        out["max_err_rows0_%d" % rows] = err
-        out["tol"] = 1e-3 * (k ** 0.5)
-        out["ok"] = bool(err <= out["tol"])
-    plan.close()
+def shapes_table(torch, shapes):
+    """Every benchmark shape on uniform[-1,1] inputs: this library's kernel and cuBLASLt, each call alone, GPU time
+    kernel start-to-end from CUPTI, median of the last N calls, ours / cuBLASLt / cuBLASLt / ours (README.md:504-525);
+    and the mean of 50 launches back to back between two events (backend/node/run_tma.py:171-175)."""
+    from warpc_public_release_b200 import ab
+    try:
+        timer = ab.KernelTimer()
+    except Exception:
+        timer = None   # no CUPTI on this box: CUDA events around each call instead, said so per row
+    rows = []
+    for (m, n, k) in shapes:
+        r = ab.ab_shape(torch, timer, m, n, k, inputs="uniform", rounds=1, series=50 if m * n * k < 2 ** 40 else 10, busy_ms=20.0)
+        mid = lambda xs: (min(xs) + max(xs)) / 2
+        rows.append({"shape": [m, n, k], "program": r["program"], "runs_as": r["runs_as"], "us": mid(r["ours_us"]), "ours_us": r["ours_us"],
+                     "cublaslt_us": r["cublaslt_us"], "vs_cublaslt_pct": r["ours_vs_cublaslt_pct"], "tflops": r["ours_tflops"],
+                     "cublaslt_tflops": r["cublaslt_tflops"], "calls_in_median": r["calls_in_median"], "timer": r["timer"],
+                     "max_abs_diff_vs_cublaslt": r["max_abs_diff_vs_cublaslt"], "tol": 1e-3 * (k ** 0.5),
+                     "ok": bool(r["max_abs_diff_vs_cublaslt"] <= 2e-3 * (k ** 0.5)),
+                     "back_to_back_us": {"ours": r["back_to_back"]["ours_us"], "ours_dependent_launch": r["back_to_back"]["ours_dependent_launch_us"],
+                                         "cublaslt": r["back_to_back"]["cublaslt_us"]},
+                     "sm_mhz": r["clocks"].get("sm_mhz"), "published_warpc_us": r["published_warpc_us"], "published_cublas138_us": r["published_cublas138_us"]})
+        torch.cuda.empty_cache()
+    if timer is not None:
+        timer.close()
+    return rows
+
+
+def time_cublaslt(torch, ab, rows, n, k, a, bt, c_ours, steps, tol):
+    """cuBLASLt on the same operands: its fastest correct algorithm, `steps` launches back to back between events, twice."""
+    c_lib = torch.empty_like(c_ours)
+    lt = ab.CublasLt(rows, n, k, a.data_ptr(), bt.data_ptr(), c_lib.data_ptr())
+    best, correct = ab.fastest_correct_algo(torch, lt, c_lib, c_ours, tol, rows * n * k)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    times = []
+    for _ in range(2):
+        for _ in range(3):
+            lt.run(best)
+        e0.record()
+        for _ in range(steps):
+            lt.run(best)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) / steps)
+    out = {"ms_per_step": min(times), "ms_per_step_runs": times, "algo": best, "correct_algos": "%d of %d" % (correct, lt.n_algos), "version": lt.version,
+           "max_abs_diff_vs_ours": ab.max_abs_diff(torch, c_lib, c_ours)}
+    lt.close()
+    del c_lib
     return out
 
 
 def ours(args, rank, world, local_rank):
     import torch
     import warpc_public_release_b200 as w
-    from warpc_public_release_b200 import shard
+    from warpc_public_release_b200 import ab, shard
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device; this library has no CPU path (use --impl reference for the CPU baseline)")
     torch.cuda.set_device(local_rank)
@@ -150,14 +186,21 @@ def ours(args, rank, world, local_rank):
     bt = (torch.rand((n, k), generator=gen, device=dev) * 2 - 1).to(torch.float16)
     gen_a = torch.Generator(device=dev).manual_seed(1000 + rank)
     a = (torch.rand((rows, k), generator=gen_a, device=dev) * 2 - 1).to(torch.float16)
-    job = shard.ShardedGemm(m, n, k, rank, world, a, bt, replicate_c=args.allgather, device=dev)
+    job = shard.ShardedGemm(m, n, k, rank, world, a, bt, device=dev)
     li = job.plan.info()
+    tol = 1e-3 * (k ** 0.5)
 
     def barrier():
         torch.cuda.synchronize()
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
+
+    def over_ranks(x):
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -169,46 +212,71 @@ def ours(args, rank, world, local_rank):
     chk = min(rows, 256)
     ref = a[:chk].float() @ bt.float().T
     err = float((job.c_local[:chk] - ref).abs().max().item())
-    tol = 1e-3 * (k ** 0.5)
-    del ref
     barrier()
     sampler.timed = True
-    if args.allgather and world > 1:
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(args.steps):
-            job.launch()
-        e1.record()
-        torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / args.steps
-    else:
-        ms = job.plan.time_launches(args.steps, warmup=0)  # CUDA events on the launching (default) stream
+    ms = job.plan.time_launches(args.steps, warmup=0)  # CUDA events on the launching (default) stream
     sampler.timed = False
     barrier()
     job.plan.status()
-    t = torch.tensor([ms], dtype=torch.float64, device=dev)
-    if dist is not None:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
+    ms = over_ranks(ms)
+    clocks = sampler.stop() if rank == 0 else None
 
-    # end to end: pinned host A (this rank's rows) and Bt in, C slab out, every step
+    # cuBLASLt on the same operands, same process, right after: library `steps`, library `steps`, ours `steps` once more
+    lib = None
+    if not args.no_cublaslt:
+        try:
+            lib = time_cublaslt(torch, ab, rows, n, k, a, bt, job.c_local, args.steps, tol)
+            lib["ms_per_step"] = over_ranks(lib["ms_per_step"])
+            lib["ours_again_ms_per_step"] = over_ranks(job.plan.time_launches(args.steps, warmup=3))
+        except Exception as e:  # the baseline library failing must not take the measurement with it
+            lib = {"unavailable": str(e)[:200]}
+        barrier()
+
+    # a replicated C (N > 1): the slab in row bands, each band sent to every rank as it completes, NCCL beside the next band's tiles
+    ms_rep = None
+    if world > 1 and not args.no_allgather:
+        rep = shard.ShardedGemm(m, n, k, rank, world, a, bt, replicate_c=True, device=dev)
+        for _ in range(2):
+            rep.launch()
+            rep.wait()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            rep.launch()
+            rep.wait()
+        e1.record()
+        torch.cuda.synchronize()
+        ms_rep = over_ranks(e0.elapsed_time(e1) / args.steps)
+        rep.status()
+        del rep
+        torch.cuda.empty_cache()
+        barrier()
+
+    # end to end: pinned host buffers in and out, every step.  One GPU: the C ABI's host-buffer call.  Several: every rank
+    # uploads its rows of A and its rows of Bt only, the Bt shards are gathered over NVLink, C's rows go back to the host
     e2e_steps = max(1, min(args.steps, 5))
-    hA, hB = a.cpu().pin_memory(), bt.cpu().pin_memory()
+    hA = a.cpu().pin_memory()
     hC = torch.empty((rows, n), dtype=torch.float32).pin_memory()
-    hplan = w.HostPlan(job.variant, rows, n, k, device=local_rank)
-    hplan.run(hA.data_ptr(), hB.data_ptr(), hC.data_ptr())
+    if world == 1:
+        hB = bt.cpu().pin_memory()
+        hplan = w.HostPlan(job.variant, rows, n, k, device=local_rank)
+        run = lambda: hplan.run(hA.data_ptr(), hB.data_ptr(), hC.data_ptr())
+        h2d, d2h = rows * k * 2 + n * k * 2, rows * n * 4
+    else:
+        hplan = shard.ShardedHostGemm(m, n, k, rank, world, dev)
+        hB = bt[hplan.blo:hplan.bhi].cpu().pin_memory()
+        run = lambda: hplan.run(hA, hB, hC)
+        h2d, d2h = hplan.h2d_bytes, hplan.d2h_bytes
+    run()
     barrier()
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
-        hplan.run(hA.data_ptr(), hB.data_ptr(), hC.data_ptr())
+        run()
     torch.cuda.synchronize()
-    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    e2e_s = over_ranks((time.perf_counter() - t0) / e2e_steps)
     hplan.status()
     e2e_err = float((hC[:chk].to(dev) - (a[:chk].float() @ bt.float().T)).abs().max().item())
-    t = torch.tensor([e2e_s], dtype=torch.float64, device=dev)
-    if dist is not None:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_s = float(t.item())
     hplan.close()
     del hA, hB, hC
 
@@ -216,29 +284,47 @@ def ours(args, rank, world, local_rank):
         if dist is not None:
             dist.destroy_process_group()
         return 0
-    clocks = sampler.stop()
     flops = 2.0 * m * n * k
     tflops = flops / (ms * 1e-3) / 1e12
     peaks, which = measured_peaks()
     per_gpu = tflops / world
+    # which measured peak the timed region compares with: the clock record says whether it ran at the burst clock or under
+    # the power cap's sustained one (the driver measured cuBLAS both ways)
+    sm, sm_max = clocks.get("sm_mhz"), clocks.get("sm_max_mhz")
+    burst = bool(sm and sm_max and sm >= 0.93 * sm_max)
+    peak = peaks["bf16_tflops"] if burst else peaks["bf16_tflops_sustained"]
     line = {
         "metric": METRIC, "value": tflops, "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "us_per_call": ms * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f16->f32", "data": "synthetic",
         "config": {"workload": WORKLOAD_NAME,
-                   "parallelism": "M-row blocks over %d GPU(s), Bt replicated, no collective%s" % (world, " + NCCL all-gather of C" if args.allgather and world > 1 else ""),
+                   "parallelism": "M-row blocks over %d GPU(s), Bt replicated, no collective" % world,
                    "per_gpu_shape": [rows, n, k], "program": "%dx%d d%d %s" % (li.tile_m, li.tile_n, li.depth, w._lib.lib().wg_kernel_name(li.kernel_id).decode()),
                    "l2": "inputs (%.1f GB per GPU) exceed the 126 MB L2; no flush between steps" % ((rows * k * 2 + n * k * 2 + rows * n * 4) / 1e9)},
         "parity": {"max_err": err, "tol": tol, "ok": bool(err <= tol), "e2e_max_err": e2e_err, "rows_checked": chk},
-        "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
-                     "frac": per_gpu / peaks["bf16_tflops_sustained"], "peak_source": which + " (cuBLAS bf16 sustained)",
-                     "frac_of_burst": per_gpu / peaks["bf16_tflops"], "frac_of_nominal_2250": per_gpu / NOMINAL_TFLOPS,
+        "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peak, "unit": "TFLOP/s", "frac": per_gpu / peak,
+                     "peak_source": "%s cuBLAS bf16 %s, chosen by the clock record (median SM clock %s of %s MHz in the timed region)" % (
+                         which, "burst" if burst else "sustained under the power cap", sm, sm_max),
+                     "frac_of_burst": per_gpu / peaks["bf16_tflops"], "frac_of_sustained": per_gpu / peaks["bf16_tflops_sustained"],
+                     "frac_of_nominal_2250": per_gpu / NOMINAL_TFLOPS,
                      "traffic": TRAFFIC_BYTES_PER_LAUNCH if world == 1 else None, "algorithmic_bytes": 2 * rows * k + 2 * n * k + 4 * rows * n},
         "e2e": {"value": flops / e2e_s / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_s * 1e3, "steps": e2e_steps,
-                "h2d_bytes_per_step": world * (rows * k * 2 + n * k * 2), "d2h_bytes_per_step": world * rows * n * 4},
+                "h2d_bytes_per_step": world * h2d, "d2h_bytes_per_step": world * d2h,
+                "path": "wg_host_run (C ABI, pipelined blocks)" if world == 1 else "per-rank rows of A and of Bt uploaded, Bt shards all-gathered over NVLink (NCCL), C rows downloaded"},
         "gpu_launches": args.steps * world,
         "clocks": clocks,
     }
+    if lib is not None:
+        if "ms_per_step" in lib:
+            lib["tflops"] = flops / (lib["ms_per_step"] * 1e-3) / 1e12
+            lib["vs_cublaslt_pct"] = 100.0 * (lib["ms_per_step"] / min(ms, lib["ours_again_ms_per_step"]) - 1.0)
+            lib["method"] = "same operands and process: ours %d steps (the timed region), cuBLASLt %d steps twice (faster kept), ours %d steps again; back to back between CUDA events, max over ranks" % (
+                args.steps, args.steps, args.steps)
+        line["cublaslt"] = lib
+    if ms_rep is not None:
+        line["ms_per_step_with_allgather"] = ms_rep
+        line["replicated_c"] = {"ms_per_step": ms_rep, "vs_sharded": ms_rep / ms,
+                                "how": "slab in 4 row bands on two streams, each band sent to every rank (grouped NCCL send/recv, in place) while the next band's tiles run"}
     if world == 1 and not args.no_cpu:
         crow = 256
         sec, threads = cpu_numpy_sample(m, n, k, crow)
@@ -246,14 +332,19 @@ def ours(args, rank, world, local_rank):
                                 "sample": "%d rows of A against all of Bt (%.3f TFLOP), numpy fp32 matmul incl. fp16->fp32 conversion, %.1f s" % (
                                     crow, 2.0 * crow * n * k / 1e12, sec)}
     if world == 1 and not args.no_sweep:
-        del job
+        del job, a, bt
         torch.cuda.empty_cache()
-        sweep = [time_shape(w, torch, *s, repeat=50) for s in SWEEP]
-        others = [time_shape(w, torch, *s, repeat=30) for s in OTHERS]
-        tot_f = sum(2.0 * a_ * b_ * c_ for a_, b_, c_ in SWEEP)
-        tot_t = sum(x["us"] for x in sweep) * 1e-6
-        line["sweep"] = {"workload": "mid-size single-GPU sweep: " + ", ".join("%dx%dx%d" % s for s in SWEEP), "tflops": tot_f / tot_t / 1e12,
-                         "timing": "mean of 50 back-to-back launches between CUDA events, per shape", "shapes": sweep, "other_shapes": others}
+        try:
+            table = shapes_table(torch, ab.SHAPES)
+            sweep = [r for r in table if tuple(r["shape"]) in SWEEP]
+            tot_f = sum(2.0 * r["shape"][0] * r["shape"][1] * r["shape"][2] for r in sweep)
+            tot_t = sum(r["back_to_back_us"]["ours"] for r in sweep) * 1e-6
+            line["shapes"] = {"method": "uniform[-1,1] inputs; us = GPU time of a call run alone (median of the last N calls, ours / cuBLASLt / cuBLASLt / ours); "
+                                        "back_to_back_us = mean of launches back to back between CUDA events",
+                              "within_2pct_of_cublaslt": sum(1 for r in table if r["vs_cublaslt_pct"] >= -2.0), "of": len(table),
+                              "mid_size_sweep_tflops_back_to_back": tot_f / tot_t / 1e12, "rows": table}
+        except Exception as e:
+            line["shapes"] = {"unavailable": str(e)[:300]}
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
@@ -261,8 +352,7 @@ def ours(args, rank, world, local_rank):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel on the one-GPU
-# workload (16384^3), from the one-pass ncu capture summarised in
-# profiles/gemm_kernel_pair_256x256_16384x16384x16384_dram.md: 7.92 GB read + 1.06 GB written.
+# workload (16384^3), from a one-pass ncu capture of those two counters: 7.92 GB read + 1.06 GB written.
 # No capture exists for the per-GPU slabs of a sharded run, so those lines carry null.
 TRAFFIC_BYTES_PER_LAUNCH = 8.98e9
 
@@ -273,7 +363,8 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--allgather", action="store_true", help="replicate C on every rank with an NCCL all-gather inside the step")
+    ap.add_argument("--no-allgather", action="store_true", help="N > 1: skip the extra leg that also replicates C on every rank")
+    ap.add_argument("--no-cublaslt", action="store_true")
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()

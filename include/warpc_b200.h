@@ -69,6 +69,7 @@ typedef struct wg_launch_info {
   int wide_rows;           /* C rows per store of a CTA's last tile when it is staged whole in the drained ring, else 0 */
   int stage_bytes;         /* one ring slot: this CTA's A half-tile and B^T tile of one k-step */
   int staging_bytes;       /* the epilogue's cycling staging copies; 0 where every tile is staged in the drained ring */
+  int ws_words;            /* fp32 words of workspace (a slot of tile_m x tile_n per CTA) when K is shared through a workspace, else 0 */
 } wg_launch_info;
 
 /* `warpc gemm M N K`: the program chosen for a shape (backend/programs.ml:46-80).
@@ -157,7 +158,8 @@ int wg_tile_origin(const wg_launch_info* li, int tile, int* row, int* col);
  * words (split-K / stream-K hand-off flags, status) live in a device array built into the
  * library: wg_noalloc_max_flags() + 8 words (16 KiB + 32 B) held by every GPU that loads it.
  *   - v == NULL takes the rule's program for the shape (wg_choose); dA, dBt, dC as wg_plan_create.
- *   - WG_E_LIMIT when the program needs more hand-off words than wg_noalloc_max_flags().
+ *   - WG_E_LIMIT when the program needs more hand-off words than wg_noalloc_max_flags(), or a
+ *     workspace for partial sums (the explicitly named workspace forms of split-K / stream-K).
  *   - The first call on a device looks up the array's device address; make that call before
  *     any stream capture begins.
  *   - Every call on a device shares the array: the call clears the words it uses on `cuda_stream`

@@ -151,6 +151,31 @@ def test_realisation_invariants():
     assert w.choose(2048, 2048, 2048).tile_m == 128 and w.choose(2048, 2048, 2048).retile == 1
 
 
+def test_workspace_forms_are_realised_as_named():
+    # explicitly named: the store from the registers with K shared means partial sums through a workspace, a slot a CTA
+    s = (512, 1024, 4096)
+    li = w.realise(w.swapped(*s, 256, 256, 4, split_grid=4, direct=True), *s)
+    assert (li.direct, li.sched, li.split, li.grid, li.ws_words) == (1, 3, 4, 32, 32 * 256 * 256)
+    assert ".ptr ws 32 65536 4" in w.header(w.swapped(*s, 256, 256, 4, split_grid=4, direct=True), *s)
+    li = w.realise(w.swapped(*s, 256, 256, 4, split_grid=4, split_add=True), *s)
+    assert (li.direct, li.sched, li.ws_words) == (0, 3, 0)
+    s = (2560, 2048, 512)
+    li = w.realise(w.swapped(*s, 256, 128, 6, streamk=True, direct=True, bufs=2), *s)
+    assert (li.direct, li.sched, li.grid, li.ws_words) == (1, 4, 148, 148 * 256 * 128)
+    # the rule's own split-in-cluster choice keeps adding in the L2
+    s = (1024, 1024, 16384)
+    v = w.choose(*s)
+    assert (v.split, v.cluster_n, v.direct) == (2, 2, 1)
+    li = w.realise(v, *s)
+    assert (li.direct, li.sched, li.split, li.ws_words) == (0, 3, 2, 0)
+    # named explicitly, the same program goes through the workspace
+    li = w.realise(w.swapped(*s, 128, 128, 9, split=2, cluster_n=2, direct=True), *s)
+    assert (li.direct, li.sched, li.split) == (1, 3, 2) and li.ws_words > 0
+    # a stream-K share shorter than a tile's k-steps could give a tile three parts: refused for the workspace form
+    with pytest.raises(_lib.WarpcError):
+        w.swapped(1024, 1024, 4096, 256, 128, 6, streamk=True, direct=True, bufs=2)
+
+
 def test_gemm_command_line():
     run = lambda *a: subprocess.run([sys.executable, "-m", "warpc_public_release_b200.gemm", *a], cwd=ROOT, capture_output=True, text=True)
     ok = run("gemm", "2048", "2048", "2048")

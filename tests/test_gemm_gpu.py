@@ -67,6 +67,11 @@ CASES = [
     ("split_k_grid_uneven", (512, 1024, 1088), lambda s: SW(*s, 256, 256, 4, split_grid=3, split_add=True, ask_ahead=True)),
     ("split_k_more_runs_than_blocks", (256, 512, 4096), lambda s: SW(*s, 256, 256, 4, split_grid=37, split_add=True)),
     ("split_k_workspace_variant", (512, 1024, 4096), lambda s: SW(*s, 256, 256, 4, split_grid=4, direct=True)),  # the reference's ws + FADD form
+    ("split_k_workspace_uneven", (512, 1024, 1088), lambda s: SW(*s, 256, 256, 4, split_grid=3, direct=True)),
+    ("split_k_workspace_more_runs_than_blocks", (256, 512, 4096), lambda s: SW(*s, 256, 256, 4, split_grid=37, direct=True)),
+    ("split_in_cluster_workspace", (256, 512, 16384), lambda s: SW(*s, 128, 128, 9, split=2, cluster_n=2, direct=True)),
+    ("stream_k_workspace", (2560, 2048, 512), lambda s: SW(*s, 256, 128, 6, streamk=True, direct=True, bufs=2)),
+    ("stream_k_workspace_fold", (1280, 1024, 1024), lambda s: SW(*s, 128, 64, 8, streamk=True, direct=True)),
     ("stream_k", (1024, 512, 1024), lambda s: SW(*s, 256, 128, 6, streamk=True, split_add=True, bufs=2, ask_ahead=True)),
     ("stream_k_long", (1024, 1024, 4096), lambda s: SW(*s, 256, 128, 6, streamk=True, split_add=True, bufs=2)),
     ("fold_rounds_partial_last_round", (256, 256, 448), lambda s: SW(*s, 128, 64, 12, direct=True)),   # 7 k-steps in rounds of 4
@@ -82,6 +87,22 @@ CASES = [
 @pytest.mark.parametrize("name,shape,build", CASES, ids=[c[0] for c in CASES])
 def test_variant_against_oracle(name, shape, build, family):
     check(build(shape), *shape, family)
+
+
+@pytest.mark.parametrize("name,shape,build", [c for c in CASES if "workspace" in c[0]], ids=lambda x: x if isinstance(x, str) else None)
+def test_workspace_forms_give_the_same_bits_every_launch(name, shape, build):
+    """K shared through a workspace adds the partial sums in a fixed order (gemm_swapped.ml:45-48 names this as what the
+    L2-add forms give up): on uniform inputs, where the order of fp32 additions shows, launch after launch and plan
+    after plan leave identical bits, within the tolerance of the oracle's product."""
+    m, n, k = shape
+    a, bt = gemm_ref.inputs_uniform(m, n, k)
+    v = build(shape)
+    li = w.realise(v, m, n, k)
+    assert li.direct == 1 and li.sched in (3, 4) and li.ws_words == li.grid * li.tile_m * li.tile_n
+    first = run_gemm(v, m, n, k, a, bt, launches=1)
+    again = run_gemm(v, m, n, k, a, bt, launches=5, dependent=True)
+    assert np.array_equal(first, again)
+    assert gemm_ref.count_wrong(first, gemm_ref.gemm_ref(a, bt), gemm_ref.tolerance("uniform", k, a, bt)) == 0
 
 
 @pytest.mark.parametrize("name,shape,build", [c for c in CASES if c[0].startswith(("split", "stream", "clc", "persistent"))],
@@ -174,8 +195,80 @@ def test_benchmark_shape_full_size_properties(shape):
     assert np.array_equal(c.astype(np.float64).sum(axis=0), (bt.astype(np.int64) @ a.astype(np.int64).sum(axis=0)).astype(np.float64))
 
 
-@pytest.mark.parametrize("shape", [(2048, 2048, 2048), (4096, 4096, 4096), (1024, 1024, 65536)], ids=lambda s: "x".join(map(str, s)))
+# ---- the shape that shards (16384^3) and its per-GPU slabs: inputs and checks stay on the device, tied to the oracle by samples
+
+BIG = 16384
+
+
+@pytest.fixture(scope="module")
+def big_hash_inputs():
+    """A and B^T of 16384^3 on the index-hash inputs (run_tma.py:58-62), evaluated on the device in row chunks; three rows
+    of each are compared with the oracle's own generator, so the device copy is the oracle's matrix."""
+    def matrix(rows, cols, salt):
+        out = torch.empty((rows, cols), dtype=torch.float16, device="cuda")
+        step = 2048
+        for r0 in range(0, rows, step):
+            i = torch.arange(r0 * cols, (r0 + step) * cols, dtype=torch.int64, device="cuda")
+            out[r0:r0 + step] = ((((i * 2654435761 + salt) >> 13) % 7) - 3).to(torch.float16).reshape(step, cols)
+        for r in (0, rows // 3 + 1, rows - 1):
+            assert np.array_equal(out[r].cpu().numpy().astype(np.int64), gemm_ref._hash_values_range(r * cols, cols, salt))
+        return out
+    a, bt = matrix(BIG, BIG, 1), matrix(BIG, BIG, 7)
+    yield a, bt
+    del a, bt
+    torch.cuda.empty_cache()
+
+
+def device_properties_exact(c, a, bt, row0=0):
+    """Size-independent checks of C = A . Bt^T on the hash inputs without a full CPU product: 64 sampled entries against
+    the oracle's integer dot products (cublas_q7.cpp:91-97), every row checksum and every column checksum exact
+    (sum_j C[i,j] = A[i,:] . sum_j Bt[j,:]; all quantities are integers below 2^53, so float64 sums are exact in any order).
+    `a`, `c` hold rows row0.. of the full A and C."""
+    m, k = a.shape
+    n = bt.shape[0]
+    for s_ in range(64):
+        i, j = (s_ * 7919 + 13) % m, (s_ * 104729 + 5) % n
+        want = int(np.dot(gemm_ref._hash_values_range((row0 + i) * k, k, 1), gemm_ref._hash_values_range(j * k, k, 7)))
+        assert float(c[i, j].item()) == float(want), (i, j)
+    bsum = bt.sum(dim=0, dtype=torch.float64)
+    asum = a.sum(dim=0, dtype=torch.float64)
+    # the expected checksums themselves against the oracle's integers, at three rows / columns
+    for i in (0, m // 2 + 3, m - 1):
+        ra = gemm_ref._hash_values_range((row0 + i) * k, k, 1)
+        assert float((a[i].double() * bsum).sum().item()) == float(int(np.dot(ra, bsum.cpu().numpy().astype(np.int64))))
+    step = 2048
+    for r0 in range(0, m, step):
+        want_rows = a[r0:r0 + step].double() @ bsum
+        assert torch.equal(c[r0:r0 + step].sum(dim=1, dtype=torch.float64), want_rows), "row checksums of rows %d.." % r0
+    for c0 in range(0, n, step):
+        want_cols = bt[c0:c0 + step].double() @ asum
+        assert torch.equal(c[:, c0:c0 + step].sum(dim=0, dtype=torch.float64), want_cols), "column checksums of columns %d.." % c0
+
+
+@pytest.mark.parametrize("gpus", [1, 2, 4, 8])
+def test_sharded_shape_and_its_slabs_full_size(big_hash_inputs, gpus):
+    """16384^3 (gpus = 1: the program the rule picks) and the slab one of 2 / 4 / 8 GPUs owns (the program
+    shard.slab_variant pins), two launches each, on rows [M/g, 2M/g) of A -- a slab that does not start at row 0."""
+    from warpc_public_release_b200 import shard
+    a, bt = big_hash_inputs
+    rank = 1 if gpus > 1 else 0
+    lo, hi = shard.slab_rows(BIG, gpus, rank)
+    rows = hi - lo
+    v = w.choose(BIG, BIG, BIG) if gpus == 1 else shard.slab_variant(rows, BIG, BIG)
+    c = torch.full((rows, BIG), float("nan"), dtype=torch.float32, device="cuda")
+    plan = w.Plan(v, rows, BIG, BIG, a[lo:hi].data_ptr(), bt.data_ptr(), c.data_ptr())
+    plan.set_timeout_ms(2000)
+    plan.launch()
+    plan.launch()
+    plan.status()
+    plan.close()
+    device_properties_exact(c, a[lo:hi], bt, row0=lo)
+
+
+@pytest.mark.parametrize("shape", BENCH_SHAPES + [(BIG, BIG, BIG)], ids=lambda s: "x".join(map(str, s)))
 def test_benchmark_shape_uniform_inputs_within_tolerance(shape):
+    """Every benchmark shape on uniform[-1,1] inputs: 64 rows spread over M against the oracle within
+    1e-3 sqrt(K) max|A| max|B|; up to 4096^3 also linearity (the same kernel on 2A)."""
     m, n, k = shape
     a, bt = gemm_ref.inputs_uniform(m, n, k)
     c = run_gemm(w.choose(m, n, k), m, n, k, a, bt)
@@ -183,12 +276,98 @@ def test_benchmark_shape_uniform_inputs_within_tolerance(shape):
     ref = gemm_ref.gemm_ref(a[rows], bt)
     tol = gemm_ref.tolerance("uniform", k, a, bt)
     assert float(np.abs(c[rows] - ref).max()) <= tol
+    if m * n * k > 4096 ** 3:
+        return
     # linearity: the same kernel on 2A gives exactly 2C (scaling by a power of two is exact in fp16 and fp32)
     c2 = run_gemm(w.choose(m, n, k), m, n, k, (a * np.float16(2)).astype(np.float16), bt)
-    if k <= 16384 and not w.choose(m, n, k).split_add:
+    if not w.realise(w.choose(m, n, k), m, n, k).sched in (3, 4):
         assert np.array_equal(c2[rows], 2 * c[rows])
     else:  # L2 adds land in any order: equal within the tolerance only
         assert float(np.abs(c2[rows] - 2 * c[rows]).max()) <= 2 * tol
+
+
+def test_phase_stamps_layout_and_order():
+    """Timing builds' stamps (the reference's: backend/stamp.ml:9-24, decoded by run_tma.py:176-203): a launch of two tiles
+    a CTA on a fixed grid, stamps on.  Per CTA 64 events x 4 tile slots; events are GPU-timer nanoseconds and must come
+    in the documented order, slots of tiles a CTA never ran stay zero, MMA events exist in pair leaders only, and the
+    product is still exact."""
+    m, n, k = 256 * 74 * 2, 256, 512          # 296 CTA tiles of 256 x 128 on 148 CTAs: two tiles each
+    a, bt = gemm_ref.inputs_integers(m, n, k)
+    v = w.swapped(m, n, k, 256, 128, 5)
+    li = w.realise(v, m, n, k)
+    assert (li.sched, li.grid) == (1, 148)
+    da, db = torch.from_numpy(a).cuda(), torch.from_numpy(bt).cuda()
+    dc = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+    plan = w.Plan(v, m, n, k, da.data_ptr(), db.data_ptr(), dc.data_ptr())
+    plan.launch()
+    plan.enable_stamps(True)
+    plan.launch()
+    st = plan.read_stamps().astype(np.int64)
+    plan.enable_stamps(False)
+    plan.status()
+    assert st.shape == (148, 32, 4)
+    assert np.array_equal(dc.cpu().numpy(), gemm_ref.gemm_ref(a, bt))
+    ENTRY, SETUP, LOAD_FIRST, LOAD_LAST, MMA_FIRST, MMA_LAST, ACC_READY, STORED, TEARDOWN, EXIT, ACC_FREE = range(11)
+    assert not st[:, :15, 2:].any() and not st[:, 22, 2:].any()          # tiles 3 and 4 never ran
+    assert not st[:, [15, 16, 17, 18, 19, 20, 21, 23], 1:].any()            # set-up / teardown events are per launch: tile slot 0 only
+    for cta in range(148):
+        e = st[cta]
+        leader = cta % 2 == 0
+        # set-up: entry <= barriers initialised (16), tensor memory allocated (17), first tile found (18) <= CTAs met (23) <= set-up done
+        for ev in (16, 17, 18):
+            assert e[ENTRY, 0] <= e[ev, 0] <= e[23, 0], (cta, ev)
+        assert e[23, 0] <= e[SETUP, 0] <= e[LOAD_FIRST, 0]
+        for t in range(2):
+            assert 0 < e[LOAD_FIRST, t] <= e[LOAD_LAST, t]
+            assert e[LOAD_FIRST, t] < e[ACC_READY, t] <= e[STORED, t]
+            if leader:
+                assert e[ACC_FREE, t] <= e[MMA_FIRST, t] <= e[MMA_LAST, t] <= e[ACC_READY, t] + 1000, (cta, t)
+                assert e[LOAD_FIRST, t] < e[MMA_FIRST, t]
+            else:
+                assert not e[[MMA_FIRST, MMA_LAST, ACC_FREE], t].any()
+        assert e[LOAD_FIRST, 0] < e[LOAD_FIRST, 1] and e[STORED, 0] < e[STORED, 1]
+        # teardown, per stamping thread: the first epilogue warp's stores issued <= read (19); thread 0's roles done <= CTAs met
+        # (20) <= exit; tensor memory is freed (21) by the MMA warp after the CTAs met (the timer ticks every 32 ns)
+        assert e[STORED, 1] <= e[19, 0] and e[TEARDOWN, 0] <= e[20, 0] <= e[EXIT, 0] and e[20, 0] <= e[21, 0] + 64
+        assert e[15, 0] > 0                                                 # SM cycles entry to exit
+        assert 0 < e[EXIT, 0] - e[ENTRY, 0] < 1_000_000                     # under a millisecond
+    plan.close()
+
+
+def test_one_thread_two_devices_and_replicated_c():
+    """Two GPUs (skipped with fewer).  (1) One host thread drives a plan on each device in turn, the current device
+    left where the caller had it.  (2) Two ranks under NCCL: ShardedGemm with a replicated C; every rank's gathered C
+    equals the oracle's product."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    m, n, k = 512, 1024, 512
+    a, bt = gemm_ref.inputs_integers(m, n, k)
+    ref = gemm_ref.gemm_ref(a, bt)
+    torch.cuda.set_device(0)
+    outs, plans = [], []
+    for dev in (0, 1):
+        da, db = torch.from_numpy(a).to("cuda:%d" % dev), torch.from_numpy(bt).to("cuda:%d" % dev)
+        dc = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda:%d" % dev)
+        plans.append((w.Plan(w.choose(m, n, k), m, n, k, da.data_ptr(), db.data_ptr(), dc.data_ptr(), device=dev), da, db))
+        outs.append(dc)
+        assert torch.cuda.current_device() == 0
+    for _ in range(3):
+        for p, _, _ in plans:
+            p.launch()
+            assert torch.cuda.current_device() == 0
+    for (p, _, _), dc in zip(plans, outs):
+        p.status()
+        assert np.array_equal(dc.cpu().numpy(), ref)
+        p.close()
+    import subprocess
+    import sys as _sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([_sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+                        "--master-port", "29541", os.path.join(root, "tests", "replicated_c_ranks.py")], cwd=root, env=env,
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert r.stdout.count("replicated C ok") == 2
 
 
 def test_host_buffer_entry_matches_device_entry():
@@ -226,6 +405,26 @@ def test_host_buffer_entry_pipelined_blocks():
         hp.status()
         assert np.array_equal(hc.numpy(), want)
     hp.close()
+
+
+def test_plans_sharing_a_kernel_with_rings_of_different_depth():
+    # the dynamic shared memory limit is an attribute of the kernel function, not of a launch: a plan with a shallow ring
+    # made after a plan with a deep one must not lower it under the first plan's launches
+    m, n, k = 512, 512, 512
+    a, bt = gemm_ref.inputs_integers(m, n, k)
+    da, db = torch.from_numpy(a).cuda(), torch.from_numpy(bt).cuda()
+    outs, plans = [], []
+    for depth in (6, 2, 4):
+        dc = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+        plans.append(w.Plan(SW(m, n, k, 256, 128, depth), m, n, k, da.data_ptr(), db.data_ptr(), dc.data_ptr()))
+        outs.append(dc)
+    for p in plans + plans[::-1]:
+        p.launch()
+    ref = gemm_ref.gemm_ref(a, bt)
+    for p, dc in zip(plans, outs):
+        p.status()
+        assert np.array_equal(dc.cpu().numpy(), ref)
+        p.close()
 
 
 def test_edges_and_errors():

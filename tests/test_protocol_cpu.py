@@ -24,6 +24,10 @@ VARIANTS = [
     ("split_k_more_runs_than_blocks", (256, 512, 4096), lambda s: SW(*s, 256, 256, 4, split_grid=37, split_add=True)),
     ("stream_k", (1024, 512, 1024), lambda s: SW(*s, 256, 128, 6, streamk=True, split_add=True, bufs=2)),
     ("stream_k_rounds", (512, 512, 1088), lambda s: SW(*s, 128, 128, 8, streamk=True, split_add=True, bufs=2)),
+    ("split_k_workspace", (512, 1024, 4096), lambda s: SW(*s, 256, 256, 4, split_grid=4, direct=True)),
+    ("split_k_workspace_uneven", (512, 1024, 1088), lambda s: SW(*s, 256, 256, 4, split_grid=3, direct=True)),
+    ("split_in_cluster_workspace", (256, 512, 16384), lambda s: SW(*s, 128, 128, 9, split=2, cluster_n=2, direct=True)),
+    ("stream_k_workspace", (2560, 2048, 512), lambda s: SW(*s, 256, 128, 6, streamk=True, direct=True, bufs=2)),
     ("rule_2048", (2048, 2048, 2048), lambda s: w.choose(*s)),
     ("rule_4096_stream_k", (4096, 4096, 1024 * 2), lambda s: w.choose(*s)),
     ("rule_split_k_long", (1024, 1024, 8192), lambda s: w.choose(*s)),
@@ -55,6 +59,19 @@ def test_a_broken_protocol_is_caught(mutation, needle):
     assert needle in str(e.value)
 
 
+@pytest.mark.parametrize("name,shape,build", [
+    ("split_k_workspace", (512, 1024, 4096), lambda s: SW(*s, 256, 256, 4, split_grid=4, direct=True)),
+    ("stream_k_workspace", (2560, 2048, 512), lambda s: SW(*s, 256, 128, 6, streamk=True, direct=True, bufs=2))], ids=["split", "stream"])
+def test_partial_sums_read_before_their_flag_is_caught(name, shape, build):
+    # through the workspace a CTA adds other CTAs' partial sums: without the wait for their flags it reads slots not written yet
+    v = build(shape)
+    assert protocol.check(v, *shape) > 0
+    with pytest.raises(protocol.Violation) as e:
+        for seed in range(6):
+            protocol.check(v, *shape, seed=seed, mutate={"ws_no_flag_wait": True})
+    assert "partial sums" in str(e.value)
+
+
 @pytest.mark.parametrize("shape", [(1024, 1024, 1024), (1536, 1536, 1536), (3072, 1280, 2048), (4096, 4096, 1024), (1024, 1024, 65536)],
                          ids=lambda s: "x".join(map(str, s)))
 def test_the_rules_program_for_a_benchmark_shape(shape):
@@ -72,7 +89,7 @@ def test_random_variants_small_shapes():
         m = tm * rng.randint(1, 5) - rng.choice([0, 0, 0, 64])
         n = 2 * tn * rng.randint(1, 4)
         k = 64 * rng.randint(1, 24)
-        kind = rng.choice(["plain", "plain", "clc", "split", "stream"])
+        kind = rng.choice(["plain", "plain", "clc", "split", "stream", "split_ws", "stream_ws"])
         kw = dict(bufs=rng.choice([None, 1, 2]), group=rng.choice([1, 2, 8]), serpentine=rng.random() < 0.3)
         if kind == "clc":
             kw.update(clc=True)
@@ -80,6 +97,11 @@ def test_random_variants_small_shapes():
             kw.update(split_grid=rng.randint(2, 5), split_add=True)
         elif kind == "stream":
             kw.update(streamk=True, split_add=True, bufs=2)
+        elif kind == "split_ws":
+            kw.update(split_grid=rng.randint(2, 5), direct=True)
+        elif kind == "stream_ws":
+            m, n = tm * rng.randint(8, 12), 2 * tn * rng.randint(3, 5)   # a tile's worth of k-steps per cluster at least
+            kw.update(streamk=True, direct=True, bufs=2)
         try:
             v = SW(m, n, k, tm, tn, rng.randint(2, 12), **kw)
             w.realise(v, m, n, k)

@@ -10,6 +10,17 @@ Before each side's turn the GPU is kept busy for a few tens of milliseconds so t
 the loaded ones, not the idle ones.
 
     python -m warpc_public_release_b200.ab [--inputs hash|uniform] [--json out.json] [M N K ...]
+
+--event-rounds R is the reference harness's other method (backend/node/ab.py:121-175): R rounds, the
+order of the sides alternating, each side's turn --repeat launches back to back between two CUDA
+events.  With it: --gap S idles S seconds before each turn (short runs after a gap stay under the
+power cap, at the full clock: AB_GAP); --block queues each turn behind a long kernel on buffers of
+its own, launched and not waited for, so the timed launches are all queued before the first of them
+runs, whatever launching from Python costs (AB_BLOCK); --warm MS runs the side's own kernel for
+about MS milliseconds right before its timed launches, not waited for (AB_WARM); --each prints
+every turn as it is taken with the SM clock, the clock's limiting reasons and the energy the device
+used per call, from NVML's counters, read-only (AB_EACH); --pdl lets each of this library's launches
+begin while the one before it runs (AB_PDL).
 """
 import argparse
 import ctypes
@@ -102,6 +113,44 @@ def make_inputs(torch, kind, m, n, k):
     return a, bt
 
 
+def max_abs_diff(torch, x, y):
+    """max |x - y| in row blocks (no temporary the size of the matrices)."""
+    worst, step = 0.0, max(1, (64 << 20) // max(1, x.shape[1]))
+    for r0 in range(0, x.shape[0], step):
+        worst = max(worst, float((x[r0:r0 + step] - y[r0:r0 + step]).abs().max().item()))
+    return worst
+
+
+def fastest_correct_algo(torch, lt, c_lib, c_ours, tol, work):
+    """The fastest cuBLASLt algorithm of the heuristic's list whose C agrees with `c_ours` within `tol`
+    (backend/node/cublas_q7.cpp:61-63, 84-127), by a quick event timing of each candidate.  Returns (index, how many were correct)."""
+    best, best_ms, correct = -1, None, 0
+    for algo in range(lt.n_algos):
+        c_lib.zero_()
+        try:
+            lt.run(algo)
+        except RuntimeError:
+            continue
+        torch.cuda.synchronize()
+        if max_abs_diff(torch, c_lib, c_ours) > tol:
+            continue
+        correct += 1
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 20 if work < 2 ** 36 else (5 if work < 2 ** 40 else 2)
+        for _ in range(min(3, reps)):
+            lt.run(algo)
+        e0.record()
+        for _ in range(reps):
+            lt.run(algo)
+        e1.record(); torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        if best_ms is None or ms < best_ms:
+            best, best_ms = algo, ms
+    if best < 0:
+        raise RuntimeError("no correct cuBLASLt algorithm")
+    return best, correct
+
+
 def ab_shape(torch, timer, m, n, k, inputs="hash", rounds=2, variant=None, busy_ms=30.0, series=0):
     a, bt = make_inputs(torch, inputs, m, n, k)
     c_ours = torch.zeros((m, n), dtype=torch.float32, device="cuda")
@@ -125,35 +174,22 @@ def ab_shape(torch, timer, m, n, k, inputs="hash", rounds=2, variant=None, busy_
             run()
         torch.cuda.synchronize()
 
-    # the fastest correct cuBLASLt algorithm, by a quick event timing of each candidate
-    best, best_ms, correct = -1, None, 0
-    for algo in range(lt.n_algos):
-        c_lib.zero_()
-        try:
-            lt.run(algo)
-        except RuntimeError:
-            continue
-        torch.cuda.synchronize()
-        err = float((c_lib - c_ours).abs().max().item())
-        if err > tol:
-            continue
-        correct += 1
+    best, correct = fastest_correct_algo(torch, lt, c_lib, c_ours, tol, m * n * k)
+
+    def by_events(run):
+        # without CUPTI: each call alone between two events (includes the launch's latency on the stream), median of the last N
+        ts = []
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        for _ in range(3):
-            lt.run(algo)
-        reps = 20 if m * n * k < 2 ** 36 else 5
-        e0.record()
-        for _ in range(reps):
-            lt.run(algo)
-        e1.record(); torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / reps
-        if best_ms is None or ms < best_ms:
-            best, best_ms = algo, ms
-    if best < 0:
-        raise RuntimeError("no correct cuBLASLt algorithm for %dx%dx%d" % (m, n, k))
+        for _ in range(calls):
+            e0.record(); run(); e1.record(); torch.cuda.synchronize()
+            ts.append(1e3 * e0.elapsed_time(e1))
+        ts = sorted(ts[-last:])
+        return ts[len(ts) // 2]
 
     def isolated(run, tag):
         busy(run)
+        if timer is None:
+            return by_events(run), last
         timer.clear()
         for _ in range(calls):
             run()
@@ -171,6 +207,9 @@ def ab_shape(torch, timer, m, n, k, inputs="hash", rounds=2, variant=None, busy_
             else:
                 # a cuBLASLt call may be more than one kernel: its GPU time is the sum of its kernels' medians
                 busy(lambda: lt.run(best))
+                if timer is None:
+                    lib.append(by_events(lambda: lt.run(best)))
+                    continue
                 timer.clear()
                 for _ in range(calls):
                     lt.run(best)
@@ -181,7 +220,7 @@ def ab_shape(torch, timer, m, n, k, inputs="hash", rounds=2, variant=None, busy_
     plan.status()
     sampler.timed = False
     clocks = sampler.stop()
-    err = float((c_lib - c_ours).abs().max().item())
+    err = max_abs_diff(torch, c_lib, c_ours)
     steady = None
     if series > 0:
         # the reference's other timing (backend/node/clusterlaunch.py:54-96, ab.py AB_SERIES / AB_PDL): mean of `series`
@@ -211,6 +250,7 @@ def ab_shape(torch, timer, m, n, k, inputs="hash", rounds=2, variant=None, busy_
            "cublaslt_correct_algos": "%d of %d" % (correct, lt.n_algos), "cublaslt_version": lt.version,
            "cublaslt_kernels": lib_kernels, "ours_tflops": flops / mid(ours) / 1e6, "cublaslt_tflops": flops / mid(lib) / 1e6,
            "ours_vs_cublaslt_pct": 100.0 * (min(lib) / mid(ours) - 1.0), "max_abs_diff_vs_cublaslt": err,
+           "timer": "CUPTI kernel start-to-end" if timer is not None else "CUDA events around each call",
            "published_warpc_us": PUBLISHED.get((m, n, k), (None, None))[0], "published_cublas138_us": PUBLISHED.get((m, n, k), (None, None))[1]}
     row["clocks"] = clocks  # over both sides' isolated calls: SM MHz (median), power (max), throttle reasons seen
     if steady is not None:
@@ -220,18 +260,127 @@ def ab_shape(torch, timer, m, n, k, inputs="hash", rounds=2, variant=None, busy_
     return row
 
 
+class Nvml:
+    """SM clock, limiting reasons and the energy counter of one GPU (read-only); every method gives None without NVML."""
+
+    def __init__(self, index):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv, self.h = pynvml, pynvml.nvmlDeviceGetHandleByIndex(index)
+        except Exception:
+            self.nv = self.h = None
+
+    def energy_mj(self):
+        try:
+            return self.nv.nvmlDeviceGetTotalEnergyConsumption(self.h)
+        except Exception:
+            return None
+
+    def clock(self):
+        try:
+            try:
+                why = self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+            except Exception:
+                why = self.nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+            return self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM), why
+        except Exception:
+            return None
+
+
+def turn_time(torch, run, repeat, warm=0, blocker=None):
+    """One side's turn of the event-rounds method: (optional) blocker and warming launches queued and not waited for,
+    then `repeat` launches between two events; mean microseconds a launch."""
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if blocker is not None:
+        blocker()
+    for _ in range(warm):
+        run()
+    e0.record()
+    for _ in range(repeat):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    return 1e3 * e0.elapsed_time(e1) / repeat
+
+
+def event_rounds(torch, m, n, k, rounds, repeat, inputs="hash", gap=0.0, block=False, warm_ms=0.0, each=False, pdl=False, out=sys.stdout):
+    """The reference harness's event-timed rounds (backend/node/ab.py:121-175) for this library's kernel and cuBLASLt
+    (its fastest correct algorithm) on one shape.  Returns a dict with each side's per-round microseconds."""
+    import statistics
+    import time
+    a, bt = make_inputs(torch, inputs, m, n, k)
+    c_ours = torch.zeros((m, n), dtype=torch.float32, device="cuda")
+    c_lib = torch.zeros((m, n), dtype=torch.float32, device="cuda")
+    v = programs.choose(m, n, k)
+    plan = Plan(v, m, n, k, a.data_ptr(), bt.data_ptr(), c_ours.data_ptr())
+    plan.launch()
+    plan.status()
+    lt = CublasLt(m, n, k, a.data_ptr(), bt.data_ptr(), c_lib.data_ptr())
+    best = fastest_correct_algo(torch, lt, c_lib, c_ours, 0.0 if inputs == "hash" else 1e-3 * (k ** 0.5), m * n * k)[0]
+    if pdl:
+        plan.set_dependent_launch(True)
+    sides = [("ours", plan.launch), ("cublaslt", lambda: lt.run(best))]
+    blocker = None
+    if block:
+        # a long kernel of this library on buffers of its own: about a millisecond for the host to queue behind
+        bm = 8192
+        ba = torch.zeros((bm, bm), dtype=torch.float16, device="cuda")
+        bc = torch.zeros((bm, bm), dtype=torch.float32, device="cuda")
+        bplan = Plan(programs.choose(bm, bm, bm), bm, bm, bm, ba.data_ptr(), ba.data_ptr(), bc.data_ptr())
+        blocker = bplan.launch
+    nvml = Nvml(torch.cuda.current_device())
+    once = {name: turn_time(torch, run, 3) for name, run in sides}
+    res = {name: [] for name, _ in sides}
+    for r in range(rounds):
+        for name, run in (sides if r % 2 == 0 else sides[::-1]):
+            if gap:
+                time.sleep(gap)
+            warm = max(1, int(1e3 * warm_ms / once[name])) if warm_ms else 0
+            e0 = nvml.energy_mj() if each else None
+            res[name].append(turn_time(torch, run, repeat, warm=warm, blocker=blocker))
+            if each:
+                e1, c = nvml.energy_mj(), nvml.clock()
+                print("round %d %-9s %.2f us%s%s" % (r, name, res[name][-1], "" if c is None else "  clock %d MHz, reasons 0x%x" % c,
+                      "" if e0 is None or e1 is None else "  energy %.1f mJ a call (the turn's blocker and warming launches included)" % ((e1 - e0) / (repeat + warm))),
+                      file=out, flush=True)
+    plan.status()
+    for name, _ in sides:
+        x = res[name]
+        print("%-10s %dx%dx%d  median %.2f us  min %.2f  max %.2f  (%d x %d)" % (name, m, n, k, statistics.median(x), min(x), max(x), rounds, repeat), file=out)
+    plan.close()
+    lt.close()
+    if block:
+        bplan.close()
+    return {"shape": [m, n, k], "rounds": rounds, "repeat": repeat, "gap_s": gap, "blocked": bool(block), "warm_ms": warm_ms, "pdl": bool(pdl),
+            "ours_us": res["ours"], "cublaslt_us": res["cublaslt"]}
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--inputs", default="hash", choices=["hash", "uniform"])
     ap.add_argument("--json", default=None)
     ap.add_argument("--rounds", type=int, default=2)
     ap.add_argument("--series", type=int, default=0, help="also time this many launches back to back between events (ours, ours with dependent launch, cuBLASLt)")
+    ap.add_argument("--event-rounds", type=int, default=0, help="the reference harness's event-timed rounds instead of isolated calls")
+    ap.add_argument("--repeat", type=int, default=30, help="launches back to back per turn of an event round")
+    ap.add_argument("--gap", type=float, default=0.0, help="seconds idle before each turn (event rounds)")
+    ap.add_argument("--block", action="store_true", help="queue each turn behind a long kernel (event rounds)")
+    ap.add_argument("--warm", type=float, default=0.0, help="milliseconds of the side's own kernel right before its timed launches (event rounds)")
+    ap.add_argument("--each", action="store_true", help="print every turn with SM clock, limiting reasons and energy per call (event rounds)")
+    ap.add_argument("--pdl", action="store_true", help="dependent launches for this library's side (event rounds)")
     ap.add_argument("dims", nargs="*", type=int)
     args = ap.parse_args(argv)
     import torch
     if not torch.cuda.is_available():
         raise SystemExit("ab: needs a CUDA device")
-    shapes = [tuple(args.dims[i:i + 3]) for i in range(0, len(args.dims), 3)] or [s for s in SHAPES if s != (16384, 16384, 16384)]
+    shapes = [tuple(args.dims[i:i + 3]) for i in range(0, len(args.dims), 3)] or list(SHAPES)
+    if args.event_rounds:
+        rows = [event_rounds(torch, m, n, k, args.event_rounds, args.repeat, inputs=args.inputs, gap=args.gap, block=args.block, warm_ms=args.warm,
+                             each=args.each, pdl=args.pdl) for (m, n, k) in shapes]
+        if args.json:
+            json.dump({"method": "event-timed rounds, order alternating, %d launches back to back a turn" % args.repeat, "rows": rows}, open(args.json, "w"), indent=1)
+        return 0
     timer = KernelTimer()
     rows = []
     print("%-18s %-12s %-28s %17s %17s %8s   %s" % ("M x N x K", "rule's program", "runs as", "ours us", "cuBLASLt us", "vs lib", "published warpc / cuBLAS 13.8 us"))

@@ -111,6 +111,7 @@ struct Plan {
   KParams p;
   uint32_t* d_flags = nullptr;
   uint32_t* d_status = nullptr;
+  float* d_ws = nullptr;
   unsigned long long* d_stamps = nullptr;
   size_t flag_bytes = 0;
   // host plans own these
@@ -171,6 +172,10 @@ void launch_config(const wg_launch_info& li, cudaStream_t stream, bool dependent
   cfg->numAttrs = dependent ? 2 : 1;
 }
 
+// The attribute is per kernel function, not per launch, and plans with rings of different depth share a function: it is
+// always raised to the most a CTA may have, so a plan made later never lowers it under a plan made earlier.
+constexpr int kMaxDynSmem = 232448;
+
 // Split-K and stream-K CTAs wait for each other's flags, so every cluster of the grid has to be
 // resident at once.  The rule's tables assume a whole B200 (148 SMs, 74 resident pairs); a device
 // or context that offers fewer is refused here rather than found out by a wait that runs out.
@@ -179,6 +184,7 @@ int check_coresident(const wb_kernel_entry* k, const wg_launch_info& li) {
   cudaLaunchConfig_t cfg;
   cudaLaunchAttribute attr[2];
   launch_config(li, nullptr, false, &cfg, attr);
+  WG_CUDA(cudaFuncSetAttribute(k->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem));
   int clusters = 0;
   WG_CUDA(cudaOccupancyMaxActiveClusters(&clusters, k->fn, &cfg));
   return li.grid / li.cluster <= clusters ? WG_OK : WG_E_VARIANT;
@@ -204,6 +210,7 @@ int fill_plan(Plan* pl, int device, const wg_variant* v, int M, int N, int K, co
   pl->flag_bytes = size_t(li.nflags > 0 ? li.nflags : 1) * sizeof(uint32_t);
   WG_CUDA(cudaMalloc(&pl->d_flags, pl->flag_bytes));
   WG_CUDA(cudaMalloc(&pl->d_status, 8 * sizeof(uint32_t)));
+  if (li.ws_words > 0) WG_CUDA(cudaMalloc(&pl->d_ws, size_t(li.ws_words) * sizeof(float)));  // every word is written before it is read
   WG_CUDA(cudaMemsetAsync(pl->d_flags, 0, pl->flag_bytes, 0));
   WG_CUDA(cudaMemsetAsync(pl->d_status, 0, 8 * sizeof(uint32_t), 0));
   WG_CUDA(cudaStreamSynchronize(0));  // the words are zero before any stream, blocking or not, can launch on the plan
@@ -229,9 +236,10 @@ int fill_plan(Plan* pl, int device, const wg_variant* v, int M, int N, int K, co
   }
   p.C = static_cast<float*>(dC);
   p.flags = pl->d_flags;
+  p.ws = pl->d_ws;
   p.status = pl->d_status;
   p.timeout_ns = 2000ull * 1000ull * 1000ull;
-  WG_CUDA(cudaFuncSetAttribute(pl->k->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, li.dynsmem));
+  WG_CUDA(cudaFuncSetAttribute(pl->k->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem));
   return check_coresident(pl->k, li);
 }
 
@@ -438,6 +446,7 @@ extern "C" int wg_plan_destroy(void* plan) {
   DeviceGuard guard(pl->device);
   if (pl->d_flags) cudaFree(pl->d_flags);
   if (pl->d_status) cudaFree(pl->d_status);
+  if (pl->d_ws) cudaFree(pl->d_ws);
   if (pl->d_stamps) cudaFree(pl->d_stamps);
   for (Plan* b : pl->blocks) wg_plan_destroy(b);
   for (auto* list : {&pl->ev_a, &pl->ev_b, &pl->ev_mm})
@@ -586,7 +595,7 @@ extern "C" int wg_launch_noalloc(int device, const wg_variant* v, int M, int N, 
   wg_launch_info li;
   int r = wg_realise(v, M, N, K, &li);
   if (r != WG_OK) return r;
-  if (li.nflags > kNoAllocMaxFlags) return WG_E_LIMIT;  // the shape needs more hand-off words than the array holds
+  if (li.nflags > kNoAllocMaxFlags || li.ws_words > 0) return WG_E_LIMIT;  // more hand-off words than the array holds, or a workspace
   uint32_t* scratch = nullptr;
   if ((r = noalloc_setup(device, &scratch)) != WG_OK) return r;
   WG_ON_DEVICE(device);
@@ -621,7 +630,7 @@ extern "C" int wg_launch_noalloc(int device, const wg_variant* v, int M, int N, 
   // the array keeps the last call's contents and the flags of one launch must all start equal:
   // clear the words this launch uses (and the status) on the stream, ahead of the kernel
   WG_CUDA(cudaMemsetAsync(scratch, 0, size_t(8 + (li.nflags > 0 ? li.nflags : 0)) * sizeof(uint32_t), stream));
-  WG_CUDA(cudaFuncSetAttribute(k->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, li.dynsmem));
+  WG_CUDA(cudaFuncSetAttribute(k->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem));
   if ((r = check_coresident(k, li)) != WG_OK) return r;
   cudaLaunchConfig_t cfg;
   cudaLaunchAttribute attr[2];

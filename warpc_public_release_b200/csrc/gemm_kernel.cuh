@@ -59,6 +59,7 @@ struct KParams {
   int epi_ring;                 // the ring holds a whole C tile: a CTA's last tile is staged there, one copy per block
   float* C;                     // direct store
   uint32_t* flags;              // split-K / stream-K hand-off words
+  float* ws;                    // split-K / stream-K through a workspace: a slot of TM x TN partial sums per CTA
   uint32_t* status;             // 8 words: [0] code, [1] site detail, [2] CTA, [3] parity/stage
   unsigned long long timeout_ns;
 #ifdef WB_TIMING_EXPERIMENTS
@@ -413,6 +414,63 @@ WB_DEV void epi_direct_tile(const KParams& p, uint32_t tbase, int row, int col, 
   }
 }
 
+// ------------------------------------------------------------------ K shared through a workspace
+// The reference's other way of sharing a tile's K between CTAs (backend/gemm_swapped.ml:716-832): a CTA leaves its
+// partial accumulator in its slot of a workspace in global memory, in the order its threads hold it (the "fragment
+// order" of backend/store.ml:106-114: block, register, lane, so every store and every load is a whole 128-byte
+// line), and one CTA per 32-row block adds the partial sums up in a fixed order and stores C.  Unlike sums added in
+// the L2, the order of the additions does not depend on timing: every launch gives the same bits.
+
+// word offset of register 0 of block i, epilogue warp quarter q, in a CTA's slot; register j is 32 words further on
+template <class C>
+WB_DEV size_t ws_offset(int i, int q, uint32_t lane) { return size_t(i * 4 + q) * (C::EPI_ROWS * 32) + lane; }
+
+// This warp's blocks of the accumulator into the CTA's slot; with S > 1 the blocks run s will sum up itself stay behind.
+template <class C>
+WB_DEV void epi_ws_put(float* slot, uint32_t tbase, int q, uint32_t lane, int S, int s) {
+  uint32_t v[C::EPI_ROWS];
+#pragma unroll 1
+  for (int i = 0; i < C::NBLK; ++i) {
+    if (S > 1 && i * S / C::NBLK == s) continue;
+    epi_load<C>(tbase, i, v);
+    tmem_wait_ld();
+    float* dst = slot + ws_offset<C>(i, q, lane);
+#pragma unroll
+    for (int j = 0; j < C::EPI_ROWS; ++j) dst[j * 32] = __uint_as_float(v[j]);
+  }
+}
+
+// The blocks this CTA sums up (all of them when S == 1; with S > 1 block i belongs to run i S / NBLK): its own part
+// from tensor memory plus the slots src0 + j * src_stride, j = 0 .. nsrc - 1 except `skip`, added in that order, then
+// stored to C from the registers.  Releases the accumulator.
+template <class C>
+WB_DEV void epi_ws_sum(const KParams& p, uint32_t tbase, int row, int col, int q, uint32_t lane, uint32_t acc_empty_addr,
+                       const float* src0, size_t src_stride, int nsrc, int skip, int S, int s) {
+  uint32_t v[C::EPI_ROWS];
+  const size_t ld = size_t(p.N);
+#pragma unroll 1
+  for (int i = 0; i < C::NBLK; ++i) {
+    if (S > 1 && i * S / C::NBLK != s) continue;
+    epi_load<C>(tbase, i, v);
+    tmem_wait_ld();
+    for (int j = 0; j < nsrc; ++j) {
+      if (j == skip) continue;
+      const float* src = src0 + size_t(j) * src_stride + ws_offset<C>(i, q, lane);  // written by another SM: read in the L2
+#pragma unroll
+      for (int r = 0; r < C::EPI_ROWS; ++r) v[r] = __float_as_uint(__fadd_rn(__uint_as_float(v[r]), __ldcg(src + r * 32)));
+    }
+    int y, x;
+    epi_coords<C>(row, col, q, i, y, x);
+    float* dst = p.C + size_t(y) * ld + size_t(x) + lane;
+#pragma unroll
+    for (int r = 0; r < C::EPI_ROWS; ++r) dst[size_t(r) * ld] = __uint_as_float(v[r]);
+  }
+  tc_fence_before();
+  __syncwarp();
+  if constexpr (C::CG == 2) mbar_arrive_cluster_if(lane == 0 ? 1u : 0u, acc_empty_addr);
+  else mbar_arrive_if(lane == 0 ? 1u : 0u, acc_empty_addr);
+}
+
 template <class C>
 __global__ void __launch_bounds__(256, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -654,7 +712,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     // never reset: every CTA's own word holds how many launches have gone by, so one past it
     // is the value all flags of this launch reach (gemm_swapped.ml:608-626)
     const bool shared_k = !C::DIRECT && (p.sched == SCHED_SPLITK || p.sched == SCHED_STREAMK);
+    // the same sharing through a workspace (store from the registers): split-K counts launches in the CTA's word like
+    // the L2 form; stream-K raises the word to 1 and the CTA that takes the partial sum puts it back to 0
+    const bool ws_k = C::DIRECT && (p.sched == SCHED_SPLITK || p.sched == SCHED_STREAMK);
+    float* ws_slot = ws_k ? p.ws + size_t(blockIdx.x) * size_t(C::TM * C::TN) : nullptr;
     uint32_t target = 0;
+    if (ws_k && p.sched == SCHED_SPLITK) target = ld_relaxed_gpu(p.flags + blockIdx.x) + 1u;
     if (shared_k) {
       target = ld_relaxed_gpu(p.flags + blockIdx.x) + 1u;
       if (p.sched == SCHED_STREAMK) {
@@ -668,10 +731,60 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       const uint32_t tbase = tmem_base + uint32_t(acc * C::NCOLS) + (uint32_t(q * 32) << 16);
       const uint32_t acc_empty_addr = acc_empty_leader + 8u * uint32_t(acc);
       if constexpr (C::DIRECT) {
-        if (!wait_bar(p, abort_addr, acc_full_bar(acc), acc_phase, ST_WAIT_ACC_FULL, uint32_t(acc))) break;
-        tc_fence_after();
-        if (first_warp && lane == 0) stamp(p, EV_ACC_READY, nth);
-        epi_direct_tile<C>(p, tbase, row, col, q, lane, acc_empty_addr);
+        if (ws_k && p.sched == SCHED_SPLITK) {
+          // ---- split-K through the workspace (gemm_swapped.ml:737-791): every run leaves the blocks it does not sum up
+          // itself in its slot and raises its flag; once the tile's other runs' flags are up it adds their parts of its
+          // own blocks, in run order, and stores them.  No warp leaves this block early: all four meet at the barriers.
+          const int S = p.split, c = int(blockIdx.x) / CG, s = c % S, base = (c / S) * S;
+          ok = wait_bar(p, abort_addr, acc_full_bar(acc), acc_phase, ST_WAIT_ACC_FULL, uint32_t(acc));
+          tc_fence_after();
+          if (first_warp && lane == 0) stamp(p, EV_ACC_READY, nth);
+          if (ok) epi_ws_put<C>(ws_slot, tbase, q, lane, S, s);
+          __threadfence();  // every store of the partial is visible GPU-wide before the flag
+          named_bar_sync(2, 128);
+          if (ok && first_warp && lane == 0) st_relaxed_gpu(p.flags + blockIdx.x, target);
+          if (first_warp) {
+            for (int j = int(lane); ok && j < S; j += 32)
+              if (j != s) ok = wait_flag(p, abort_addr, p.flags + (base + j) * CG + int(rank), target, uint32_t(j));
+          }
+          fence_acq_rel_gpu();
+          named_bar_sync(2, 128);
+          ok = ok && (ld_shared_u32(abort_addr) == 0u);
+          if (ok) epi_ws_sum<C>(p, tbase, row, col, q, lane, acc_empty_addr, p.ws + size_t(base * CG + int(rank)) * size_t(C::TM * C::TN),
+                                size_t(CG) * size_t(C::TM * C::TN), S, s, S, s);
+        } else if (ws_k && w.ke < p.kt) {
+          // ---- stream-K through the workspace (gemm_swapped.ml:793-832): a segment that ends before its tile does leaves
+          // its partial in this CTA's slot and raises this CTA's word
+          ok = wait_bar(p, abort_addr, acc_full_bar(acc), acc_phase, ST_WAIT_ACC_FULL, uint32_t(acc));
+          tc_fence_after();
+          if (ok) {
+            epi_ws_put<C>(ws_slot, tbase, q, lane, 1, 0);
+            tc_fence_before();
+            __syncwarp();
+            if constexpr (CG == 2) mbar_arrive_cluster_if(lane == 0 ? 1u : 0u, acc_empty_addr);
+            else mbar_arrive_if(lane == 0 ? 1u : 0u, acc_empty_addr);
+          }
+          __threadfence();
+          named_bar_sync(2, 128);
+          if (ok && first_warp && lane == 0) st_relaxed_gpu(p.flags + blockIdx.x, 1u);
+        } else if (ws_k && w.kb != 0) {
+          // ... and the segment that starts after its tile does (the next cluster's: every cluster holds a tile's worth of
+          // k-steps at least, so a tile has two parts at most) waits for that word, puts it back, and adds the slot
+          uint32_t* before = p.flags + blockIdx.x - CG;
+          if (first_warp) ok = wait_flag(p, abort_addr, before, 1u, uint32_t(w.tile));
+          fence_acq_rel_gpu();
+          named_bar_sync(2, 128);
+          ok = ok && (ld_shared_u32(abort_addr) == 0u);
+          if (ok && first_warp && lane == 0) st_relaxed_gpu(before, 0u);
+          ok = ok && wait_bar(p, abort_addr, acc_full_bar(acc), acc_phase, ST_WAIT_ACC_FULL, uint32_t(acc));
+          tc_fence_after();
+          if (ok) epi_ws_sum<C>(p, tbase, row, col, q, lane, acc_empty_addr, ws_slot - size_t(CG) * size_t(C::TM * C::TN), 0, 1, -1, 1, 0);
+        } else {
+          if (!wait_bar(p, abort_addr, acc_full_bar(acc), acc_phase, ST_WAIT_ACC_FULL, uint32_t(acc))) break;
+          tc_fence_after();
+          if (first_warp && lane == 0) stamp(p, EV_ACC_READY, nth);
+          epi_direct_tile<C>(p, tbase, row, col, q, lane, acc_empty_addr);
+        }
       } else if (!shared_k) {
         if (!wait_bar(p, abort_addr, acc_full_bar(acc), acc_phase, ST_WAIT_ACC_FULL, uint32_t(acc))) break;
         tc_fence_after();

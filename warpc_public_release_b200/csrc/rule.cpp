@@ -262,10 +262,14 @@ extern "C" int wg_realise(const wg_variant* v, int M, int N, int K, wg_launch_in
     li.cl_n = tiles_n / 2;
     li.group = effective_group(8, tiles_m, li.cl_n);
   } else {
-    // K shared between CTAs (split in the cluster, split over the grid, stream-K) always adds in the L2 here, the
-    // reference's workspace variants included (backend/gemm_swapped.ml:716-832: partial sums in a workspace, FADD by
-    // the last run): same sums, no workspace; so none of them stores from the registers
-    li.cg = 2, li.tile_m = v->tile_m, li.tile_n = v->tile_n, li.direct = v->direct && v->split == 1 && v->split_grid <= 1 && !v->streamk;
+    // K shared between CTAs (split in the cluster, split over the grid, stream-K).  A variant named explicitly runs in the
+    // form it names: partial sums through a workspace, added up in a fixed order by the CTA that stores the block
+    // (backend/gemm_swapped.ml:716-832; store from the registers), or added in the L2 (split_add).  Split inside a cluster
+    // (`split`) is the same split over the grid, two pairs a tile, through the workspace.  The rule's own choices
+    // (retile) always add in the L2: same sums, no workspace, and measured faster.
+    const bool shares_k = v->streamk || v->split_grid > 1 || v->split > 1;
+    const bool via_ws = shares_k && v->direct && !v->split_add && !v->retile;
+    li.cg = 2, li.tile_m = v->tile_m, li.tile_n = v->tile_n, li.direct = v->direct && (!shares_k || via_ws);
     li.cluster = 2;
     li.nbuf = v->nbuf;
     int group = v->group, clc = v->clc, streamk = v->streamk;
@@ -353,6 +357,7 @@ extern "C" int wg_realise(const wg_variant* v, int M, int N, int K, wg_launch_in
   li.mbarriers = 2 * li.rounds + 4 + 3;  // full + empty a round, two accumulators' full + empty, scheduler's three
   // a CTA's last tile is staged whole in the ring when the ring can hold it
   li.wide_rows = (!li.direct && size_t(li.depth) * size_t(e->stage_bytes) >= size_t(li.tile_m) * size_t(li.tile_n) * 4) ? e->wide_rows : 0;
+  li.ws_words = (li.direct && (li.sched == 3 || li.sched == 4)) ? li.grid * li.tile_m * li.tile_n : 0;
   (void)K;
   return WG_OK;
 }
@@ -398,11 +403,12 @@ extern "C" int wg_header(const wg_variant* v, int M, int N, int K, char* buf, si
   append(s, ".tmap a %d %d 2 %d 64 128", M, K, li.a_box_rows);
   append(s, ".tmap bt %d %d 2 %d 64 128", N, K, li.bt_box_rows);
   if (li.nflags > 0) append(s, ".ptr flags 1 %d 4", li.nflags);
+  if (li.ws_words > 0) append(s, ".ptr ws %d %d 4", li.grid, li.tile_m * li.tile_n);
   append(s, ".grid %d 1", li.grid);
   append(s, ".mbarriers %d", li.mbarriers);
   append(s, ".cluster %d", li.cluster);
   append(s, ".tcgen05");
-  append(s, li.nflags > 0 ? ".params 8 8 8 8" : ".params 8 8 8");
+  append(s, li.ws_words > 0 ? ".params 8 8 8 8 8" : li.nflags > 0 ? ".params 8 8 8 8" : ".params 8 8 8");
   if (s.size() + 1 > cap) return WG_E_ARG;
   std::memcpy(buf, s.c_str(), s.size() + 1);
   return int(s.size());

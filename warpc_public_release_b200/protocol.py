@@ -84,6 +84,7 @@ class Model:
         self.slots = {}           # (cta, slot) -> None | ("loading"|"full", tile, kstep, bytes_left)
         self.acc = {}             # (cluster, buffer) -> dict(state, tile, ks, readers, complete)
         self.flags = defaultdict(int)
+        self.ws = {}              # (CTA, epilogue warp) -> tile whose partial sums that warp has left in the CTA's workspace slot
         self.nbar = defaultdict(set)  # (CTA, use) -> epilogue warps that have reached the named barrier
         self.tile_log = defaultdict(list)  # tile -> [(kind, frozenset(ksteps))]
         self.clc_next = min(self.clusters, RESIDENT_CLUSTERS)  # first cluster not resident at launch
@@ -212,6 +213,7 @@ class Model:
         leader, rank = c * cg, cta % cg
         acc, acc_use, nth = 0, 0, 0
         shared_k = (not li.direct) and li.sched in (SCHED_SPLITK, SCHED_STREAMK)
+        ws_k = bool(li.direct) and li.sched in (SCHED_SPLITK, SCHED_STREAMK)   # the same sharing through a workspace
         # hand-off words count launches; every epilogue thread reads its CTA's word before any of them
         # moves on (a named barrier in the kernel), so in this first launch they all mean 1
         target = 1 if shared_k else 0
@@ -223,7 +225,39 @@ class Model:
                 continue
             _, tile, kb, ke, last = item
             wide = last and li.wide_rows != 0  # the tile is staged in the ring, which has to be drained by then
-            if not shared_k:
+            if ws_k and li.sched == SCHED_SPLITK:
+                # every run leaves its partial in its slot, raises its flag, waits for the tile's other runs' flags, then
+                # sums and stores its own share of the tile's blocks (tensor memory is read again: released last)
+                S, s = li.split, c % li.split
+                base = (c // S) * S
+                yield ("wait", (cta, "acc_full", acc), acc_use)
+                yield ("peek", c, acc, tile, "partial", warp, cta)
+                yield ("nbar", cta, 2 * nth, warp)
+                if warp == 0:
+                    yield ("flag", ("cta", cta), 1)
+                    for j in range(S):
+                        if j != s and not self.mut.get("ws_no_flag_wait"):
+                            yield ("flagwait", ("cta", (base + j) * cg + rank), 1)
+                yield ("nbar", cta, 2 * nth + 1, warp)
+                yield ("wsread", tile, [(base + j) * cg + rank for j in range(S) if j != s], warp, cta)
+                yield ("share", tile, s, S, warp, cta)
+                yield ("read", c, acc, leader, tile, "sum", warp, cta, False)
+            elif ws_k and ke < self.kt:
+                yield ("wait", (cta, "acc_full", acc), acc_use)
+                yield ("read", c, acc, leader, tile, "partial", warp, cta, False)
+                yield ("nbar", cta, 2 * nth, warp)
+                if warp == 0:
+                    yield ("flag", ("cta", cta), 1)
+            elif ws_k and kb != 0:
+                if warp == 0 and not self.mut.get("ws_no_flag_wait"):
+                    yield ("flagwait", ("cta", cta - cg), 1)
+                yield ("nbar", cta, 2 * nth, warp)
+                if warp == 0:
+                    yield ("flag", ("cta", cta - cg), 0)
+                yield ("wsread", tile, [cta - cg], warp, cta)
+                yield ("wait", (cta, "acc_full", acc), acc_use)
+                yield ("read", c, acc, leader, tile, "sum", warp, cta, False)
+            elif not shared_k:
                 yield ("wait", (cta, "acc_full", acc), acc_use)
                 yield ("read", c, acc, leader, tile, "store", warp, cta, wide)
             elif li.sched == SCHED_SPLITK:
@@ -341,15 +375,29 @@ class Model:
                     cta, warp, acc, tile, a["state"], a["tile"], a["complete"]))
             if warp == 0:
                 self.tile_log[tile].append((how, frozenset(a["ks"])))
+            if how == "partial":
+                self.ws[cta, warp] = tile
             a["readers"] += 1
             if a["readers"] == 4 * self.cg:
                 a["state"] = "read"
             self.bars[leader, "acc_empty", acc].arrive(0)
-        elif kind == "zero":
+        elif kind in ("zero", "share"):
             _, tile, s, S, warp, cta = ev
             if warp == 0:
                 nblk = self.blocks_per_warp()
-                self.tile_log[tile].append(("zero", frozenset(i for i in range(nblk) if i * S // nblk == s)))
+                self.tile_log[tile].append((kind, frozenset(i for i in range(nblk) if i * S // nblk == s)))
+        elif kind == "wsread":
+            _, tile, others, warp, cta = ev
+            for x in others:
+                if self.ws.get((x, warp)) != tile - tile % self.cg + x % self.cg:
+                    raise Violation("CTA %d warp %d adds CTA %d's partial sums for tile %d, but that slot holds %r" % (cta, warp, x, tile, self.ws.get((x, warp))))
+        elif kind == "peek":   # tensor memory read without giving the accumulator up (its owner reads it again later)
+            _, c, acc, tile, how, warp, cta = ev
+            self.ws[cta, warp] = tile
+            a = self.acc[c, acc]
+            if a["state"] != "live" or not a["complete"] or a["tile"] != tile - tile % self.cg:
+                raise Violation("CTA %d warp %d reads accumulator %d for tile %d, which is %s (tile %r, MMAs complete: %s)" % (
+                    cta, warp, acc, tile, a["state"], a["tile"], a["complete"]))
         return True
 
     def blocks_per_warp(self):
@@ -425,13 +473,21 @@ class Model:
                 raise Violation("CTA %d leaves with slot %d still holding %r" % (cta, slot, have))
         for tile in range(self.tiles):
             log = self.tile_log.get(tile, [])
-            pieces = [ks for how, ks in log if how in ("store", "add")]
+            pieces = [ks for how, ks in log if how in ("store", "add", "partial", "sum")]
             seen = sorted(k for ks in pieces for k in ks)
             if seen != list(range(self.kt)):
                 raise Violation("tile %d: k-steps accumulated %s, wanted each of 0..%d once" % (tile, _ranges(seen), self.kt - 1))
             stores = [how for how, _ in log if how == "store"]
             zeros = sorted(i for how, ks in log if how == "zero" for i in ks)
-            if self.li.sched == SCHED_SPLITK and not self.li.direct:
+            if self.li.direct and self.li.sched == SCHED_SPLITK:
+                nblk, shares = self.blocks_per_warp(), sorted(i for how, ks in log if how == "share" for i in ks)
+                if stores or shares != list(range(nblk)):
+                    raise Violation("tile %d: the runs summed and stored blocks %s (wanted each of %d once) and stored it whole %d times" % (tile, shares, nblk, len(stores)))
+            elif self.li.direct and self.li.sched == SCHED_STREAMK:
+                kinds = [how for how, _ in log]
+                if kinds not in (["store"], ["partial", "sum"]):
+                    raise Violation("tile %d through the workspace: %s (wanted one store, or a partial left and then summed)" % (tile, kinds))
+            elif self.li.sched == SCHED_SPLITK and not self.li.direct:
                 nblk = self.blocks_per_warp()
                 if stores or zeros != list(range(nblk)):
                     raise Violation("tile %d: split-K zeroed blocks %s (wanted each of %d once) and stored %d times" % (tile, zeros, nblk, len(stores)))

@@ -49,17 +49,28 @@ def gather_slabs(c_full, c_local):
 class ShardedGemm:
     """One rank's share of C = A . Bt^T.  `a_local` (M/g x K fp16), `bt` (N x K fp16) are this
     rank's CUDA tensors; `c_full` (M x N fp32) is allocated on every rank only when
-    `replicate_c` (the slab then lives inside it, so the all-gather is in place)."""
+    `replicate_c` (the slab then lives inside it, so the gather is in place).
 
-    def __init__(self, m, n, k, rank, world, a_local, bt, replicate_c=False, device=None, pin_large=True):
+    With `replicate_c` the slab is computed in `bands` row bands, one launch each on two
+    alternating streams (a band's last, partly filled wave of tiles runs beside the next band's
+    first), and each band is sent to every other rank as soon as its launch is done: one group
+    of NCCL sends and receives per band, straight into place (a band of every rank's slab is a
+    block of whole rows of C, so it is contiguous), on NCCL's own stream -- the transfers of band
+    b run under the tensor cores' work on band b + 1.  Only programs whose CTAs never wait for one
+    another (one tile a CTA, fixed grid, launch control) are overlapped this way: NCCL's kernels
+    take SMs, and split-K / stream-K grids need every CTA resident at once."""
+
+    def __init__(self, m, n, k, rank, world, a_local, bt, replicate_c=False, device=None, pin_large=True, bands=4):
         import torch
         from .plan import Plan
+        from .programs import realise
         self.m, self.n, self.k, self.rank, self.world = m, n, k, rank, world
         self.lo, self.hi = slab_rows(m, world, rank)
         rows = self.hi - self.lo
         if tuple(a_local.shape) != (rows, k) or tuple(bt.shape) != (n, k):
             raise ValueError("A slab must be %d x %d and Bt %d x %d" % (rows, k, n, k))
         device = a_local.device if device is None else device
+        self.device = device
         self.replicate_c = replicate_c
         if replicate_c:
             self.c_full = torch.empty((m, n), dtype=torch.float32, device=device)
@@ -68,13 +79,132 @@ class ShardedGemm:
             self.c_full = None
             self.c_local = torch.empty((rows, n), dtype=torch.float32, device=device)
         self.variant = slab_variant(rows, n, k, pin_large)
-        self.plan = Plan(self.variant, rows, n, k, a_local.data_ptr(), bt.data_ptr(), self.c_local.data_ptr(),
-                         device=device.index or 0)
+        dev_index = device.index or 0
+        self.plan = Plan(self.variant, rows, n, k, a_local.data_ptr(), bt.data_ptr(), self.c_local.data_ptr(), device=dev_index)
         self._keep = (a_local, bt)
+        self.band_plans, self._pending = [], []
+        if replicate_c and world > 1 and device.type == "cuda":
+            self.band_rows = band_rows(rows, bands, self.variant.tile_m)
+            for (b0, b1) in self.band_rows:
+                v = slab_variant(b1 - b0, n, k, pin_large)
+                if realise(v, b1 - b0, n, k).sched in (3, 4):
+                    self.band_plans = []   # CTAs that wait for one another: no NCCL kernel beside them, one launch then one gather
+                    break
+                self.band_plans.append(Plan(v, b1 - b0, n, k, a_local[b0:b1].data_ptr(), bt.data_ptr(), self.c_local[b0:b1].data_ptr(), device=dev_index))
+            if self.band_plans:
+                self._streams = [torch.cuda.Stream(device=device), torch.cuda.Stream(device=device)]
 
     def launch(self):
-        """This rank's GEMM (asynchronous, default stream); with `replicate_c`, followed by the all-gather."""
-        self.plan.launch()
-        if self.replicate_c and self.world > 1:
+        """This rank's GEMM (asynchronous).  Without `replicate_c`: one launch on the default stream.  With it: the
+        bands' launches and their gathers are queued; call wait() before reading `c_full`."""
+        import torch
+        if not (self.replicate_c and self.world > 1):
+            self.plan.launch()
+            return self.c_local
+        if not self.band_plans:
+            self.plan.launch()
             gather_slabs(self.c_full, self.c_local)
-        return self.c_full if self.replicate_c else self.c_local
+            return self.c_full
+        import torch.distributed as dist
+        rows = self.hi - self.lo
+        start = torch.cuda.current_stream(self.device)
+        for i, ((b0, b1), plan) in enumerate(zip(self.band_rows, self.band_plans)):
+            s = self._streams[i % 2]
+            if i < 2:
+                s.wait_stream(start)   # what the caller queued before (the inputs) comes first
+            with torch.cuda.stream(s):
+                plan.launch(stream=s.cuda_stream)
+                ops = []
+                for q in range(self.world):
+                    if q == self.rank:
+                        continue
+                    ops.append(dist.P2POp(dist.isend, self.c_local[b0:b1], q))
+                    ops.append(dist.P2POp(dist.irecv, self.c_full[q * rows + b0:q * rows + b1], q))
+                self._pending += dist.batch_isend_irecv(ops)   # NCCL's stream waits for this band's launch, not for the next
+        return self.c_full
+
+    def wait(self):
+        """Make the current stream wait for everything launch() queued (band launches and gathers)."""
+        import torch
+        if self.band_plans:
+            cur = torch.cuda.current_stream(self.device)
+            for work in self._pending:
+                work.wait()
+            self._pending = []
+            for s in self._streams:
+                cur.wait_stream(s)
+
+    def status(self):
+        self.plan.status()
+        for p in self.band_plans:
+            p.status()
+
+
+class ShardedHostGemm:
+    """The sharded product from HOST buffers, one rank's part: `run(hA, hBt_shard, hC)` takes this rank's rows of A
+    (M/g x K), this rank's rows of Bt (N/g x K) and gives this rank's rows of C (M/g x N), all in pinned host memory.
+    Every operand crosses PCIe once in the whole job: each rank uploads only its own rows of Bt, and the shards are
+    gathered into every GPU's copy of Bt by one in-place NCCL all-gather over NVLink (plain NCCL on each GPU's own
+    buffer).  A's rows go in and C's rows come out in row bands on streams of their own, a band's launch waiting only
+    for that band of A (and for Bt), so the copies in, the tensor cores and the copies out overlap."""
+
+    def __init__(self, m, n, k, rank, world, device, bands=None, pin_large=True):
+        import torch
+        from .plan import Plan
+        self.m, self.n, self.k, self.rank, self.world, self.device = m, n, k, rank, world, device
+        self.lo, self.hi = slab_rows(m, world, rank)
+        self.blo, self.bhi = slab_rows(n, world, rank)
+        rows = self.hi - self.lo
+        self.a = torch.empty((rows, k), dtype=torch.float16, device=device)
+        self.bt = torch.empty((n, k), dtype=torch.float16, device=device)
+        self.c = torch.empty((rows, n), dtype=torch.float32, device=device)
+        bands = bands or max(1, min(4, rows // 1024))
+        self.bands = band_rows(rows, bands, 256)
+        self.plans = [Plan(slab_variant(b1 - b0, n, k, pin_large), b1 - b0, n, k, self.a[b0:b1].data_ptr(), self.bt.data_ptr(),
+                           self.c[b0:b1].data_ptr(), device=device.index or 0) for (b0, b1) in self.bands]
+        self.s_in, self.s_mm, self.s_out = (torch.cuda.Stream(device=device) for _ in range(3))
+        self.ev_bt = torch.cuda.Event()
+        self.ev_a = [torch.cuda.Event() for _ in self.bands]
+        self.ev_mm = [torch.cuda.Event() for _ in self.bands]
+        self.h2d_bytes = rows * k * 2 + (self.bhi - self.blo) * k * 2
+        self.d2h_bytes = rows * n * 4
+
+    def run(self, hA, hBt_shard, hC):
+        """hA (M/g x K fp16), hBt_shard (N/g x K fp16), hC (M/g x N fp32): pinned CPU tensors.  Returns when hC is complete."""
+        import torch
+        import torch.distributed as dist
+        with torch.cuda.stream(self.s_in):
+            self.bt[self.blo:self.bhi].copy_(hBt_shard, non_blocking=True)
+            self.ev_bt.record()
+            for (b0, b1), ev in zip(self.bands, self.ev_a):
+                self.a[b0:b1].copy_(hA[b0:b1], non_blocking=True)
+                ev.record()
+        with torch.cuda.stream(self.s_mm):
+            self.s_mm.wait_event(self.ev_bt)
+            if self.world > 1:
+                dist.all_gather_into_tensor(self.bt, self.bt[self.blo:self.bhi])   # in place: every rank's shard to every GPU
+            for plan, ev_a, ev_mm in zip(self.plans, self.ev_a, self.ev_mm):
+                self.s_mm.wait_event(ev_a)
+                plan.launch(stream=self.s_mm.cuda_stream)
+                ev_mm.record()
+        with torch.cuda.stream(self.s_out):
+            for (b0, b1), ev in zip(self.bands, self.ev_mm):
+                self.s_out.wait_event(ev)
+                hC[b0:b1].copy_(self.c[b0:b1], non_blocking=True)
+        self.s_out.synchronize()
+
+    def status(self):
+        for p in self.plans:
+            p.status()
+
+    def close(self):
+        for p in self.plans:
+            p.close()
+
+
+def band_rows(rows, bands, tile_m):
+    """`rows` cut into at most `bands` contiguous bands of whole tile rows, as equal as whole tiles allow."""
+    tiles = max(1, rows // tile_m)
+    bands = max(1, min(bands, tiles))
+    cuts = [(i * tiles // bands) * tile_m for i in range(bands)] + [rows]
+    return [(cuts[i], cuts[i + 1]) for i in range(bands) if cuts[i + 1] > cuts[i]]
