@@ -206,7 +206,6 @@ int fill_plan(Plan* pl, int device, const wg_variant* v, int M, int N, int K, co
   if ((r = encode_2d(&pl->map_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, dBt, N, K, li.bt_box_rows, 64)) != WG_OK) return r;
   if (!li.direct && (r = encode_2d(&pl->map_c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dC, M, N, li.c_box_rows, 32, CU_TENSOR_MAP_SWIZZLE_NONE, ldc)) != WG_OK) return r;
   if (!li.direct && (r = encode_2d(&pl->map_cw, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dC, M, N, pl->k->wide_rows, 32, CU_TENSOR_MAP_SWIZZLE_NONE, ldc)) != WG_OK) return r;
-  if (li.direct && ldc > 0 && ldc != N) return WG_E_VARIANT;  // the store from the registers takes C's rows N apart
   pl->flag_bytes = size_t(li.nflags > 0 ? li.nflags : 1) * sizeof(uint32_t);
   WG_CUDA(cudaMalloc(&pl->d_flags, pl->flag_bytes));
   WG_CUDA(cudaMalloc(&pl->d_status, 8 * sizeof(uint32_t)));
@@ -217,6 +216,7 @@ int fill_plan(Plan* pl, int device, const wg_variant* v, int M, int N, int K, co
   KParams& p = pl->p;
   std::memset(&p, 0, sizeof p);
   p.M = M, p.N = N, p.K = K;
+  p.ldc = ldc > 0 ? ldc : N;
   p.kt = K / 64;
   const int tiles_m = (M + li.tile_m - 1) / li.tile_m, tiles_n = (N + li.tile_n - 1) / li.tile_n;
   p.ntiles = tiles_m * tiles_n;
@@ -609,7 +609,7 @@ extern "C" int wg_launch_noalloc(int device, const wg_variant* v, int M, int N, 
   if (!li.direct && (r = encode_2d(&map_cw, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dC, M, N, k->wide_rows, 32, CU_TENSOR_MAP_SWIZZLE_NONE)) != WG_OK) return r;
   KParams p;
   std::memset(&p, 0, sizeof p);
-  p.M = M, p.N = N, p.K = K, p.kt = K / 64;
+  p.M = M, p.N = N, p.K = K, p.ldc = N, p.kt = K / 64;
   p.ntiles = ((M + li.tile_m - 1) / li.tile_m) * ((N + li.tile_n - 1) / li.tile_n);
   p.cl_n = li.cl_n > 0 ? li.cl_n : 1, p.group = li.group > 0 ? li.group : 1, p.serp = li.serpentine;
   p.depth = li.depth, p.nbuf = li.nbuf, p.sched = li.sched, p.ask_ahead = li.ask_ahead, p.split = li.split;

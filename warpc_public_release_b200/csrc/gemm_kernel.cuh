@@ -41,6 +41,7 @@ enum : uint32_t {
 
 struct KParams {
   int M, N, K;
+  int ldc;        // fp32 words between rows of C (N, or more when C is a block of a wider matrix): the store from the registers
   int kt;         // K / 64 k-steps
   int ntiles;     // CTA tiles in all
   int cl_n;       // clusters (CG CTAs side by side) across the output
@@ -406,9 +407,9 @@ WB_DEV void epi_direct_tile(const KParams& p, uint32_t tbase, int row, int col, 
     }
     int y, x;
     epi_coords<C>(row, col, q, i, y, x);
-    float* dst = p.C + size_t(y) * size_t(p.N) + size_t(x) + lane;
+    float* dst = p.C + size_t(y) * size_t(p.ldc) + size_t(x) + lane;
     // whole tiles only (the host refuses the store from the registers otherwise): no bounds to test
-    const size_t ld = size_t(p.N);
+    const size_t ld = size_t(p.ldc);
 #pragma unroll
     for (int j = 0; j < C::EPI_ROWS; ++j) dst[size_t(j) * ld] = __uint_as_float(v[i & 1][j]);
   }
@@ -447,7 +448,7 @@ template <class C>
 WB_DEV void epi_ws_sum(const KParams& p, uint32_t tbase, int row, int col, int q, uint32_t lane, uint32_t acc_empty_addr,
                        const float* src0, size_t src_stride, int nsrc, int skip, int S, int s) {
   uint32_t v[C::EPI_ROWS];
-  const size_t ld = size_t(p.N);
+  const size_t ld = size_t(p.ldc);
 #pragma unroll 1
   for (int i = 0; i < C::NBLK; ++i) {
     if (S > 1 && i * S / C::NBLK != s) continue;

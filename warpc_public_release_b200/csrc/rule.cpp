@@ -276,8 +276,7 @@ extern "C" int wg_realise(const wg_variant* v, int M, int N, int K, wg_launch_in
     const bool plain = !v->streamk && v->split_grid <= 1 && v->split <= 1;
     if (v->retile && plain) {
       // Measured on a B200 (no TMA multicast): one tcgen05.mma costs 55-90 cycles to issue whatever
-      // its N, so MMAs narrower than N = 256 (tile_m < 256) cannot keep the tensor pipe full; the
-      // store through staging copies and TMA beats the store from the registers at every size; and
+      // its N, so MMAs narrower than N = 256 (tile_m < 256) cannot keep the tensor pipe full; and
       // a fixed grid walking tiles by stride beats cluster launch control until tiles are 256 x 256.
       li.direct = 0;
       const int pair_tiles_256 = (M % 256 == 0 && N % 256 == 0) ? (M / 256) * (N / 256) : 0;
@@ -292,6 +291,14 @@ extern "C" int wg_realise(const wg_variant* v, int M, int N, int K, wg_launch_in
         const int clusters = kSms / 2, waves = (pair_tiles_256 + clusters - 1) / clusters;
         if (10 * pair_tiles_256 < 9 * waves * clusters) streamk = 1, li.nbuf = 2;
       }
+      // The store: where a CTA's tiles are whole and K is not shared, 128-column tiles go out from the registers
+      // (isolated calls, both input families: 2048^3 18.9 against 20.4 us, 3072x1280x2048 18.8 / 20.4, 4096x4096x1024
+      // 34.3 / 37.8, 1536^3 12.7 / 13.8).  A one-tile launch ends on its store either way, and a TMA store's source is
+      // only read ~1 us after it is issued, which the CTA has to wait out before it may leave; on the fixed-grid walk
+      // the register stores of tile t run beside tile t+1's loads without taking the copy engine from them, and the
+      // ring gets the staging copies' room (one more stage).  The 64-column fold tile (1024^3) measures the same both
+      // ways and the 256 x 256 tile's exposed 256 KB store is faster through the copy engine: both stay staged.
+      if (!streamk && !clc && li.tile_n == 128 && M % li.tile_m == 0 && N % li.tile_n == 0) li.direct = 1;
     }
     const int tiles_m = (M + li.tile_m - 1) / li.tile_m, tiles_n = (N + li.tile_n - 1) / li.tile_n;
     const int total = tiles_m * tiles_n;
