@@ -107,6 +107,25 @@ int wg_last_device_status(void* plan, unsigned out[4]);
 int wg_plan_reset(void* plan);
 int wg_plan_destroy(void* plan);
 
+/* A replicated C, fused into the GEMM (no counterpart in the reference, which runs on one GPU): `n` further copies of
+ * this plan's C -- device pointers this process can write, typically other GPUs' memory opened through CUDA IPC with
+ * peer access enabled, each M x N fp32 row-major with the same row pitch as dC.  Every launch that follows stores each
+ * block of C to all of them as well, from the same staged copy, tile by tile (TMA stores over NVLink), so the transfer
+ * overlaps the tensor cores' work; the copies are complete when the launch is.  Only for programs that store through
+ * staging copies and do not share K between CTAs (one tile a CTA, fixed grid, launch control); WG_E_VARIANT otherwise.
+ * n = 0 turns it off.  No TMA load ever touches these pointers. */
+int wg_plan_set_replicas(void* plan, int n, void* const* peer_dC);
+
+/* Sharing a device buffer between the processes of one box (one process per GPU), for wg_plan_set_replicas: the owner
+ * exports a pointer (anywhere inside an allocation) as 64 opaque bytes plus its offset inside the allocation; another
+ * process imports it WITH ITS OWN DEVICE CURRENT (`device`), which maps the owner's memory into that device's address
+ * space with peer access, and gets a pointer it may hand to wg_plan_set_replicas.  (CUDA IPC; an import of an allocation
+ * this process has already imported returns the same mapping, counted.)  wg_ipc_release undoes one import.
+ * Returns a cudaError_t / CUresult on failure, WG_E_ARG for a pointer that was not imported. */
+int wg_ipc_export(int device, const void* dptr, unsigned char handle[64], unsigned long long* offset);
+int wg_ipc_import(int device, const unsigned char handle[64], unsigned long long offset, void** dptr);
+int wg_ipc_release(int device, void* dptr);
+
 /* Host-buffer entry: a plan that owns device copies of A, Bt and C.  wg_host_run copies
  * hA, hBt in, launches, copies C out to hC and synchronises -- the call the reference's
  * harness makes around a launch (backend/node/run_tma.py:68-70, 142).  A large problem (>= 256 MB moved, M and N

@@ -18,16 +18,31 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
-    for (m, n, k) in ((1024, 1024, 512), (4096, 2048, 1024)):
+    # shapes whose slab program stores through staging copies (the copy to the other GPUs can be fused into the kernel) and
+    # one whose program stores from the registers (falls back to NCCL); both ways of replicating asked for explicitly
+    import warpc_public_release_b200 as w
+    clc = lambda r, n, k: w.swapped(r, n, k, 256, 256, 4, clc=True, serpentine=True, ask_ahead=True)   # the large shape's program
+    stride = lambda r, n, k: w.swapped(r, n, k, 128, 128, 8, bufs=2)                                    # a fixed grid, two accumulators
+    cases = [((1024, 1024, 512), "fused", None, "fused"),          # the rule's program for the slab: staged, one tile a CTA
+             ((4096, 4096, 1024), "fused", clc, "fused"), ((8192, 2304, 256), "fused", stride, "fused"),
+             ((8192, 4096, 1024), "fused", None, "nccl"),          # the rule's program stores from the registers: NCCL in row bands
+             ((8192, 4096, 1024), "nccl", clc, "nccl"),
+             ((4096, 4096, 4096), "fused", None, "nccl")]          # the rule's program shares K between CTAs (stream-K): one launch, one all-gather
+    for (m, n, k), how, build, runs in cases:
         a, bt = gemm_ref.inputs_integers(m, n, k)
         lo, hi = shard.slab_rows(m, world, rank)
-        job = shard.ShardedGemm(m, n, k, rank, world, torch.from_numpy(a[lo:hi]).to(dev), torch.from_numpy(bt).to(dev), replicate_c=True, device=dev)
+        job = shard.ShardedGemm(m, n, k, rank, world, torch.from_numpy(a[lo:hi]).to(dev), torch.from_numpy(bt).to(dev), replicate_c=True, device=dev,
+                                how=how, variant=build(hi - lo, n, k) if build else None)
+        assert job.how == runs, (m, n, k, how, job.how)
         for _ in range(3):
             c = job.launch()
-        job.plan.status()
-        job.wait()
+            job.wait()
+        job.status()
         torch.cuda.synchronize()
-        assert np.array_equal(c.cpu().numpy(), gemm_ref.gemm_ref(a, bt)), "rank %d: gathered C differs at %dx%dx%d" % (rank, m, n, k)
+        assert np.array_equal(c.cpu().numpy(), gemm_ref.gemm_ref(a, bt)), "rank %d: gathered C differs at %dx%dx%d (%s)" % (rank, m, n, k, job.how)
+        print("rank %d %dx%dx%d asked %s ran %s" % (rank, m, n, k, how, job.how), flush=True)
+        del job
+        dist.barrier()
     dist.barrier()
     print("replicated C ok (rank %d)" % rank, flush=True)
     dist.destroy_process_group()

@@ -69,6 +69,10 @@ def lib():
         "wg_time_launches": ([vp, i, i, ctypes.POINTER(ctypes.c_float)], i),
         "wg_plan_enable_stamps": ([vp, i], i),
         "wg_plan_set_dependent_launch": ([vp, i], i),
+        "wg_plan_set_replicas": ([vp, i, ctypes.POINTER(vp)], i),
+        "wg_ipc_export": ([i, vp, ctypes.c_char_p, ctypes.POINTER(ctypes.c_ulonglong)], i),
+        "wg_ipc_import": ([i, ctypes.c_char_p, ctypes.c_ulonglong, ctypes.POINTER(vp)], i),
+        "wg_ipc_release": ([i, vp], i),
         "wg_plan_read_stamps": ([vp, ctypes.POINTER(ctypes.c_ulonglong), ctypes.c_size_t], i),
         "wg_plan_debug_set_flag": ([vp, i, u], i),
         "wg_plan_debug_set_mode": ([vp, u], i),

@@ -112,6 +112,8 @@ struct Plan {
   uint32_t* d_flags = nullptr;
   uint32_t* d_status = nullptr;
   float* d_ws = nullptr;
+  CUtensorMap* d_replicas = nullptr;
+  int ldc = 0;
   unsigned long long* d_stamps = nullptr;
   size_t flag_bytes = 0;
   // host plans own these
@@ -216,6 +218,7 @@ int fill_plan(Plan* pl, int device, const wg_variant* v, int M, int N, int K, co
   KParams& p = pl->p;
   std::memset(&p, 0, sizeof p);
   p.M = M, p.N = N, p.K = K;
+  pl->ldc = ldc;
   p.ldc = ldc > 0 ? ldc : N;
   p.kt = K / 64;
   const int tiles_m = (M + li.tile_m - 1) / li.tile_m, tiles_n = (N + li.tile_n - 1) / li.tile_n;
@@ -411,6 +414,102 @@ extern "C" int wg_launch(void* plan, void* cuda_stream) {
   return int(cudaLaunchKernelExC(&cfg, pl->k->fn, args));
 }
 
+extern "C" int wg_plan_set_replicas(void* plan, int n, void* const* peer_dC) {
+  Plan* pl = static_cast<Plan*>(plan);
+  if (!pl || n < 0 || n > 15 || (n > 0 && !peer_dC)) return WG_E_ARG;
+  WG_ON_DEVICE(pl->device);
+  WG_CUDA(cudaDeviceSynchronize());  // no launch in flight reads the maps about to be replaced
+  if (pl->d_replicas) cudaFree(pl->d_replicas);
+  pl->d_replicas = nullptr, pl->p.replicas = nullptr, pl->p.nrep = 0;
+  if (n == 0) return WG_OK;
+  const wg_launch_info& li = pl->li;
+  if (li.direct || li.sched == SCHED_SPLITK || li.sched == SCHED_STREAMK) return WG_E_VARIANT;
+  std::vector<CUtensorMap> maps(size_t(2 * n));
+  for (int r = 0; r < n; ++r) {
+    if (!peer_dC[r] || (reinterpret_cast<uintptr_t>(peer_dC[r]) & 15u)) return WG_E_ARG;
+    int e = encode_2d(&maps[size_t(2 * r)], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, peer_dC[r], pl->M, pl->N, li.c_box_rows, 32, CU_TENSOR_MAP_SWIZZLE_NONE, pl->ldc);
+    if (e == WG_OK)
+      e = encode_2d(&maps[size_t(2 * r + 1)], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, peer_dC[r], pl->M, pl->N, pl->k->wide_rows, 32, CU_TENSOR_MAP_SWIZZLE_NONE, pl->ldc);
+    if (e != WG_OK) return e;
+  }
+  WG_CUDA(cudaMalloc(&pl->d_replicas, maps.size() * sizeof(CUtensorMap)));
+  WG_CUDA(cudaMemcpy(pl->d_replicas, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice));
+  pl->p.replicas = pl->d_replicas, pl->p.nrep = n;
+  return WG_OK;
+}
+
+// ------------------------------------------------------------------ buffers shared between processes (CUDA IPC)
+namespace {
+struct Imported {
+  unsigned char handle[64];
+  int device;
+  void* base;
+  int refs;
+};
+std::vector<Imported> g_imported;
+std::mutex g_imported_mutex;
+typedef CUresult (*AddressRangeFn)(CUdeviceptr*, size_t*, CUdeviceptr);
+}  // namespace
+
+extern "C" int wg_ipc_export(int device, const void* dptr, unsigned char handle[64], unsigned long long* offset) {
+  if (!dptr || !handle || !offset) return WG_E_ARG;
+  WG_ON_DEVICE(device);
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &fn, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) return WG_E_NODRIVER;
+  CUdeviceptr base = 0;
+  size_t size = 0;
+  const CUresult r = reinterpret_cast<AddressRangeFn>(fn)(&base, &size, reinterpret_cast<CUdeviceptr>(dptr));
+  if (r != CUDA_SUCCESS) return int(r);
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle travels as 64 bytes");
+  cudaIpcMemHandle_t h;
+  WG_CUDA(cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(base)));
+  std::memcpy(handle, &h, 64);
+  *offset = reinterpret_cast<CUdeviceptr>(dptr) - base;
+  return WG_OK;
+}
+
+extern "C" int wg_ipc_import(int device, const unsigned char handle[64], unsigned long long offset, void** dptr) {
+  if (!handle || !dptr) return WG_E_ARG;
+  *dptr = nullptr;
+  WG_ON_DEVICE(device);  // the importing GPU is current: the mapping (and its peer access) is made for this device
+  std::lock_guard<std::mutex> lock(g_imported_mutex);
+  for (Imported& im : g_imported)
+    if (im.device == device && std::memcmp(im.handle, handle, 64) == 0) {
+      im.refs += 1;
+      *dptr = static_cast<char*>(im.base) + offset;
+      return WG_OK;
+    }
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle, 64);
+  void* base = nullptr;
+  WG_CUDA(cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess));
+  Imported im;
+  std::memcpy(im.handle, handle, 64);
+  im.device = device, im.base = base, im.refs = 1;
+  g_imported.push_back(im);
+  *dptr = static_cast<char*>(base) + offset;
+  return WG_OK;
+}
+
+extern "C" int wg_ipc_release(int device, void* dptr) {
+  if (!dptr) return WG_E_ARG;
+  WG_ON_DEVICE(device);
+  std::lock_guard<std::mutex> lock(g_imported_mutex);
+  // the mapping whose base is the closest at or below the pointer
+  int best = -1;
+  for (size_t i = 0; i < g_imported.size(); ++i)
+    if (g_imported[i].device == device && g_imported[i].base <= dptr &&
+        (best < 0 || g_imported[i].base > g_imported[size_t(best)].base)) best = int(i);
+  if (best < 0) return WG_E_ARG;
+  if (--g_imported[size_t(best)].refs == 0) {
+    const cudaError_t e = cudaIpcCloseMemHandle(g_imported[size_t(best)].base);
+    g_imported.erase(g_imported.begin() + best);
+    if (e != cudaSuccess) return int(e);
+  }
+  return WG_OK;
+}
+
 extern "C" int wg_plan_set_dependent_launch(void* plan, int on) {
   Plan* pl = static_cast<Plan*>(plan);
   if (!pl) return WG_E_ARG;
@@ -447,6 +546,7 @@ extern "C" int wg_plan_destroy(void* plan) {
   if (pl->d_flags) cudaFree(pl->d_flags);
   if (pl->d_status) cudaFree(pl->d_status);
   if (pl->d_ws) cudaFree(pl->d_ws);
+  if (pl->d_replicas) cudaFree(pl->d_replicas);
   if (pl->d_stamps) cudaFree(pl->d_stamps);
   for (Plan* b : pl->blocks) wg_plan_destroy(b);
   for (auto* list : {&pl->ev_a, &pl->ev_b, &pl->ev_mm})

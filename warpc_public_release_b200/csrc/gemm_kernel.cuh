@@ -61,6 +61,8 @@ struct KParams {
   float* C;                     // direct store
   uint32_t* flags;              // split-K / stream-K hand-off words
   float* ws;                    // split-K / stream-K through a workspace: a slot of TM x TN partial sums per CTA
+  const CUtensorMap* replicas;  // further copies of C (other GPUs' memory): per copy the block map and the wide map, in global memory
+  int nrep;                     // how many; every staged block is stored to each of them as well
   uint32_t* status;             // 8 words: [0] code, [1] site detail, [2] CTA, [3] parity/stage
   unsigned long long timeout_ns;
 #ifdef WB_TIMING_EXPERIMENTS
@@ -337,7 +339,8 @@ WB_DEV void epi_coords(int row, int col, int q, int i, int& y, int& x) {
 // has retired) can hold it, every block gets a copy of its own there and no store is waited for.
 template <class C>
 WB_DEV void epi_staged_tile(const CUtensorMap* map_c, const CUtensorMap* map_cw, uint32_t tbase, uint32_t my_staging, int row, int col, int q, uint32_t lane,
-                            bool add, uint32_t acc_empty_addr, uint64_t policy, uint32_t wide = 0, unsigned long long* prof = nullptr) {
+                            bool add, uint32_t acc_empty_addr, uint64_t policy, uint32_t wide = 0, unsigned long long* prof = nullptr,
+                            const CUtensorMap* replicas = nullptr, int nrep = 0) {
   uint32_t v[2][C::EPI_ROWS];
   long long t_ld = 0, t_copy = 0, t_sts = 0, t_tma = 0, t_issue = 0, t0 = 0;
   if (prof) t0 = clock64();
@@ -376,10 +379,16 @@ WB_DEV void epi_staged_tile(const CUtensorMap* map_c, const CUtensorMap* map_cw,
     fence_proxy_async_smem();
     __syncwarp();
     if (prof) t_sts += clock64() - t0, t0 = clock64();
+    // a replicated C: the same staged box goes to every other copy too (peer GPUs over NVLink), inside the same bulk
+    // group, so the tile's transfer runs under the next tiles' MMAs and the copy is free again when all have read it
     if (wide == 0u) {
+      for (int r = 0; r < nrep; ++r) tma_store_if(lane == 0 ? 1u : 0u, replicas + 2 * r, x, y, copy, policy);
       tma_store_commit_if(lane == 0 ? 1u : 0u, add ? 1u : 0u, map_c, x, y, copy, policy);
     } else if ((i + 1) % C::WIDE_BLKS == 0) {
       // the last WIDE_BLKS blocks are WIDE_ROWS consecutive rows of C and of the ring: one store
+      for (int r = 0; r < nrep; ++r)
+        tma_store_if(lane == 0 ? 1u : 0u, replicas + 2 * r + 1, x, y - (C::WIDE_BLKS - 1) * C::EPI_ROWS,
+                     copy - uint32_t(C::WIDE_BLKS - 1) * C::EPI_COPY_BYTES, policy);
       tma_store_commit_if(lane == 0 ? 1u : 0u, add ? 1u : 0u, map_cw, x, y - (C::WIDE_BLKS - 1) * C::EPI_ROWS,
                           copy - uint32_t(C::WIDE_BLKS - 1) * C::EPI_COPY_BYTES, policy);
     }
@@ -792,7 +801,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         if (first_warp && lane == 0) stamp(p, EV_ACC_READY, nth);
         // timing runs: the first warp's cycles in each part of the tile's store, events 11-14
         unsigned long long* prof = (p.stamps != nullptr && first_warp && nth < 4) ? p.stamps + (size_t(blockIdx.x) * 64 + 11) * 4 + nth : nullptr;
-        epi_staged_tile<C>(&map_c, &map_cw, tbase, my_staging, row, col, q, lane, false, acc_empty_addr, store_policy, wide, prof);
+        epi_staged_tile<C>(&map_c, &map_cw, tbase, my_staging, row, col, q, lane, false, acc_empty_addr, store_policy, wide, prof, p.replicas, p.nrep);
       } else if (p.sched == SCHED_SPLITK) {
         // ---- split-K over the grid, adding in the L2 (gemm_swapped.ml:660-710).  The S runs
         // of a tile first zero disjoint shares of it (while their k loops run), raise their

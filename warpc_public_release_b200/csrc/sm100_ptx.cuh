@@ -353,6 +353,15 @@ WB_DEV void tma_store_commit_if(uint32_t issuer, uint32_t add, const void* map, 
       "r"(add), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(src), "l"(policy)
       : "memory");
 }
+// the same store without closing the bulk group (further stores of the same box follow, then one commit)
+WB_DEV void tma_store_if(uint32_t issuer, const void* map, int x, int y, uint32_t src, uint64_t policy) {
+  asm volatile(
+      "{\n\t.reg .pred e;\n\t"
+      "setp.ne.u32 e, %0, 0;\n\t"
+      "@e cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%1, {%2, %3}], [%4], %5;\n\t}" ::"r"(issuer),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(src), "l"(policy)
+      : "memory");
+}
 WB_DEV uint64_t l2_policy_evict_first() {
   uint64_t p;
   asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));

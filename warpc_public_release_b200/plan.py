@@ -48,6 +48,12 @@ class _Base:
         or writes global memory."""
         check(_lib.lib().wg_plan_set_dependent_launch(self._h, int(bool(on))), "wg_plan_set_dependent_launch")
 
+    def set_replicas(self, pointers):
+        """Further copies of C (integer device addresses this process can write, e.g. other GPUs' memory opened through
+        CUDA IPC): every launch that follows stores each block of C to all of them too, tile by tile."""
+        arr = (ctypes.c_void_p * max(1, len(pointers)))(*[ctypes.c_void_p(x) for x in pointers])
+        check(_lib.lib().wg_plan_set_replicas(self._h, len(pointers), arr), "wg_plan_set_replicas")
+
     def enable_stamps(self, on=True):
         check(_lib.lib().wg_plan_enable_stamps(self._h, int(bool(on))), "wg_plan_enable_stamps")
 
@@ -116,6 +122,24 @@ class HostPlan(_Base):
 
     def buffer(self, which):
         return _lib.lib().wg_host_plan_buffer(self._h, which)
+
+
+def ipc_export(dptr, device=0):
+    """(handle bytes, offset) naming a device buffer of this process for another process of the same box (wg_ipc_export)."""
+    handle, offset = ctypes.create_string_buffer(64), ctypes.c_ulonglong()
+    check(_lib.lib().wg_ipc_export(device, ctypes.c_void_p(dptr), handle, ctypes.byref(offset)), "wg_ipc_export")
+    return handle.raw, offset.value
+
+
+def ipc_import(handle, offset, device=0):
+    """Another process's buffer mapped for `device` of this process (peer access over NVLink); returns its address here."""
+    out = ctypes.c_void_p()
+    check(_lib.lib().wg_ipc_import(device, handle, offset, ctypes.byref(out)), "wg_ipc_import")
+    return out.value
+
+
+def ipc_release(dptr, device=0):
+    check(_lib.lib().wg_ipc_release(device, ctypes.c_void_p(dptr)), "wg_ipc_release")
 
 
 def launch_noalloc(variant, m, n, k, dA, dBt, dC, device=0, stream=None):

@@ -51,16 +51,18 @@ class ShardedGemm:
     rank's CUDA tensors; `c_full` (M x N fp32) is allocated on every rank only when
     `replicate_c` (the slab then lives inside it, so the gather is in place).
 
-    With `replicate_c` the slab is computed in `bands` row bands, one launch each on two
-    alternating streams (a band's last, partly filled wave of tiles runs beside the next band's
-    first), and each band is sent to every other rank as soon as its launch is done: one group
-    of NCCL sends and receives per band, straight into place (a band of every rank's slab is a
-    block of whole rows of C, so it is contiguous), on NCCL's own stream -- the transfers of band
-    b run under the tensor cores' work on band b + 1.  Only programs whose CTAs never wait for one
-    another (one tile a CTA, fixed grid, launch control) are overlapped this way: NCCL's kernels
-    take SMs, and split-K / stream-K grids need every CTA resident at once."""
+    With `replicate_c` the copy to the other GPUs is part of the GEMM itself (`how` = "fused", the default where it can
+    be set up): every rank opens the other ranks' C through CUDA IPC, and the kernel stores each staged block of its
+    slab to every GPU's copy, tile by tile, with TMA stores over NVLink -- no collective kernel runs and no SM is
+    taken from the tensor cores' work; wait() is then a one-word all-reduce that tells every rank the others' launches
+    are done.  Where that cannot be set up (`how` = "nccl": no peer access, a program that stores from the registers
+    or shares K between CTAs) the slab is computed in `bands` row bands, one launch each on two alternating streams,
+    and each band is sent to every other rank as soon as its launch is done: one group of NCCL sends and receives per
+    band, straight into place (a band of every rank's slab is whole rows of C, so it is contiguous), on NCCL's own
+    stream.  Programs whose CTAs wait for one another (split-K, stream-K) are not overlapped with NCCL's kernels,
+    which take SMs: one launch, then one all-gather."""
 
-    def __init__(self, m, n, k, rank, world, a_local, bt, replicate_c=False, device=None, pin_large=True, bands=4):
+    def __init__(self, m, n, k, rank, world, a_local, bt, replicate_c=False, device=None, pin_large=True, bands=4, how=None, variant=None):
         import torch
         from .plan import Plan
         from .programs import realise
@@ -78,29 +80,91 @@ class ShardedGemm:
         else:
             self.c_full = None
             self.c_local = torch.empty((rows, n), dtype=torch.float32, device=device)
-        self.variant = slab_variant(rows, n, k, pin_large)
+        self.variant = variant if variant is not None else slab_variant(rows, n, k, pin_large)   # `variant`: a program named by the caller for the slab's shape
         dev_index = device.index or 0
         self.plan = Plan(self.variant, rows, n, k, a_local.data_ptr(), bt.data_ptr(), self.c_local.data_ptr(), device=dev_index)
         self._keep = (a_local, bt)
         self.band_plans, self._pending = [], []
+        self.how = None
         if replicate_c and world > 1 and device.type == "cuda":
-            self.band_rows = band_rows(rows, bands, self.variant.tile_m)
+            import os
+            want = how or os.environ.get("WARPC_REPLICATE", "fused")
+            self.how = "fused" if want == "fused" and self._open_peers() else "nccl"
+        if self.how == "nccl":
+            self.band_rows = band_rows(rows, bands, 256)
             for (b0, b1) in self.band_rows:
-                v = slab_variant(b1 - b0, n, k, pin_large)
-                if realise(v, b1 - b0, n, k).sched in (3, 4):
+                try:
+                    v = slab_variant(b1 - b0, n, k, pin_large)
+                    shares_k = realise(v, b1 - b0, n, k).sched in (3, 4)
+                except Exception:
+                    shares_k = True        # the rule has no program for a band of this height: the slab stays whole
+                if shares_k:
                     self.band_plans = []   # CTAs that wait for one another: no NCCL kernel beside them, one launch then one gather
                     break
                 self.band_plans.append(Plan(v, b1 - b0, n, k, a_local[b0:b1].data_ptr(), bt.data_ptr(), self.c_local[b0:b1].data_ptr(), device=dev_index))
             if self.band_plans:
                 self._streams = [torch.cuda.Stream(device=device), torch.cuda.Stream(device=device)]
 
+    def _open_peers(self):
+        """Every other rank's `c_full` mapped into this process for this rank's GPU (CUDA IPC, imported with this GPU
+        current so the mapping carries peer access), and this rank's rows of each given to the plan as further copies
+        of C.  False when any rank cannot (the ranks agree on the answer, so all take the same path)."""
+        import torch
+        import torch.distributed as dist
+        from . import plan as wplan
+        dev_index = self.device.index or 0
+        ok, mine, peers = True, None, []
+        try:
+            if realise_sched_direct(self.variant, self.hi - self.lo, self.n, self.k):
+                raise RuntimeError("the slab's program stores from the registers or shares K between CTAs")
+            mine = wplan.ipc_export(self.c_full.data_ptr(), device=dev_index)
+        except Exception:
+            ok = False
+        everyone = [None] * self.world
+        dist.all_gather_object(everyone, (dev_index, mine))
+        ok = ok and all(x[1] is not None for x in everyone)
+        if ok:
+            try:
+                for q, (their_device, (handle, offset)) in enumerate(everyone):
+                    if q == self.rank:
+                        continue
+                    if not torch.cuda.can_device_access_peer(dev_index, their_device):
+                        raise RuntimeError("no peer access from GPU %d to GPU %d" % (dev_index, their_device))
+                    peers.append(wplan.ipc_import(handle, offset, device=dev_index))
+            except Exception:
+                ok = False
+        flag = torch.tensor([1 if ok else 0], device=self.device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            for ptr in peers:
+                wplan.ipc_release(ptr, device=dev_index)
+            return False
+        self._peers = peers
+        slab_offset = self.lo * self.n * 4               # this rank's rows inside every copy of C
+        self.plan.set_replicas([ptr + slab_offset for ptr in peers])
+        self._token = torch.zeros(1, device=self.device)
+        return True
+
+    def close(self):
+        """Give the other ranks' buffers back (after every rank is done launching)."""
+        from . import plan as wplan
+        if getattr(self, "_peers", None):
+            self.plan.set_replicas([])
+            for ptr in self._peers:
+                wplan.ipc_release(ptr, device=self.device.index or 0)
+            self._peers = []
+
     def launch(self):
         """This rank's GEMM (asynchronous).  Without `replicate_c`: one launch on the default stream.  With it: the
-        bands' launches and their gathers are queued; call wait() before reading `c_full`."""
+        launch also fills the other ranks' copies (fused), or the bands' launches and their gathers are queued (nccl);
+        call wait() before reading `c_full`."""
         import torch
         if not (self.replicate_c and self.world > 1):
             self.plan.launch()
             return self.c_local
+        if self.how == "fused":
+            self.plan.launch()
+            return self.c_full
         if not self.band_plans:
             self.plan.launch()
             gather_slabs(self.c_full, self.c_local)
@@ -126,6 +190,10 @@ class ShardedGemm:
     def wait(self):
         """Make the current stream wait for everything launch() queued (band launches and gathers)."""
         import torch
+        if self.how == "fused":
+            import torch.distributed as dist
+            dist.all_reduce(self._token)   # stream-ordered behind this rank's launch; done when every rank's launch is
+            return
         if self.band_plans:
             cur = torch.cuda.current_stream(self.device)
             for work in self._pending:
@@ -200,6 +268,13 @@ class ShardedHostGemm:
     def close(self):
         for p in self.plans:
             p.close()
+
+
+def realise_sched_direct(variant, m, n, k):
+    """True when the program for this shape cannot take further copies of C (wg_plan_set_replicas refuses it)."""
+    from .programs import realise
+    li = realise(variant, m, n, k)
+    return bool(li.direct) or li.sched in (3, 4)
 
 
 def band_rows(rows, bands, tile_m):
