@@ -95,6 +95,11 @@ int wg_header(const wg_variant* v, int M, int N, int K, char* buf, size_t cap);
  * (0 = the default, 2000 ms). */
 int wg_plan_create(int device, const wg_variant* v, int M, int N, int K, const void* dA, const void* dBt, void* dC,
                    void** plan);
+/* The same for a product that is a COLUMN BLOCK of a wider C: dC points at the block's first entry and consecutive rows
+ * of C are `ldc` fp32 words apart (ldc >= N, a multiple of 4).  dBt is then the block's N rows of the wider B^T.  Used to
+ * run one problem as several launches side by side (no reference counterpart: its harness launches one kernel). */
+int wg_plan_create_block(int device, const wg_variant* v, int M, int N, int K, const void* dA, const void* dBt, void* dC, int ldc,
+                         void** plan);
 int wg_plan_set_timeout_ms(void* plan, unsigned ms);
 int wg_plan_info(void* plan, wg_launch_info* out);
 /* One launch on `cuda_stream` (a cudaStream_t, NULL = the default stream); asynchronous. */

@@ -247,22 +247,53 @@ def device_properties_exact(c, a, bt, row0=0):
 
 @pytest.mark.parametrize("gpus", [1, 2, 4, 8])
 def test_sharded_shape_and_its_slabs_full_size(big_hash_inputs, gpus):
-    """16384^3 (gpus = 1: the program the rule picks) and the slab one of 2 / 4 / 8 GPUs owns (the program
-    shard.slab_variant pins), two launches each, on rows [M/g, 2M/g) of A -- a slab that does not start at row 0."""
+    """16384^3 (gpus = 1: the program the rule picks) and the slab one of 2 / 4 / 8 GPUs owns, launched the way the
+    multi-GPU runner launches it (shard.ShardedGemm: the pinned large-shape program), two launches each, on rows
+    [M/g, 2M/g) of A -- a slab that does not start at row 0."""
     from warpc_public_release_b200 import shard
     a, bt = big_hash_inputs
     rank = 1 if gpus > 1 else 0
     lo, hi = shard.slab_rows(BIG, gpus, rank)
     rows = hi - lo
-    v = w.choose(BIG, BIG, BIG) if gpus == 1 else shard.slab_variant(rows, BIG, BIG)
-    c = torch.full((rows, BIG), float("nan"), dtype=torch.float32, device="cuda")
-    plan = w.Plan(v, rows, BIG, BIG, a[lo:hi].data_ptr(), bt.data_ptr(), c.data_ptr())
-    plan.set_timeout_ms(2000)
-    plan.launch()
-    plan.launch()
-    plan.status()
-    plan.close()
+    if gpus == 1:
+        c = torch.full((rows, BIG), float("nan"), dtype=torch.float32, device="cuda")
+        plan = w.Plan(w.choose(BIG, BIG, BIG), rows, BIG, BIG, a.data_ptr(), bt.data_ptr(), c.data_ptr())
+        plan.set_timeout_ms(2000)
+        plan.launch()
+        plan.launch()
+        plan.status()
+        plan.close()
+    else:
+        job = shard.ShardedGemm(BIG, BIG, BIG, rank, gpus, a[lo:hi], bt, device=a.device)
+        assert (job.variant.tile_m, job.variant.tile_n, job.variant.clc) == (256, 256, 1)
+        job.c_local.fill_(float("nan"))
+        job.launch()
+        job.launch()
+        torch.cuda.synchronize()
+        job.status()
+        c = job.c_local
     device_properties_exact(c, a[lo:hi], bt, row0=lo)
+
+
+def test_column_block_plans_side_by_side():
+    """One product as two launches on two streams, each a column block of the same C (wg_plan_create_block: rows ldc
+    apart), one through staging copies and TMA, one from the registers; bit-exact."""
+    m, n, k, n1 = 512, 1536, 512, 1024
+    a, bt = gemm_ref.inputs_integers(m, n, k)
+    da, db = torch.from_numpy(a).cuda(), torch.from_numpy(bt).cuda()
+    dc = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+    p1 = w.Plan(SW(m, n1, k, 256, 256, 4, clc=True, serpentine=True, ask_ahead=True), m, n1, k, da.data_ptr(), db.data_ptr(), dc.data_ptr(), ldc=n)
+    p2 = w.Plan(SW(m, n - n1, k, 256, 128, 7, clc=True, serpentine=True, direct=True, bufs=2), m, n - n1, k, da.data_ptr(), db[n1:].data_ptr(),
+                dc[:, n1:].data_ptr(), ldc=n)
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    for _ in range(3):
+        p1.launch(stream=s1.cuda_stream)
+        p2.launch(stream=s2.cuda_stream)
+    p1.status()
+    p2.status()
+    assert np.array_equal(dc.cpu().numpy(), gemm_ref.gemm_ref(a, bt))
+    p1.close()
+    p2.close()
 
 
 @pytest.mark.parametrize("shape", BENCH_SHAPES + [(BIG, BIG, BIG)], ids=lambda s: "x".join(map(str, s)))

@@ -62,3 +62,21 @@ def test_slab_rows_and_programs():
     assert (v.tile_m, v.tile_n) == (192, 128)
     v = shard.slab_variant(1024, 1024, 1024)
     assert (v.tile_m, v.tile_n) == (128, 64)
+
+
+def test_row_bands_and_which_slabs_can_take_fused_copies():
+    import warpc_public_release_b200 as w
+    from warpc_public_release_b200 import shard
+    # bands: whole 256-row tile rows, contiguous, covering the slab, as equal as whole tiles allow
+    assert shard.band_rows(8192, 4, 256) == [(0, 2048), (2048, 4096), (4096, 6144), (6144, 8192)]
+    assert shard.band_rows(512, 4, 256) == [(0, 256), (256, 512)]
+    assert shard.band_rows(2304, 4, 256) == [(0, 512), (512, 1024), (1024, 1536), (1536, 2304)]
+    for rows in (256, 1280, 2048, 4352):
+        bands = shard.band_rows(rows, 4, 256)
+        assert bands[0][0] == 0 and bands[-1][1] == rows and all(a[1] == b[0] for a, b in zip(bands, bands[1:]))
+        assert all(b0 % 256 == 0 for b0, _ in bands)
+    # a replicated C can be fused into programs that store through staging copies and do not share K between CTAs
+    big = shard.slab_variant(8192, 16384, 16384)
+    assert not shard.realise_sched_direct(big, 8192, 16384, 16384)                       # 256 x 256, launch control
+    assert shard.realise_sched_direct(shard.slab_variant(4096, 4096, 1024), 4096, 4096, 1024)   # stores from the registers
+    assert shard.realise_sched_direct(shard.slab_variant(2048, 4096, 4096), 2048, 4096, 4096)   # stream-K

@@ -57,6 +57,7 @@ def lib():
         "wg_realise": ([PV, i, i, i, PL], i),
         "wg_header": ([PV, i, i, i, ctypes.c_char_p, ctypes.c_size_t], i),
         "wg_plan_create": ([i, PV, i, i, i, vp, vp, vp, ctypes.POINTER(vp)], i),
+        "wg_plan_create_block": ([i, PV, i, i, i, vp, vp, vp, i, ctypes.POINTER(vp)], i),
         "wg_plan_set_timeout_ms": ([vp, u], i),
         "wg_plan_info": ([vp, PL], i),
         "wg_launch": ([vp, vp], i),

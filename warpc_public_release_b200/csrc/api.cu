@@ -361,6 +361,21 @@ extern "C" int wg_plan_create(int device, const wg_variant* v, int M, int N, int
   return WG_OK;
 }
 
+extern "C" int wg_plan_create_block(int device, const wg_variant* v, int M, int N, int K, const void* dA, const void* dBt, void* dC, int ldc,
+                                    void** plan) {
+  if (!plan || ldc < N || ldc % 4 != 0) return WG_E_ARG;
+  *plan = nullptr;
+  Plan* pl = new (std::nothrow) Plan();
+  if (!pl) return WG_E_ARG;
+  const int r = fill_plan(pl, device, v, M, N, K, dA, dBt, dC, ldc);
+  if (r != WG_OK) {
+    wg_plan_destroy(pl);
+    return r;
+  }
+  *plan = pl;
+  return WG_OK;
+}
+
 extern "C" int wg_host_plan_create(int device, const wg_variant* v, int M, int N, int K, void** plan) {
   if (!plan || !v || M <= 0 || N <= 0 || K <= 0) return WG_E_ARG;
   *plan = nullptr;

@@ -127,6 +127,7 @@ struct Ctrl {
   uint32_t sched_slot[2];  // valid, first CTA of the cancelled cluster
   uint32_t tmem_base;
   uint32_t abort;
+  uint64_t pump[4];        // a replicated C: an epilogue warp's reload of a block of the tile it has just stored
 };
 static_assert(sizeof(Ctrl) <= 512 && offsetof(Ctrl, clc_answer) % 16 == 0, "control block");
 
@@ -379,10 +380,9 @@ WB_DEV void epi_staged_tile(const CUtensorMap* map_c, const CUtensorMap* map_cw,
     fence_proxy_async_smem();
     __syncwarp();
     if (prof) t_sts += clock64() - t0, t0 = clock64();
-    // a replicated C: the same staged box goes to every other copy too (peer GPUs over NVLink), inside the same bulk
-    // group, so the tile's transfer runs under the next tiles' MMAs and the copy is free again when all have read it
+    // a replicated C: a CTA's last tile, staged whole in the drained ring, goes to every other copy (peer GPUs over NVLink)
+    // from the same staged boxes; tiles that cycle through the two staging copies are sent on afterwards (epi_forward_tile)
     if (wide == 0u) {
-      for (int r = 0; r < nrep; ++r) tma_store_if(lane == 0 ? 1u : 0u, replicas + 2 * r, x, y, copy, policy);
       tma_store_commit_if(lane == 0 ? 1u : 0u, add ? 1u : 0u, map_c, x, y, copy, policy);
     } else if ((i + 1) % C::WIDE_BLKS == 0) {
       // the last WIDE_BLKS blocks are WIDE_ROWS consecutive rows of C and of the ring: one store
@@ -395,6 +395,37 @@ WB_DEV void epi_staged_tile(const CUtensorMap* map_c, const CUtensorMap* map_cw,
     if (prof) t_tma += clock64() - t0;
   }
   if (prof && lane == 0) prof[0] = t_ld, prof[4] = t_copy, prof[8] = t_sts, prof[12] = t_tma, prof[44] = t_issue;  // events 11-14 and 22
+}
+
+// A replicated C, for a tile that went out through the two cycling staging copies: once the tile's stores have landed in
+// this GPU's C, the warp fetches its blocks back (they are still in the L2) one staging copy at a time and stores each to
+// every other copy of C -- TMA loads of this GPU's memory, TMA stores to the peers' over NVLink.  It runs while the MMA warp
+// is already on the next tile (the accumulator was released before the tile's stores), in the ~100 us the epilogue warps
+// otherwise sit idle, so a tile's transfer neither holds its staging copies through the epilogue nor lands on the link in
+// one burst with every other CTA's.  One lane does it all; `bar` is this warp's own barrier, `phase` its parity.
+template <class C>
+WB_DEV bool epi_forward_tile(const KParams& p, uint32_t abort_addr, const CUtensorMap* map_c, uint32_t my_staging, uint32_t bar, uint32_t& phase,
+                             int row, int col, int q, uint32_t lane, uint64_t policy) {
+  bool ok = true;
+  if (lane == 0) {
+    bulk_wait<0>();  // the tile's stores are written, not just read out of the staging copies
+#pragma unroll 1
+    for (int i = 0; ok && i < C::NBLK; ++i) {
+      int y, x;
+      epi_coords<C>(row, col, q, i, y, x);
+      const uint32_t copy = my_staging + uint32_t(i % C::EPI_COPIES) * C::EPI_COPY_BYTES;
+      bulk_wait_read<C::EPI_COPIES - 1>();  // the stores that last read this copy are done with it
+      mbar_arrive_expect_tx(bar, uint32_t(C::EPI_COPY_BYTES));
+      tma_load_2d<1>(copy, map_c, x, y, bar);
+      ok = wait_bar<false, false>(p, abort_addr, bar, phase, ST_WAIT_FULL, 0x200u + uint32_t(i));
+      phase ^= 1u;
+      if (!ok) break;
+      for (int r = 0; r < p.nrep; ++r) tma_store_2d(p.replicas + 2 * r, x, y, copy);
+      bulk_commit();
+    }
+  }
+  __syncwarp();
+  return ok;
 }
 
 // Straight from the registers: register j of a block is row y + j, the warp's lanes are 32
@@ -531,6 +562,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       // takers of an answer: a producer a CTA, the leader's MMA warp, four epilogue warps a CTA
       mbar_init(ctrl_at(offsetof(Ctrl, sched_empty)), CG + 1 + 4 * CG);
       st_shared_u32(abort_addr, 0u);
+    } else if (lane >= 20 && lane < 24) {
+      mbar_init(ctrl_at(offsetof(Ctrl, pump) + 8 * (lane - 20)), 1);
     } else if (lane == 19) {
       prefetch_tmap(&map_a);
       prefetch_tmap(&map_b);
@@ -713,7 +746,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     const int q = int(warp & 3u);
     const bool first_warp = (warp == 4);
     int acc = 0, nth = 0;
-    uint32_t acc_phase = 0;
+    uint32_t acc_phase = 0, pump_phase = 0;
     bool ok = true;
     const uint32_t acc_empty_leader = (CG == 2) ? mapa(acc_empty_bar(0), 0) : acc_empty_bar(0);
     const uint64_t store_policy = (((WB_DEBUG_WORD(p) >> 4) ^ uint32_t(p.l2_hints)) & 1u) ? l2_policy_evict_first() : l2_policy_evict_normal();
@@ -802,6 +835,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         // timing runs: the first warp's cycles in each part of the tile's store, events 11-14
         unsigned long long* prof = (p.stamps != nullptr && first_warp && nth < 4) ? p.stamps + (size_t(blockIdx.x) * 64 + 11) * 4 + nth : nullptr;
         epi_staged_tile<C>(&map_c, &map_cw, tbase, my_staging, row, col, q, lane, false, acc_empty_addr, store_policy, wide, prof, p.replicas, p.nrep);
+        if (p.nrep > 0 && wide == 0u)
+          ok = epi_forward_tile<C>(p, abort_addr, &map_c, my_staging, ctrl_at(offsetof(Ctrl, pump) + 8 * q), pump_phase, row, col, q, lane, store_policy);
       } else if (p.sched == SCHED_SPLITK) {
         // ---- split-K over the grid, adding in the L2 (gemm_swapped.ml:660-710).  The S runs
         // of a tile first zero disjoint shares of it (while their k loops run), raise their

@@ -101,10 +101,15 @@ class Plan(_Base):
     """Tensor maps + kernel-owned words for device pointers dA (M x K fp16), dBt (N x K fp16),
     dC (M x N fp32), row-major, 16-byte aligned."""
 
-    def __init__(self, variant, m, n, k, dA, dBt, dC, device=0):
+    def __init__(self, variant, m, n, k, dA, dBt, dC, device=0, ldc=None):
+        """`ldc`: C is a column block of a wider matrix whose rows are ldc fp32 words apart (wg_plan_create_block)."""
         h = ctypes.c_void_p()
-        check(_lib.lib().wg_plan_create(device, ctypes.byref(variant), m, n, k, ctypes.c_void_p(dA), ctypes.c_void_p(dBt),
-                                        ctypes.c_void_p(dC), ctypes.byref(h)), "wg_plan_create")
+        if ldc is None:
+            check(_lib.lib().wg_plan_create(device, ctypes.byref(variant), m, n, k, ctypes.c_void_p(dA), ctypes.c_void_p(dBt),
+                                            ctypes.c_void_p(dC), ctypes.byref(h)), "wg_plan_create")
+        else:
+            check(_lib.lib().wg_plan_create_block(device, ctypes.byref(variant), m, n, k, ctypes.c_void_p(dA), ctypes.c_void_p(dBt),
+                                                  ctypes.c_void_p(dC), int(ldc), ctypes.byref(h)), "wg_plan_create_block")
         self._h, self.shape, self.variant = h, (m, n, k), variant
 
 
