@@ -126,7 +126,8 @@ def shapes_table(torch, shapes):
         timer = None   # no CUPTI on this box: CUDA events around each call instead, said so per row
     rows = []
     for (m, n, k) in shapes:
-        r = ab.ab_shape(torch, timer, m, n, k, inputs="uniform", rounds=2 if m * n * k < 2 ** 40 else 1, series=50 if m * n * k < 2 ** 40 else 10, busy_ms=20.0)
+        r = ab.ab_shape(torch, timer, m, n, k, inputs="uniform", rounds=2 if m * n * k < 2 ** 40 else 1, series=50 if m * n * k < 2 ** 40 else 10,
+                        busy_ms=20.0 if m * n * k < 2 ** 35 else 250.0)   # long calls heat the chip: a longer run-in, so every turn sees the settled clock
         mid = lambda xs: (min(xs) + max(xs)) / 2
         rows.append({"shape": [m, n, k], "program": r["program"], "runs_as": r["runs_as"], "us": mid(r["ours_us"]), "ours_us": r["ours_us"],
                      "cublaslt_us": r["cublaslt_us"], "vs_cublaslt_pct": r["ours_vs_cublaslt_pct"], "vs_cublaslt_mean_pct": r["ours_vs_cublaslt_mean_pct"], "tflops": r["ours_tflops"],

@@ -8,6 +8,7 @@ import re
 import subprocess
 import sys
 
+import numpy as np
 import pytest
 
 import warpc_public_release_b200 as w
@@ -212,6 +213,26 @@ def test_a_header_text_rebuilds_the_exact_program():
         run_tma.variant_from_header(text.replace(".grid ", ".grid 1"), *cases[-4][0])
     with pytest.raises(RuntimeError):
         run_tma.variant_from_header("\n".join(l for l in text.splitlines() if not l.startswith("# variant")), *cases[-4][0])
+
+
+def test_mismatch_diagnostics(monkeypatch):
+    """run_tma's description of a wrong result (the reference's WARPC_TILES / WARPC_DIAG, run_tma.py:144-168) on a doctored C:
+    one tile never written and one entry holding a value from elsewhere."""
+    import io
+    from warpc_public_release_b200 import run_tma
+    monkeypatch.setenv("WARPC_TILES", "1")
+    monkeypatch.setenv("WARPC_DIAG", "1")
+    m, n, k = 512, 512, 256
+    li = w.realise(w.swapped(m, n, k, 256, 128, 5), m, n, k)
+    ref = np.arange(m * n, dtype=np.float32).reshape(m, n)
+    c = ref.copy()
+    c[256:512, 128:256] = 0
+    c[3, 5] = ref[7, 9]
+    out = io.StringIO()
+    run_tma.describe_mismatch(c, ref, np.argwhere(~(np.abs(c - ref) <= 1e-3)), 1e-3, li, out)
+    text = out.getvalue()
+    assert "wrong tiles 2 of 8, of them all-zero (never written) 1" in text and "x...\n" in text and ".x..\n" in text
+    assert "zero where wrong: 32768 of 32769" in text and "the reference has that value at [[7, 9]]" in text
 
 
 def test_no_cpu_fallback_without_a_device():

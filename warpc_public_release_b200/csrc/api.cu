@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <new>
@@ -85,8 +86,13 @@ int encode_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem, const void* pt
   cuuint64_t strides[1] = {cuuint64_t(ld > 0 ? ld : cols) * cuuint64_t(elem)};  // ld: elements between rows, when the matrix is a block of a wider one
   cuuint32_t box[2] = {cuuint32_t(box_cols), cuuint32_t(box_rows)};
   cuuint32_t estr[2] = {1, 1};
+  // L2 promotion of the maps' loads: 128 bytes as the reference's harness encodes them, WARPC_L2PROMO=0..3 to try
+  // another (none, 64, 128, 256 bytes: backend/node/run_tma.py:42)
+  int promo = int(CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
+  if (const char* e = std::getenv("WARPC_L2PROMO"))
+    if (e[0] >= '0' && e[0] <= '3' && e[1] == 0) promo = e[0] - '0';
   CUresult r = enc(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                   swizzle, CUtensorMapL2promotion(promo), CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? WG_OK : int(r);
 }
 

@@ -15,7 +15,10 @@ events and the last line reads
 
 WARPC_PDL=1 lets each timed launch begin while the one before it runs (the reference's AB_PDL,
 backend/node/ab.py:95-118).  WARPC_NO_CHECK=1 skips the check (prints UNCHECKED), WARPC_VERIFY_LAST=1 also checks what the
-last timed launch left, WARPC_STAMPS=1 prints the phase stamps of one more launch.  Returns
+last timed launch left, WARPC_STAMPS=1 prints the phase stamps of one more launch.  For a mismatch
+(run_tma.py:144-168): WARPC_DUMP=file.npy saves C and the reference stacked, WARPC_TILES=1 prints which
+output tiles are wrong and which of those were never written, WARPC_DIAG=1 where in a tile the wrong
+entries sit.  WARPC_L2PROMO=0..3 is read by the library when it encodes the tensor maps (run_tma.py:42).  Returns
 True when the check passed.  The numpy product is the harness's checker, exactly as in the
 reference; the kernel never runs on the CPU.
 """
@@ -73,6 +76,35 @@ def variant_from_header(text, m, n, k):
     return v
 
 
+def describe_mismatch(c, ref, bad, tol, li, out):
+    """Where a wrong result is wrong, in this kernel's own geometry: CTA tiles of tile_m x tile_n; inside a tile an
+    epilogue warp owns 32 columns (a lane a column) and handles them in blocks of 32 rows."""
+    import collections
+    m, n = c.shape
+    tm, tn = li.tile_m, li.tile_n
+    if os.environ.get("WARPC_TILES") and m % tm == 0 and n % tn == 0:
+        wrong = ~(np.abs(c - ref) <= tol)
+        per_tile = wrong.reshape(m // tm, tm, n // tn, tn).any(axis=(1, 3))
+        untouched = (c == 0).reshape(m // tm, tm, n // tn, tn).all(axis=(1, 3))
+        print("   wrong tiles %d of %d, of them all-zero (never written) %d" % (int(per_tile.sum()), per_tile.size, int((per_tile & untouched).sum())), file=out)
+        for i in range(min(per_tile.shape[0], 16)):
+            print("   " + "".join("x" if x else "." for x in per_tile[i, :128]), file=out)
+    if os.environ.get("WARPC_DIAG"):
+        rows, cols = bad[:, 0], bad[:, 1]
+        count = lambda xs: sorted(collections.Counter(int(x) for x in xs).items())
+        print("   zero where wrong: %d of %d" % (int(np.sum(c[rows, cols] == 0.0)), len(bad)), file=out)
+        print("   tiles (row, column) most hit: %s" % collections.Counter(zip((rows // tm).tolist(), (cols // tn).tolist())).most_common(5), file=out)
+        print("   32-row block in the tile: %s" % count((rows % tm) // 32), file=out)
+        print("   epilogue warp (32-column group in the tile): %s" % count((cols % tn) // 32), file=out)
+        print("   lane (column in the group), first ten: %s" % count(cols % 32)[:10], file=out)
+        print("   row in the block, first ten: %s" % count(rows % 32)[:10], file=out)
+        live = bad[c[rows, cols] != 0.0]
+        if len(live):
+            i, j = live[0]
+            same = np.argwhere(np.abs(ref - c[i, j]) <= tol)[:4].tolist()
+            print("   (%d,%d) holds %s; the reference has that value at %s" % (i, j, c[i, j], same), file=out)
+
+
 def run(variant, m, n, k, repeat=20, seed=1, name=None, out=sys.stdout):
     import torch
     if not torch.cuda.is_available():
@@ -97,7 +129,11 @@ def run(variant, m, n, k, repeat=20, seed=1, name=None, out=sys.stdout):
         return True
     c = dc.cpu().numpy()
     bad = np.argwhere(~(np.abs(c - ref) <= tol))
+    if os.environ.get("WARPC_DUMP"):
+        np.save(os.environ["WARPC_DUMP"], np.stack([c, ref]))
     print("first launch done, %d wrong" % len(bad), file=sys.stderr, flush=True)
+    if len(bad) and (os.environ.get("WARPC_TILES") or os.environ.get("WARPC_DIAG")):
+        describe_mismatch(c, ref, bad, tol, programs.realise(variant, m, n, k), out)
     ms = plan.time_launches(repeat, warmup=0)
     plan.status()
     if os.environ.get("WARPC_STAMPS"):
