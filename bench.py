@@ -356,9 +356,9 @@ def ours(args, rank, world, local_rank):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel on the one-GPU
-# workload (16384^3), from a one-pass ncu capture of those two counters: 7.92 GB read + 1.06 GB written.
+# workload (16384^3), from a one-pass ncu capture of those two counters: 8.82 GB read + 1.06 GB written.
 # No capture exists for the per-GPU slabs of a sharded run, so those lines carry null.
-TRAFFIC_BYTES_PER_LAUNCH = 8.98e9
+TRAFFIC_BYTES_PER_LAUNCH = 9.88e9
 
 
 def main():
