@@ -326,7 +326,7 @@ def ours(args, rank, world, local_rank):
     if ms_rep is not None:
         line["ms_per_step_with_allgather"] = ms_rep
         line["replicated_c"] = {"ms_per_step": ms_rep, "vs_sharded": ms_rep / ms,
-                                "how": {"fused": "the kernel itself fills every GPU's copy of C: each epilogue warp sends a stored tile's blocks on to the peers (TMA load from this GPU's L2, TMA store to peer memory over NVLink) while the next tile's MMAs run; a one-word all-reduce ends the step",
+                                "how": {"fused": "the kernel itself fills every GPU's copy of C: a forwarding warp reads each stored tile back from this GPU's L2 and stores it to the peers' memory over NVLink while the next tiles are computed; a one-word all-reduce ends the step",
                                         "nccl": "slab in 4 row bands on two streams, each band sent to every rank (grouped NCCL send/recv, in place) while the next band's tiles run"}[rep_how]}
     if world == 1 and not args.no_cpu:
         crow = 256

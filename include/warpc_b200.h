@@ -114,10 +114,12 @@ int wg_plan_destroy(void* plan);
 
 /* A replicated C, fused into the GEMM (no counterpart in the reference, which runs on one GPU): `n` further copies of
  * this plan's C -- device pointers this process can write, typically other GPUs' memory opened through CUDA IPC with
- * peer access enabled, each M x N fp32 row-major with the same row pitch as dC.  Every launch that follows stores each
- * block of C to all of them as well, from the same staged copy, tile by tile (TMA stores over NVLink), so the transfer
- * overlaps the tensor cores' work; the copies are complete when the launch is.  Only for programs that store through
- * staging copies and do not share K between CTAs (one tile a CTA, fixed grid, launch control); WG_E_VARIANT otherwise.
+ * peer access enabled, each M x N fp32 row-major with the same row pitch as dC.  Every launch that follows sends each
+ * tile of C it has stored on to all of them (a warp of the kernel reads the tile back from this GPU's L2 and stores it
+ * over NVLink while the next tiles are computed; a CTA's last tile goes out by TMA stores from its staged copy), so the
+ * transfer overlaps the tensor cores' work; the copies are complete when the launch is.  Only for programs that store
+ * through staging copies and do not share K between CTAs (one tile a CTA, fixed grid, launch control), with M and N
+ * whole multiples of the tile; WG_E_VARIANT otherwise.
  * n = 0 turns it off.  No TMA load ever touches these pointers. */
 int wg_plan_set_replicas(void* plan, int n, void* const* peer_dC);
 

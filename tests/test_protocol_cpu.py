@@ -72,6 +72,35 @@ def test_partial_sums_read_before_their_flag_is_caught(name, shape, build):
     assert "partial sums" in str(e.value)
 
 
+REPLICATED = [
+    ("launch_control_256x256", (1024, 2048, 512), lambda s: SW(*s, 256, 256, 4, clc=True, serpentine=True)),
+    ("launch_control_more_clusters_than_fit", (2304, 2048, 128), lambda s: SW(*s, 192 + 64, 128, 6, clc=True)),
+    ("stride_two_accumulators_last_tile_from_the_ring", (2048, 2304, 256), lambda s: SW(*s, 128, 128, 8, bufs=2, group=16)),
+    ("one_tile_a_cta", (512, 512, 256), lambda s: SW(*s, 256, 128, 5)),
+]
+
+
+@pytest.mark.parametrize("name,shape,build", REPLICATED, ids=[v[0] for v in REPLICATED])
+def test_a_replicated_c_reaches_every_copy_once(name, shape, build):
+    # every tile goes to the other copies exactly once: handed to the forwarding warp through the two slots, or (a CTA's
+    # last tile, staged whole in the ring) stored to them by the epilogue itself
+    v = build(shape)
+    for seed in (0, 1, 2):
+        assert protocol.check(v, *shape, seed=seed, replicas=3) > 0
+
+
+def test_a_forwarding_slot_overwritten_before_it_is_taken_is_caught():
+    # a forwarding warp that runs far behind (its copies cross NVLink) and an epilogue that does not wait for the slot's last
+    # use to have been taken: the slot is overwritten, or its barrier gets a fifth arrival
+    shape = (4096, 2304, 64)
+    v = SW(*shape, 128, 128, 8, bufs=2, group=16)   # eight tiles a CTA: the two slots are used several times
+    assert protocol.check(v, *shape, replicas=1, mutate={"fwd_copy_ticks": 600}) > 0
+    with pytest.raises(protocol.Violation) as e:
+        for seed in range(8):
+            protocol.check(v, *shape, seed=seed, replicas=1, mutate={"fwd_no_empty_wait": True, "fwd_copy_ticks": 600})
+    assert "forwarding slot" in str(e.value) or "beyond its" in str(e.value) or "parity would alias" in str(e.value)
+
+
 @pytest.mark.parametrize("shape", [(1024, 1024, 1024), (1536, 1536, 1536), (3072, 1280, 2048), (4096, 4096, 1024), (1024, 1024, 65536)],
                          ids=lambda s: "x".join(map(str, s)))
 def test_the_rules_program_for_a_benchmark_shape(shape):

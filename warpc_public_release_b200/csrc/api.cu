@@ -441,10 +441,11 @@ extern "C" int wg_plan_set_replicas(void* plan, int n, void* const* peer_dC) {
   WG_ON_DEVICE(pl->device);
   WG_CUDA(cudaDeviceSynchronize());  // no launch in flight reads the maps about to be replaced
   if (pl->d_replicas) cudaFree(pl->d_replicas);
-  pl->d_replicas = nullptr, pl->p.replicas = nullptr, pl->p.nrep = 0;
+  pl->d_replicas = nullptr, pl->p.replicas = nullptr, pl->p.rep_ptrs = nullptr, pl->p.nrep = 0;
   if (n == 0) return WG_OK;
   const wg_launch_info& li = pl->li;
   if (li.direct || li.sched == SCHED_SPLITK || li.sched == SCHED_STREAMK) return WG_E_VARIANT;
+  if (pl->M % li.tile_m != 0 || pl->N % li.tile_n != 0) return WG_E_VARIANT;  // whole tiles only: the forwarding warp copies without bounds
   std::vector<CUtensorMap> maps(size_t(2 * n));
   for (int r = 0; r < n; ++r) {
     if (!peer_dC[r] || (reinterpret_cast<uintptr_t>(peer_dC[r]) & 15u)) return WG_E_ARG;
@@ -453,9 +454,14 @@ extern "C" int wg_plan_set_replicas(void* plan, int n, void* const* peer_dC) {
       e = encode_2d(&maps[size_t(2 * r + 1)], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, peer_dC[r], pl->M, pl->N, pl->k->wide_rows, 32, CU_TENSOR_MAP_SWIZZLE_NONE, pl->ldc);
     if (e != WG_OK) return e;
   }
-  WG_CUDA(cudaMalloc(&pl->d_replicas, maps.size() * sizeof(CUtensorMap)));
-  WG_CUDA(cudaMemcpy(pl->d_replicas, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice));
-  pl->p.replicas = pl->d_replicas, pl->p.nrep = n;
+  // the maps, then the same copies' plain addresses, in one allocation
+  const size_t map_bytes = maps.size() * sizeof(CUtensorMap);
+  WG_CUDA(cudaMalloc(&pl->d_replicas, map_bytes + size_t(n) * sizeof(float*)));
+  WG_CUDA(cudaMemcpy(pl->d_replicas, maps.data(), map_bytes, cudaMemcpyHostToDevice));
+  WG_CUDA(cudaMemcpy(reinterpret_cast<char*>(pl->d_replicas) + map_bytes, peer_dC, size_t(n) * sizeof(float*), cudaMemcpyHostToDevice));
+  pl->p.replicas = pl->d_replicas;
+  pl->p.rep_ptrs = reinterpret_cast<float* const*>(reinterpret_cast<char*>(pl->d_replicas) + map_bytes);
+  pl->p.nrep = n;
   return WG_OK;
 }
 

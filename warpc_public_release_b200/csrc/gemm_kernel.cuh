@@ -62,7 +62,8 @@ struct KParams {
   uint32_t* flags;              // split-K / stream-K hand-off words
   float* ws;                    // split-K / stream-K through a workspace: a slot of TM x TN partial sums per CTA
   const CUtensorMap* replicas;  // further copies of C (other GPUs' memory): per copy the block map and the wide map, in global memory
-  int nrep;                     // how many; every staged block is stored to each of them as well
+  float* const* rep_ptrs;       // the same copies' addresses (of this plan's C inside each), in global memory
+  int nrep;                     // how many; every tile is sent on to each of them
   uint32_t* status;             // 8 words: [0] code, [1] site detail, [2] CTA, [3] parity/stage
   unsigned long long timeout_ns;
 #ifdef WB_TIMING_EXPERIMENTS
@@ -127,7 +128,10 @@ struct Ctrl {
   uint32_t sched_slot[2];  // valid, first CTA of the cancelled cluster
   uint32_t tmem_base;
   uint32_t abort;
-  uint64_t pump[4];        // a replicated C: an epilogue warp's reload of a block of the tile it has just stored
+  // a replicated C: the epilogue hands each tile it has stored to the forwarding warp through two slots
+  uint64_t fwd_full[2];    // the four epilogue warps' stores of the slot's tile are written
+  uint64_t fwd_empty[2];   // the forwarding warp has taken the slot's coordinates
+  int32_t fwd_slot[2][2];  // row, column of the tile; row < 0: no more tiles
 };
 static_assert(sizeof(Ctrl) <= 512 && offsetof(Ctrl, clc_answer) % 16 == 0, "control block");
 
@@ -381,7 +385,7 @@ WB_DEV void epi_staged_tile(const CUtensorMap* map_c, const CUtensorMap* map_cw,
     __syncwarp();
     if (prof) t_sts += clock64() - t0, t0 = clock64();
     // a replicated C: a CTA's last tile, staged whole in the drained ring, goes to every other copy (peer GPUs over NVLink)
-    // from the same staged boxes; tiles that cycle through the two staging copies are sent on afterwards (epi_forward_tile)
+    // from the same staged boxes; tiles that cycle through the two staging copies are sent on by the forwarding warp
     if (wide == 0u) {
       tma_store_commit_if(lane == 0 ? 1u : 0u, add ? 1u : 0u, map_c, x, y, copy, policy);
     } else if ((i + 1) % C::WIDE_BLKS == 0) {
@@ -397,35 +401,59 @@ WB_DEV void epi_staged_tile(const CUtensorMap* map_c, const CUtensorMap* map_cw,
   if (prof && lane == 0) prof[0] = t_ld, prof[4] = t_copy, prof[8] = t_sts, prof[12] = t_tma, prof[44] = t_issue;  // events 11-14 and 22
 }
 
-// A replicated C, for a tile that went out through the two cycling staging copies: once the tile's stores have landed in
-// this GPU's C, the warp fetches its blocks back (they are still in the L2) one staging copy at a time and stores each to
-// every other copy of C -- TMA loads of this GPU's memory, TMA stores to the peers' over NVLink.  It runs while the MMA warp
-// is already on the next tile (the accumulator was released before the tile's stores), in the ~100 us the epilogue warps
-// otherwise sit idle, so a tile's transfer neither holds its staging copies through the epilogue nor lands on the link in
-// one burst with every other CTA's.  One lane does it all; `bar` is this warp's own barrier, `phase` its parity.
-template <class C>
-WB_DEV bool epi_forward_tile(const KParams& p, uint32_t abort_addr, const CUtensorMap* map_c, uint32_t my_staging, uint32_t bar, uint32_t& phase,
-                             int row, int col, int q, uint32_t lane, uint64_t policy) {
+// A replicated C, for a tile that went out through the two cycling staging copies.  The tile is stored to this GPU's C as
+// always; the epilogue warps then hand its coordinates to the forwarding warp (warp 3, idle after set-up), which reads
+// the tile back (it is still in the L2) and writes it to every other copy -- plain 16-byte loads and stores, the stores
+// crossing NVLink -- while the epilogue and the MMA warp carry on with the next tiles.  The link takes what it takes: a
+// burst of every CTA's tile at once, or more bytes a tile than a tile's time carries, only makes the forwarding warp run
+// behind, not the epilogue (whose staging copies a TMA store to a peer would hold until the link had taken them).
+//
+// Epilogue side, all four warps: once this warp's stores of the tile are written (not just read out of the staging
+// copies) it arrives on the slot's `full` barrier; the first warp puts the coordinates in the slot before it does, having
+// waited for the forwarding warp to be done with the slot's use two tiles ago.  row < 0 says there are no more tiles.
+WB_DEV bool fwd_hand_over(const KParams& p, uint32_t abort_addr, uint32_t ctrl, uint32_t& count, int row, int col, bool first_warp, uint32_t lane) {
+  const uint32_t s = count & 1u, phase = (count >> 1) & 1u;
+  const uint32_t slot = ctrl + uint32_t(offsetof(Ctrl, fwd_slot)) + 8u * s;
   bool ok = true;
-  if (lane == 0) {
-    bulk_wait<0>();  // the tile's stores are written, not just read out of the staging copies
-#pragma unroll 1
-    for (int i = 0; ok && i < C::NBLK; ++i) {
-      int y, x;
-      epi_coords<C>(row, col, q, i, y, x);
-      const uint32_t copy = my_staging + uint32_t(i % C::EPI_COPIES) * C::EPI_COPY_BYTES;
-      bulk_wait_read<C::EPI_COPIES - 1>();  // the stores that last read this copy are done with it
-      mbar_arrive_expect_tx(bar, uint32_t(C::EPI_COPY_BYTES));
-      tma_load_2d<1>(copy, map_c, x, y, bar);
-      ok = wait_bar<false, false>(p, abort_addr, bar, phase, ST_WAIT_FULL, 0x200u + uint32_t(i));
-      phase ^= 1u;
-      if (!ok) break;
-      for (int r = 0; r < p.nrep; ++r) tma_store_2d(p.replicas + 2 * r, x, y, copy);
-      bulk_commit();
-    }
+  if (lane == 0 && row >= 0) {
+    bulk_wait<0>();
+    fence_proxy_async_global();  // written by the copy engine, read next by ordinary loads of another warp
+  }
+  if (first_warp) {
+    ok = wait_bar(p, abort_addr, ctrl + uint32_t(offsetof(Ctrl, fwd_empty)) + 8u * s, phase ^ 1u, ST_WAIT_EMPTY, 0x300u + s);
+    if (lane == 0) st_shared_u32(slot, uint32_t(row)), st_shared_u32(slot + 4u, uint32_t(col));
   }
   __syncwarp();
+  if (lane == 0) mbar_arrive(ctrl + uint32_t(offsetof(Ctrl, fwd_full)) + 8u * s);
+  ++count;
   return ok;
+}
+
+// Forwarding warp: one CTA tile of this GPU's C (whole: the host refuses further copies of a C with ragged tiles) to every
+// other copy, eight rows of loads in flight at a time.
+template <class C>
+WB_DEV void fwd_copy_tile(const KParams& p, int row, int col, uint32_t lane) {
+  constexpr int ROW_BYTES = C::TN * 4, V = (ROW_BYTES + 511) / 512, BATCH = 8;
+  const size_t ld = size_t(p.ldc);
+  const bool live[2] = {int(lane) * 16 < ROW_BYTES, int(lane) * 16 + 512 < ROW_BYTES};
+#pragma unroll 1
+  for (int r0 = 0; r0 < C::TM; r0 += BATCH) {
+    float4 v[BATCH][V];
+    const size_t at = size_t(row + r0) * ld + size_t(col) + lane * 4u;
+#pragma unroll
+    for (int b = 0; b < BATCH; ++b)
+#pragma unroll
+      for (int j = 0; j < V; ++j)
+        if (live[j]) v[b][j] = __ldcg(reinterpret_cast<const float4*>(p.C + at + size_t(b) * ld + size_t(j) * 128));
+    for (int r = 0; r < p.nrep; ++r) {
+      float* dst = p.rep_ptrs[r] + at;
+#pragma unroll
+      for (int b = 0; b < BATCH; ++b)
+#pragma unroll
+        for (int j = 0; j < V; ++j)
+          if (live[j]) *reinterpret_cast<float4*>(dst + size_t(b) * ld + size_t(j) * 128) = v[b][j];
+    }
+  }
 }
 
 // Straight from the registers: register j of a block is row y + j, the warp's lanes are 32
@@ -562,8 +590,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       // takers of an answer: a producer a CTA, the leader's MMA warp, four epilogue warps a CTA
       mbar_init(ctrl_at(offsetof(Ctrl, sched_empty)), CG + 1 + 4 * CG);
       st_shared_u32(abort_addr, 0u);
-    } else if (lane >= 20 && lane < 24) {
-      mbar_init(ctrl_at(offsetof(Ctrl, pump) + 8 * (lane - 20)), 1);
+    } else if (lane == 20 || lane == 21) {
+      mbar_init(ctrl_at(offsetof(Ctrl, fwd_full) + 8 * (lane - 20)), 4);   // the four epilogue warps
+      mbar_init(ctrl_at(offsetof(Ctrl, fwd_empty) + 8 * (lane - 20)), 1);  // the forwarding warp
     } else if (lane == 19) {
       prefetch_tmap(&map_a);
       prefetch_tmap(&map_b);
@@ -741,12 +770,28 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         if (!valid) break;
       }
     }
+  } else if (warp == 3) {
+    // ===== forwarding warp (a replicated C): tiles the epilogue has stored, on to the other GPUs' copies
+    if constexpr (!C::DIRECT) {
+      if (p.nrep > 0) {
+        for (uint32_t taken = 0;; ++taken) {
+          const uint32_t s = taken & 1u, phase = (taken >> 1) & 1u;
+          if (!wait_bar(p, abort_addr, ctrl_at(offsetof(Ctrl, fwd_full) + 8 * s), phase, ST_WAIT_FULL, 0x300u + s)) break;
+          const int t_row = int(ld_shared_u32(ctrl_at(offsetof(Ctrl, fwd_slot) + 8 * s)));
+          const int t_col = int(ld_shared_u32(ctrl_at(offsetof(Ctrl, fwd_slot) + 8 * s + 4)));
+          __syncwarp();
+          if (lane == 0) mbar_arrive(ctrl_at(offsetof(Ctrl, fwd_empty) + 8 * s));
+          if (t_row < 0) break;
+          fwd_copy_tile<C>(p, t_row, t_col, lane);
+        }
+      }
+    }
   } else if (warp >= 4) {
     // ===== epilogue: tensor memory -> registers -> C
     const int q = int(warp & 3u);
     const bool first_warp = (warp == 4);
     int acc = 0, nth = 0;
-    uint32_t acc_phase = 0, pump_phase = 0;
+    uint32_t acc_phase = 0, handed = 0;
     bool ok = true;
     const uint32_t acc_empty_leader = (CG == 2) ? mapa(acc_empty_bar(0), 0) : acc_empty_bar(0);
     const uint64_t store_policy = (((WB_DEBUG_WORD(p) >> 4) ^ uint32_t(p.l2_hints)) & 1u) ? l2_policy_evict_first() : l2_policy_evict_normal();
@@ -835,8 +880,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         // timing runs: the first warp's cycles in each part of the tile's store, events 11-14
         unsigned long long* prof = (p.stamps != nullptr && first_warp && nth < 4) ? p.stamps + (size_t(blockIdx.x) * 64 + 11) * 4 + nth : nullptr;
         epi_staged_tile<C>(&map_c, &map_cw, tbase, my_staging, row, col, q, lane, false, acc_empty_addr, store_policy, wide, prof, p.replicas, p.nrep);
-        if (p.nrep > 0 && wide == 0u)
-          ok = epi_forward_tile<C>(p, abort_addr, &map_c, my_staging, ctrl_at(offsetof(Ctrl, pump) + 8 * q), pump_phase, row, col, q, lane, store_policy);
+        if (p.nrep > 0 && wide == 0u) ok = fwd_hand_over(p, abort_addr, ctrl, handed, row, col, first_warp, lane);
       } else if (p.sched == SCHED_SPLITK) {
         // ---- split-K over the grid, adding in the L2 (gemm_swapped.ml:660-710).  The S runs
         // of a tile first zero disjoint shares of it (while their k loops run), raise their
@@ -911,6 +955,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       ++nth;
     }
     if constexpr (!C::DIRECT) {
+      if (p.nrep > 0) fwd_hand_over(p, abort_addr, ctrl, handed, -1, 0, first_warp, lane);  // the forwarding warp may leave
       // this warp is done with its partner CTA (its last word there was the accumulator's
       // release): it says so before waiting for its own stores, not after
       if (CG == 2 && ld_shared_u32(abort_addr) == 0u) {

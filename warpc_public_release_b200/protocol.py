@@ -67,8 +67,11 @@ class Barrier:
 
 
 class Model:
-    def __init__(self, li, m, n, k, seed=0, mutate=None):
+    def __init__(self, li, m, n, k, seed=0, mutate=None, replicas=0):
         self.li, self.m, self.n, self.k = li, m, n, k
+        # further copies of C (wg_plan_set_replicas): the epilogue hands stored tiles to a forwarding warp
+        self.replicas = replicas if (not li.direct and li.sched in (SCHED_ONE, SCHED_STRIDE, SCHED_CLC)) else 0
+        self.fwd_slot, self.forwarded, self.peer_stored = {}, defaultdict(int), defaultdict(int)
         self.rng = random.Random(seed)
         self.mut = dict(mutate or {})
         self.cg = li.cg
@@ -96,6 +99,9 @@ class Model:
             for b in range(2):
                 self.bars[cta, "acc_full", b] = Barrier("CTA %d acc_full[%d]" % (cta, b), 1)
                 self.bars[cta, "acc_empty", b] = Barrier("CTA %d acc_empty[%d]" % (cta, b), self.mut.get("acc_empty_count", 4 * self.cg))
+            for s_ in range(2):
+                self.bars[cta, "fwd_full", s_] = Barrier("CTA %d fwd_full[%d]" % (cta, s_), 4)
+                self.bars[cta, "fwd_empty", s_] = Barrier("CTA %d fwd_empty[%d]" % (cta, s_), 1)
             self.bars[cta, "sched_full", 0] = Barrier("CTA %d sched_full" % cta, 1)
             self.bars[cta, "sched_empty", 0] = Barrier("CTA %d sched_empty" % cta, self.cg + 1 + 4 * self.cg)
             for s in range(li.depth):
@@ -211,7 +217,7 @@ class Model:
     def epilogue(self, cta, warp):
         li, cg, c = self.li, self.cg, cta // self.cg
         leader, rank = c * cg, cta % cg
-        acc, acc_use, nth = 0, 0, 0
+        acc, acc_use, nth, handed = 0, 0, 0, 0
         shared_k = (not li.direct) and li.sched in (SCHED_SPLITK, SCHED_STREAMK)
         ws_k = bool(li.direct) and li.sched in (SCHED_SPLITK, SCHED_STREAMK)   # the same sharing through a workspace
         # hand-off words count launches; every epilogue thread reads its CTA's word before any of them
@@ -260,6 +266,13 @@ class Model:
             elif not shared_k:
                 yield ("wait", (cta, "acc_full", acc), acc_use)
                 yield ("read", c, acc, leader, tile, "store", warp, cta, wide)
+                if self.replicas and wide:
+                    if warp == 0:
+                        yield ("peerstore", tile)        # the last tile, staged whole in the ring: TMA stores to every copy
+                elif self.replicas:
+                    for ev in self.hand_over(cta, warp, handed, tile):
+                        yield ev
+                    handed += 1
             elif li.sched == SCHED_SPLITK:
                 S, s = li.split, c % li.split
                 yield ("zero", tile, s, S, warp, cta)
@@ -290,6 +303,34 @@ class Model:
             acc += 1
             if acc == self.nbuf:
                 acc, acc_use = 0, acc_use + 1
+        if self.replicas:
+            for ev in self.hand_over(cta, warp, handed, None):   # no more tiles: the forwarding warp may leave
+                yield ev
+
+    def hand_over(self, cta, warp, count, tile):
+        """An epilogue warp's part in handing a stored tile to the forwarding warp (fwd_hand_over): the first warp waits for
+        the slot's last use to have been taken and writes the tile into it; all four arrive on the slot's `full` barrier."""
+        s, index = count & 1, count >> 1
+        if warp == 0:
+            if not self.mut.get("fwd_no_empty_wait"):
+                yield ("wait", (cta, "fwd_empty", s), index - 1)
+            yield ("fwdslot", cta, s, tile)
+        yield ("arrive", (cta, "fwd_full", s), 0)
+
+    def forwarder(self, cta):
+        taken = 0
+        while True:
+            s, index = taken & 1, taken >> 1
+            yield ("wait", (cta, "fwd_full", s), index)
+            tile = self.fwd_slot.get((cta, s), "unset")
+            yield ("fwdtake", cta, s)
+            yield ("arrive", (cta, "fwd_empty", s), 0)
+            if tile is None:
+                return
+            yield ("fwdcopy", cta, tile)
+            for _ in range(self.mut.get("fwd_copy_ticks", 40)):   # the copy crosses NVLink and may take longer than a tile does
+                yield ("tick",)
+            taken += 1
 
     def scheduler(self, cta):
         cg = self.cg
@@ -381,6 +422,23 @@ class Model:
             if a["readers"] == 4 * self.cg:
                 a["state"] = "read"
             self.bars[leader, "acc_empty", acc].arrive(0)
+        elif kind == "fwdslot":
+            _, cta, s, tile = ev
+            if (cta, s) in self.fwd_slot:
+                raise Violation("CTA %d puts tile %r into forwarding slot %d, which still holds tile %r the forwarding warp has not taken" % (cta, tile, s, self.fwd_slot[cta, s]))
+            self.fwd_slot[cta, s] = tile
+        elif kind == "fwdtake":
+            _, cta, s = ev
+            if (cta, s) not in self.fwd_slot:
+                raise Violation("CTA %d's forwarding warp takes slot %d, which nobody has filled" % (cta, s))
+            del self.fwd_slot[cta, s]
+        elif kind == "fwdcopy":
+            _, cta, tile = ev
+            if not any(how == "store" for how, _ in self.tile_log.get(tile, [])):
+                raise Violation("CTA %d forwards tile %d before it is stored" % (cta, tile))
+            self.forwarded[tile] += 1
+        elif kind == "peerstore":
+            self.peer_stored[ev[1]] += 1
         elif kind in ("zero", "share"):
             _, tile, s, S, warp, cta = ev
             if warp == 0:
@@ -420,6 +478,8 @@ class Model:
                     roles.append(["CTA %d scheduler" % cta, self.scheduler(cta), None])
             for w in range(4):
                 roles.append(["CTA %d epilogue warp %d" % (cta, w), self.epilogue(cta, w), None])
+            if self.replicas:
+                roles.append(["CTA %d forwarding warp" % cta, self.forwarder(cta), None])
         live = list(range(len(roles)))
         while live or self.asyncs or any(self.commit_queue.values()):
             progressed = False
@@ -495,6 +555,12 @@ class Model:
                 raise Violation("tile %d is stored %d times" % (tile, len(stores)))
             elif log[0][0] != "store":
                 raise Violation("tile %d is added to before it is stored" % tile)
+        if self.replicas:
+            for tile in range(self.tiles):
+                if self.forwarded[tile] + self.peer_stored[tile] != 1:
+                    raise Violation("tile %d reaches the other copies of C %d times" % (tile, self.forwarded[tile] + self.peer_stored[tile]))
+            if self.fwd_slot:
+                raise Violation("forwarding slots still filled at the end: %r" % self.fwd_slot)
         extra = [t for t in self.tile_log if t >= self.tiles]
         if extra:
             raise Violation("tiles beyond the output were written: %s" % extra[:4])
@@ -511,11 +577,11 @@ def _ranges(xs):
     return ",".join(out) or "none"
 
 
-def check(variant, m, n, k, seed=0, mutate=None):
+def check(variant, m, n, k, seed=0, mutate=None, replicas=0):
     """Run the model for `variant` on an M x N x K problem; returns the number of events, raises
-    Violation with the first finding."""
+    Violation with the first finding.  `replicas` > 0: with further copies of C (wg_plan_set_replicas)."""
     li = programs.realise(variant, m, n, k)
-    return Model(li, m, n, k, seed=seed, mutate=mutate).run()
+    return Model(li, m, n, k, seed=seed, mutate=mutate, replicas=replicas).run()
 
 
 def main(argv=None):
