@@ -126,12 +126,13 @@ def shapes_table(torch, shapes):
         timer = None   # no CUPTI on this box: CUDA events around each call instead, said so per row
     rows = []
     for (m, n, k) in shapes:
+        long_calls = m * n * k >= 2 ** 35   # from 4096^3 up a block of calls runs into the power cap and the clock drifts across it:
         r = ab.ab_shape(torch, timer, m, n, k, inputs="uniform", rounds=2 if m * n * k < 2 ** 40 else 1, series=50 if m * n * k < 2 ** 40 else 10,
-                        busy_ms=20.0 if m * n * k < 2 ** 35 else 250.0)   # long calls heat the chip: a longer run-in, so every turn sees the settled clock
+                        busy_ms=20.0 if not long_calls else 100.0, alternate=long_calls)   # there the sides take turns call by call
         mid = lambda xs: (min(xs) + max(xs)) / 2
         rows.append({"shape": [m, n, k], "program": r["program"], "runs_as": r["runs_as"], "us": mid(r["ours_us"]), "ours_us": r["ours_us"],
                      "cublaslt_us": r["cublaslt_us"], "vs_cublaslt_pct": r["ours_vs_cublaslt_pct"], "vs_cublaslt_mean_pct": r["ours_vs_cublaslt_mean_pct"], "tflops": r["ours_tflops"],
-                     "cublaslt_tflops": r["cublaslt_tflops"], "calls_in_median": r["calls_in_median"], "timer": r["timer"],
+                     "cublaslt_tflops": r["cublaslt_tflops"], "calls_in_median": r["calls_in_median"], "timer": r["timer"], "order": r["order"],
                      "max_abs_diff_vs_cublaslt": r["max_abs_diff_vs_cublaslt"], "tol": 1e-3 * (k ** 0.5),
                      "ok": bool(r["max_abs_diff_vs_cublaslt"] <= 2e-3 * (k ** 0.5)),
                      "back_to_back_us": {"ours": r["back_to_back"]["ours_us"], "ours_dependent_launch": r["back_to_back"]["ours_dependent_launch_us"],
@@ -342,7 +343,8 @@ def ours(args, rank, world, local_rank):
             sweep = [r for r in table if tuple(r["shape"]) in SWEEP]
             tot_f = sum(2.0 * r["shape"][0] * r["shape"][1] * r["shape"][2] for r in sweep)
             tot_t = sum(r["back_to_back_us"]["ours"] for r in sweep) * 1e-6
-            line["shapes"] = {"method": "uniform[-1,1] inputs; us = GPU time of a call run alone (median of the last N calls; ours / cuBLASLt / cuBLASLt / ours, twice up to 8192^3); "
+            line["shapes"] = {"method": "uniform[-1,1] inputs; us = GPU time of a call run alone, median of the last N calls; up to 4096x4096x1024 in the published order (a block of calls a side: ours / cuBLASLt / cuBLASLt / ours, twice), "
+                                        "from 4096^3 up the sides take turns call by call (long calls run into the power cap and the clock drifts across a block; `order` per row); "
                                         "vs_cublaslt_pct = the library's fastest run against the midpoint of ours (README.md:93-95), vs_cublaslt_mean_pct = mean of runs against mean of runs; "
                                         "back_to_back_us = mean of launches back to back between CUDA events",
                               "within_2pct_of_cublaslt": sum(1 for r in table if r["vs_cublaslt_pct"] >= -2.0), "of": len(table),

@@ -151,7 +151,12 @@ def fastest_correct_algo(torch, lt, c_lib, c_ours, tol, work):
     return best, correct
 
 
-def ab_shape(torch, timer, m, n, k, inputs="hash", rounds=2, variant=None, busy_ms=30.0, series=0):
+def ab_shape(torch, timer, m, n, k, inputs="hash", rounds=2, variant=None, busy_ms=30.0, series=0, alternate=False):
+    """One shape, both sides.  `alternate`: instead of the published order (a block of calls a side: ours, library,
+    library, ours) the sides take turns call by call, each call still alone.  Long calls run the chip into its power cap
+    and the clock drifts over a block of them (seconds), so a side's block is measured at another clock than the other's;
+    taking turns gives both the same clock.  For short calls the published order is the fair one: a call that follows the
+    other side's finds the other side's C in the L2 instead of its own operands."""
     a, bt = make_inputs(torch, inputs, m, n, k)
     c_ours = torch.zeros((m, n), dtype=torch.float32, device="cuda")
     c_lib = torch.zeros((m, n), dtype=torch.float32, device="cuda")
@@ -200,7 +205,34 @@ def ab_shape(torch, timer, m, n, k, inputs="hash", rounds=2, variant=None, busy_
     sampler = ClockSampler(torch.cuda.current_device())
     sampler.start()
     sampler.timed = True
-    for _ in range(rounds):
+    if alternate:
+        for _ in range(rounds):
+            busy(plan.launch)
+            busy(lambda: lt.run(best))
+            mine, theirs = [], []
+            for _ in range(calls):
+                for side in ("ours", "lib"):
+                    if timer is not None:
+                        timer.clear()
+                    if timer is None:
+                        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        e0.record()
+                    (plan.launch() if side == "ours" else lt.run(best))
+                    if timer is None:
+                        e1.record()
+                    torch.cuda.synchronize()
+                    if timer is None:
+                        t = 1e3 * e0.elapsed_time(e1)
+                    else:
+                        names = timer.names()
+                        if side == "lib":
+                            lib_kernels = list(names)
+                        t = sum(timer.median(nm, 1)[0] for nm in names)
+                    (mine if side == "ours" else theirs).append(t)
+            med = lambda xs: sorted(xs[-last:])[len(xs[-last:]) // 2]
+            ours.append(med(mine))
+            lib.append(med(theirs))
+    for _ in range(0 if alternate else rounds):
         for side in ("ours", "lib", "lib", "ours"):
             if side == "ours":
                 ours.append(isolated(plan.launch, "gemm_kernel")[0])
@@ -253,6 +285,7 @@ def ab_shape(torch, timer, m, n, k, inputs="hash", rounds=2, variant=None, busy_
            # the same comparison without the published formula's lean to the library (its fastest run against our midpoint): mean of runs against mean of runs
            "ours_vs_cublaslt_mean_pct": 100.0 * ((sum(lib) / len(lib)) / (sum(ours) / len(ours)) - 1.0), "max_abs_diff_vs_cublaslt": err,
            "timer": "CUPTI kernel start-to-end" if timer is not None else "CUDA events around each call",
+           "order": "the sides take turns call by call" if alternate else "a block of calls a side: ours, library, library, ours",
            "published_warpc_us": PUBLISHED.get((m, n, k), (None, None))[0], "published_cublas138_us": PUBLISHED.get((m, n, k), (None, None))[1]}
     row["clocks"] = clocks  # over both sides' isolated calls: SM MHz (median), power (max), throttle reasons seen
     if steady is not None:
@@ -364,6 +397,7 @@ def main(argv=None):
     ap.add_argument("--json", default=None)
     ap.add_argument("--rounds", type=int, default=2)
     ap.add_argument("--series", type=int, default=0, help="also time this many launches back to back between events (ours, ours with dependent launch, cuBLASLt)")
+    ap.add_argument("--alternate", action="store_true", help="isolated calls, the sides taking turns call by call instead of in blocks (long calls under the power cap)")
     ap.add_argument("--event-rounds", type=int, default=0, help="the reference harness's event-timed rounds instead of isolated calls")
     ap.add_argument("--repeat", type=int, default=30, help="launches back to back per turn of an event round")
     ap.add_argument("--gap", type=float, default=0.0, help="seconds idle before each turn (event rounds)")
@@ -387,7 +421,7 @@ def main(argv=None):
     rows = []
     print("%-18s %-12s %-28s %17s %17s %8s   %s" % ("M x N x K", "rule's program", "runs as", "ours us", "cuBLASLt us", "vs lib", "published warpc / cuBLAS 13.8 us"))
     for (m, n, k) in shapes:
-        row = ab_shape(torch, timer, m, n, k, inputs=args.inputs, rounds=args.rounds, series=args.series)
+        row = ab_shape(torch, timer, m, n, k, inputs=args.inputs, rounds=args.rounds, series=args.series, alternate=args.alternate)
         rows.append(row)
         print("%-18s %-12s %-28s %8.2f-%-8.2f %8.2f-%-8.2f %+7.1f%%   %s / %s" % (
             "%dx%dx%d" % (m, n, k), row["program"], row["runs_as"], *row["ours_us"], *row["cublaslt_us"], row["ours_vs_cublaslt_pct"],
