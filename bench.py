@@ -252,6 +252,8 @@ def ours(args, rank, world, local_rank):
         ms_rep = over_ranks(e0.elapsed_time(e1) / args.steps)
         rep.status()
         rep_how = rep.how
+        barrier()       # every rank is done writing the others' copies before any of them is unmapped or freed
+        rep.close()
         del rep
         torch.cuda.empty_cache()
         barrier()

@@ -41,6 +41,8 @@ def main():
         torch.cuda.synchronize()
         assert np.array_equal(c.cpu().numpy(), gemm_ref.gemm_ref(a, bt)), "rank %d: gathered C differs at %dx%dx%d (%s)" % (rank, m, n, k, job.how)
         print("rank %d %dx%dx%d asked %s ran %s" % (rank, m, n, k, how, job.how), flush=True)
+        dist.barrier()
+        job.close()
         del job
         dist.barrier()
     dist.barrier()

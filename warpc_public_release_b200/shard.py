@@ -146,13 +146,20 @@ class ShardedGemm:
         return True
 
     def close(self):
-        """Give the other ranks' buffers back (after every rank is done launching)."""
+        """Give the other ranks' buffers back.  Call it on every rank once all ranks are done launching (after a barrier)
+        and before any rank frees its `c_full`: a kernel still running elsewhere may be writing this rank's copy."""
         from . import plan as wplan
         if getattr(self, "_peers", None):
-            self.plan.set_replicas([])
+            self.plan.set_replicas([])     # synchronises this device
             for ptr in self._peers:
                 wplan.ipc_release(ptr, device=self.device.index or 0)
             self._peers = []
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
     def launch(self):
         """This rank's GEMM (asynchronous).  Without `replicate_c`: one launch on the default stream.  With it: the
