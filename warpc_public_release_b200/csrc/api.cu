@@ -130,7 +130,7 @@ struct Plan {
   // the launches and the copies out run as a pipeline (see wg_host_run)
   std::vector<Plan*> blocks;
   int block_rows = 0, block_cols = 0;
-  cudaStream_t s_in = nullptr, s_mm = nullptr, s_out = nullptr, s_out2 = nullptr;  // copies out alternate between two streams
+  cudaStream_t s_in = nullptr, s_mm = nullptr, s_out = nullptr;
   std::vector<cudaEvent_t> ev_a, ev_b, ev_mm;  // launches carry the programmatic stream serialization attribute
   int M = 0, N = 0, K = 0;
 };
@@ -280,7 +280,6 @@ int make_blocks(Plan* pl, int device) {
   WG_CUDA(cudaStreamCreateWithFlags(&pl->s_in, cudaStreamNonBlocking));
   WG_CUDA(cudaStreamCreateWithFlags(&pl->s_mm, cudaStreamNonBlocking));
   WG_CUDA(cudaStreamCreateWithFlags(&pl->s_out, cudaStreamNonBlocking));
-  WG_CUDA(cudaStreamCreateWithFlags(&pl->s_out2, cudaStreamNonBlocking));
   pl->ev_a.resize(nr), pl->ev_b.resize(nc), pl->ev_mm.resize(size_t(nr) * nc);
   for (auto* list : {&pl->ev_a, &pl->ev_b, &pl->ev_mm})
     for (auto& e : *list) WG_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
@@ -294,7 +293,6 @@ int host_run_blocks(Plan* pl, const void* hA, const void* hBt, void* hC) {
   constexpr int B = 2048;
   const int nr = pl->block_rows, nc = pl->block_cols, N = pl->N, K = pl->K;
   const size_t panel = size_t(B) * K * 2;
-  int copies_out = 0;
   for (int d = 0; d < (nr > nc ? nr : nc); ++d) {
     if (d < nr) {
       WG_CUDA(cudaMemcpyAsync(static_cast<char*>(pl->dA) + d * panel, static_cast<const char*>(hA) + d * panel, panel, cudaMemcpyHostToDevice, pl->s_in));
@@ -310,14 +308,12 @@ int host_run_blocks(Plan* pl, const void* hA, const void* hBt, void* hC) {
       return wg_launch(pl->blocks[size_t(i) * nc + j], pl->s_mm);
     };
     // rows [r0, r0 + rows) x columns [c0, c0 + cols) of C out, once everything launched so far is done
-    // (a pitched copy of short row pieces does not fill the link by itself: two of them in flight, on two streams, do better)
     auto copy_out = [&](cudaEvent_t done, int r0, int rows, int c0, int cols) -> int {
-      cudaStream_t out = (copies_out++ & 1) ? pl->s_out2 : pl->s_out;
       WG_CUDA(cudaEventRecord(done, pl->s_mm));
-      WG_CUDA(cudaStreamWaitEvent(out, done, 0));
+      WG_CUDA(cudaStreamWaitEvent(pl->s_out, done, 0));
       const size_t off = (size_t(r0) * N + size_t(c0)) * 4;
       WG_CUDA(cudaMemcpy2DAsync(static_cast<char*>(hC) + off, size_t(N) * 4, static_cast<const char*>(pl->dC) + off, size_t(N) * 4, size_t(cols) * 4,
-                                size_t(rows), cudaMemcpyDeviceToHost, out));
+                                size_t(rows), cudaMemcpyDeviceToHost, pl->s_out));
       return WG_OK;
     };
     int r = WG_OK;
@@ -335,7 +331,6 @@ int host_run_blocks(Plan* pl, const void* hA, const void* hBt, void* hC) {
     if (r != WG_OK) return r;
   }
   WG_CUDA(cudaStreamSynchronize(pl->s_out));
-  WG_CUDA(cudaStreamSynchronize(pl->s_out2));
   WG_CUDA(cudaStreamSynchronize(pl->s_mm));
   return WG_OK;
 }
@@ -584,7 +579,7 @@ extern "C" int wg_plan_destroy(void* plan) {
   for (auto* list : {&pl->ev_a, &pl->ev_b, &pl->ev_mm})
     for (auto& e : *list)
       if (e) cudaEventDestroy(e);
-  for (cudaStream_t s : {pl->s_in, pl->s_mm, pl->s_out, pl->s_out2})
+  for (cudaStream_t s : {pl->s_in, pl->s_mm, pl->s_out})
     if (s) cudaStreamDestroy(s);
   if (pl->owns_buffers) {
     if (pl->dA) cudaFree(pl->dA);
