@@ -70,6 +70,7 @@ typedef struct wg_launch_info {
   int stage_bytes;         /* one ring slot: this CTA's A half-tile and B^T tile of one k-step */
   int staging_bytes;       /* the epilogue's cycling staging copies; 0 where every tile is staged in the drained ring */
   int ws_words;            /* fp32 words of workspace (a slot of tile_m x tile_n per CTA) when K is shared through a workspace, else 0 */
+  int sk_dp;               /* stream-K: pair tiles walked whole, by stride (a multiple of the resident pairs); the k-steps of the rest are dealt out evenly */
 } wg_launch_info;
 
 /* `warpc gemm M N K`: the program chosen for a shape (backend/programs.ml:46-80).

@@ -137,6 +137,9 @@ def test_realisation_invariants():
             assert li.grid <= 148 and li.nflags >= li.grid
         if li.sched == 1:
             assert li.grid == 148
+        if li.sched == 4:              # stream-K: whole waves of pair tiles by stride, at least one wave's worth of tiles shared
+            pairs = (s[0] // li.tile_m) * (s[1] // li.tile_n) // 2
+            assert li.sk_dp % 74 == 0 and 0 <= li.sk_dp <= pairs - 74 or li.sk_dp == 0
         assert li.group & (li.group - 1) == 0
         # the ring: rounds of ksub slots, all of it inside the 227 KB a CTA may have
         assert li.ksub in (1, 2, 4) and li.rounds >= 2 and li.rounds * li.ksub <= li.depth
@@ -150,6 +153,17 @@ def test_realisation_invariants():
     assert w.realise(w.swapped(2048, 2048, 2048, 128, 128, 8), 2048, 2048, 2048).tile_m == 128
     assert w.realise(w.choose(2048, 2048, 2048), 2048, 2048, 2048).tile_m == 256
     assert w.choose(2048, 2048, 2048).tile_m == 128 and w.choose(2048, 2048, 2048).retile == 1
+
+
+def test_stream_k_shares_only_the_last_wave_where_the_library_chose_it():
+    # 4096^3: 256 pair tiles on 74 resident pairs: two waves walked whole by stride, the third and the remainder dealt out
+    li = w.realise(w.choose(4096, 4096, 4096), 4096, 4096, 4096)
+    assert (li.sched, li.grid, li.sk_dp, li.nbuf) == (4, 148, 148, 2)
+    assert w.realise(w.choose(8192, 2048, 4096), 8192, 2048, 4096).sk_dp == 148
+    # the rule's own stream-K program (under a wave of tiles) and explicitly named stream-K deal every tile out, as the reference does
+    assert w.realise(w.choose(2048, 2048, 16384), 2048, 2048, 16384).sk_dp == 0
+    v = w.swapped(4096, 4096, 4096, 256, 128, 6, streamk=True, split_add=True, bufs=2)
+    assert w.realise(v, 4096, 4096, 4096).sk_dp == 0
 
 
 def test_workspace_forms_are_realised_as_named():

@@ -29,7 +29,8 @@ VARIANTS = [
     ("split_in_cluster_workspace", (256, 512, 16384), lambda s: SW(*s, 128, 128, 9, split=2, cluster_n=2, direct=True)),
     ("stream_k_workspace", (2560, 2048, 512), lambda s: SW(*s, 256, 128, 6, streamk=True, direct=True, bufs=2)),
     ("rule_2048", (2048, 2048, 2048), lambda s: w.choose(*s)),
-    ("rule_4096_stream_k", (4096, 4096, 1024 * 2), lambda s: w.choose(*s)),
+    ("rule_4096_stream_k", (4096, 4096, 1024 * 2), lambda s: w.choose(*s)),      # three waves by stride, the last wave's tiles shared
+    ("rule_stream_k_remainder_too_fine", (4096, 4864, 2048), lambda s: w.choose(*s)),  # 304 pair tiles: 4 waves + 8: one wave less by stride
     ("rule_split_k_long", (1024, 1024, 8192), lambda s: w.choose(*s)),
 ]
 

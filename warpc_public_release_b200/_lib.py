@@ -31,7 +31,7 @@ class LaunchInfo(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int) for n in (
         "kernel_id", "cg", "tile_m", "tile_n", "direct", "epi_rows", "grid", "cluster", "threads", "dynsmem", "mbarriers",
         "tmem_cols", "sched", "depth", "nbuf", "group", "cl_n", "serpentine", "ask_ahead", "split", "nflags",
-        "a_box_rows", "bt_box_rows", "c_box_rows", "ksub", "rounds", "wide_rows", "stage_bytes", "staging_bytes", "ws_words")]
+        "a_box_rows", "bt_box_rows", "c_box_rows", "ksub", "rounds", "wide_rows", "stage_bytes", "staging_bytes", "ws_words", "sk_dp")]
 
     def as_dict(self):
         return {n: getattr(self, n) for n, _ in self._fields_}

@@ -240,8 +240,8 @@ int fill_plan(Plan* pl, int device, const wg_variant* v, int M, int N, int K, co
   p.late_launch = v->late_launch;
   p.epi_ring = li.wide_rows != 0;
   if (li.sched == SCHED_STREAMK) {
-    const int clusters = li.grid / li.cluster, units = (p.ntiles / li.cluster) * p.kt;
-    p.sk_clusters = clusters, p.sk_q = units / clusters, p.sk_r = units % clusters;
+    const int clusters = li.grid / li.cluster, units = (p.ntiles / li.cluster - li.sk_dp) * p.kt;
+    p.sk_clusters = clusters, p.sk_q = units / clusters, p.sk_r = units % clusters, p.sk_dp = li.sk_dp;
   }
   p.C = static_cast<float*>(dC);
   p.flags = pl->d_flags;
@@ -746,8 +746,8 @@ extern "C" int wg_launch_noalloc(int device, const wg_variant* v, int M, int N, 
   p.late_launch = v->late_launch;
   p.epi_ring = li.wide_rows != 0;
   if (li.sched == SCHED_STREAMK) {
-    const int clusters = li.grid / li.cluster, units = (p.ntiles / li.cluster) * p.kt;
-    p.sk_clusters = clusters, p.sk_q = units / clusters, p.sk_r = units % clusters;
+    const int clusters = li.grid / li.cluster, units = (p.ntiles / li.cluster - li.sk_dp) * p.kt;
+    p.sk_clusters = clusters, p.sk_q = units / clusters, p.sk_r = units % clusters, p.sk_dp = li.sk_dp;
   }
   p.C = static_cast<float*>(dC);
   p.status = scratch;      // 8 status words, then the flags

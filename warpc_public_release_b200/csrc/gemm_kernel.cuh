@@ -53,6 +53,8 @@ struct KParams {
   int ask_ahead;  // probe the next stage before releasing this one
   int split;      // SCHED_SPLITK: runs of K per tile
   int sk_q, sk_r, sk_clusters;  // SCHED_STREAMK: units = q * clusters + r
+  int sk_dp;                    // SCHED_STREAMK: the first sk_dp cluster tiles (a multiple of the clusters) are walked whole, by stride,
+                                // after the units of the rest have been dealt out evenly
   int staging_bytes;            // the cycling staging copies (0: every tile is a CTA's last and is staged in the ring)
   int l2_hints;                 // bit 0: C's lines leave the L2 first; bit 1: operand lines leave it last
   int late_launch;              // the next grid in the stream is let go when the producer's last load is out, not at entry
@@ -233,8 +235,8 @@ struct Walker {
   uint32_t abort_addr, sched_full, sched_slot, sched_empty_first;  // shared addresses (the last in the first CTA)
   uint32_t rank, lane;
   uint32_t sched_parity = 0;
-  int tile = -1, seg = 0, t_first = 0, t_last = -1, kb_first = 0, ke_last = 0;
-  bool started = false;
+  int tile = -1, seg = 0, t_first = 0, t_last = -1, kb_first = 0, ke_last = 0, dp_tile = 0;
+  bool started = false, whole_tiles = false;
 
   WB_DEV Walker(const KParams& p_, uint32_t ctrl_addr, uint32_t rank_, uint32_t lane_) : p(p_), rank(rank_), lane(lane_) {
     abort_addr = ctrl_addr + offsetof(Ctrl, abort);
@@ -262,11 +264,14 @@ struct Walker {
       if (sched == SCHED_STREAMK) {
         // cluster c owns units [c q + c r / G, (c+1) q + (c+1) r / G) of tiles x k-steps,
         // walked from its last tile down to its first
+        // The shared part first, the whole tiles after it: the launch ends on a full wave of whole tiles in step
+        // (its clusters read the same operand panels at the same time), and each cluster shares one or two tiles only.
         const int c = blockIdx.x / C::CG, G = p.sk_clusters;
         const int b = c * p.sk_q + (c * p.sk_r) / G, l = (c + 1) * p.sk_q + ((c + 1) * p.sk_r) / G - 1;
-        if (l < b) return false;
+        dp_tile = c;
         t_first = b / p.kt, kb_first = b % p.kt, t_last = l / p.kt, ke_last = l % p.kt + 1;
         seg = t_last;
+        if (l < b) seg = t_first - 1;  // no units of the shared part for this cluster
       } else {
         return tile < p.ntiles;
       }
@@ -288,12 +293,19 @@ struct Walker {
         w.tile = tile, w.kb = 0, w.ke = p.kt;
         return true;
       }
-      seg -= 1;  // stream-K
+      if (!whole_tiles) seg -= 1;  // stream-K
     }
-    if (seg < t_first) return false;
-    w.tile = seg * C::CG + int(rank);
-    w.kb = (seg == t_first) ? kb_first : 0;
-    w.ke = (seg == t_last) ? ke_last : p.kt;
+    if (!whole_tiles && seg >= t_first) {
+      w.tile = (p.sk_dp + seg) * C::CG + int(rank);
+      w.kb = (seg == t_first) ? kb_first : 0;
+      w.ke = (seg == t_last) ? ke_last : p.kt;
+      return true;
+    }
+    whole_tiles = true;
+    if (dp_tile >= p.sk_dp) return false;
+    w.tile = dp_tile * C::CG + int(rank);
+    w.kb = 0, w.ke = p.kt;
+    dp_tile += p.sk_clusters;
     return true;
   }
 
@@ -303,7 +315,7 @@ struct Walker {
     const int sched = p.sched;
     if (sched == SCHED_ONE || sched == SCHED_SPLITK) return true;
     if (sched == SCHED_STRIDE) return w.tile + int(gridDim.x) >= p.ntiles;
-    if (sched == SCHED_STREAMK) return seg == t_first;
+    if (sched == SCHED_STREAMK) return whole_tiles ? dp_tile >= p.sk_dp : (seg == t_first && p.sk_dp == 0);
     return false;
   }
 };
@@ -873,7 +885,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           if (first_warp && lane == 0) stamp(p, EV_ACC_READY, nth);
           epi_direct_tile<C>(p, tbase, row, col, q, lane, acc_empty_addr);
         }
-      } else if (!shared_k) {
+      } else if (!shared_k || (p.sched == SCHED_STREAMK && w.kb == 0 && w.ke == p.kt)) {
+        // (a tile one cluster computes whole has no other part to wait for or to tell: stored like any tile)
         if (!wait_bar(p, abort_addr, acc_full_bar(acc), acc_phase, ST_WAIT_ACC_FULL, uint32_t(acc))) break;
         tc_fence_after();
         if (first_warp && lane == 0) stamp(p, EV_ACC_READY, nth);

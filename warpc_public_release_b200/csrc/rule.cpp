@@ -308,6 +308,16 @@ extern "C" int wg_realise(const wg_variant* v, int M, int N, int K, wg_launch_in
     if (streamk) {
       li.sched = 4, li.grid = kSms / 2 * 2;
       li.nflags = li.grid + total;
+      // Where this library chose stream-K itself (a poorly filled last wave), only the last whole wave and the remainder are
+      // shared: the waves before them are walked whole, by stride, in step.  Dealing every tile's k-steps out (the
+      // reference's stream-K, kept for variants named explicitly) leaves the 74 clusters at 74 different places of the walk,
+      // reading different operand panels at any one time: 8192x2048x4096 then reads its operands 2.5 times from DRAM.
+      // Measured, each call alone, pair tiles walked whole 0 / 74 / 148 / 222 of 256: 4096^3 91.1 / 90.9 / 89.0 / 89.7 us,
+      // 8192x2048x4096 92.0 / 91.1 / 88.8 / 89.3 (uniform inputs alike): one wave and the remainder shared is the best.
+      if (v->retile && !v->streamk) {
+        const int clusters = li.grid / 2, waves = (total / 2) / clusters;
+        li.sk_dp = waves > 1 ? (waves - 1) * clusters : 0;
+      }
     } else if (v->split_grid > 1 || v->split > 1) {
       li.split = v->split_grid > 1 ? v->split_grid : v->split;
       li.sched = 3, li.grid = total * li.split;

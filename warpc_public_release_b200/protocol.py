@@ -121,14 +121,18 @@ class Model:
             yield ("work", (c // S) * cg + rank, s * q + (s * r) // S, (s + 1) * q + ((s + 1) * r) // S, True)
             return
         if li.sched == SCHED_STREAMK:
-            G, units = self.clusters, (self.tiles // cg) * kt
+            # the first sk_dp cluster tiles are walked whole, by stride, after the units of the rest, which are dealt out evenly
+            G, dp = self.clusters, li.sk_dp
+            units = (self.tiles // cg - dp) * kt
             q, r = units // G, units % G
             b, last = c * q + (c * r) // G, (c + 1) * q + ((c + 1) * r) // G - 1
-            if last < b:
-                return
-            t_first, kb_first, t_last, ke_last = b // kt, b % kt, last // kt, last % kt + 1
-            for seg in range(t_last, t_first - 1, -1):
-                yield ("work", seg * cg + rank, kb_first if seg == t_first else 0, ke_last if seg == t_last else kt, seg == t_first)
+            if last >= b:
+                t_first, kb_first, t_last, ke_last = b // kt, b % kt, last // kt, last % kt + 1
+                for seg in range(t_last, t_first - 1, -1):
+                    yield ("work", (dp + seg) * cg + rank, kb_first if seg == t_first else 0, ke_last if seg == t_last else kt, seg == t_first and dp == 0)
+            whole = list(range(c, dp, G))
+            for i, t in enumerate(whole):
+                yield ("work", t * cg + rank, 0, kt, i == len(whole) - 1)
             return
         tile = cta
         if tile >= self.tiles:
@@ -263,7 +267,8 @@ class Model:
                 yield ("wsread", tile, [cta - cg], warp, cta)
                 yield ("wait", (cta, "acc_full", acc), acc_use)
                 yield ("read", c, acc, leader, tile, "sum", warp, cta, False)
-            elif not shared_k:
+            elif not shared_k or (li.sched == SCHED_STREAMK and kb == 0 and ke == self.kt):
+                # (under stream-K a tile one cluster computes whole has no other part: stored like any tile, no flag)
                 yield ("wait", (cta, "acc_full", acc), acc_use)
                 yield ("read", c, acc, leader, tile, "store", warp, cta, wide)
                 if self.replicas and wide:
