@@ -276,6 +276,8 @@ def ab_shape(torch, timer, m, n, k, inputs="hash", rounds=2, variant=None, busy_
     mid = lambda xs: (min(xs) + max(xs)) / 2
     li = programs.realise(v, m, n, k)
     sched = ("one tile a CTA", "fixed grid", "launch control", "split-K", "stream-K")[li.sched]
+    if li.sched == 4 and li.sk_dp:
+        sched = "fixed grid for %d pair tiles, stream-K for the rest" % li.sk_dp
     row = {"shape": [m, n, k], "inputs": inputs, "program": "%dx%d d%d" % (v.tile_m, v.tile_n, v.depth),
            "runs_as": "%dx%d d%d %s" % (li.tile_m, li.tile_n, li.depth, sched), "calls_in_median": last,
            "ours_us": [min(ours), max(ours)], "cublaslt_us": [min(lib), max(lib)], "cublaslt_algo": best,
