@@ -24,7 +24,7 @@ using namespace wb;
 template <class C>
 wb_kernel_entry entry(int id, const char* name) {
   wb_kernel_entry e;
-  e.id = id, e.cg = C::CG, e.tile_m = C::TM, e.tile_n = C::TN, e.direct = C::DIRECT ? 1 : 0;
+  e.id = id, e.cg = C::CG, e.tile_m = C::TM, e.tile_n = C::TN, e.direct = C::DIRECT ? 1 : 0, e.simple = C::SIMPLE ? 1 : 0, e.ksub = C::KSUB;
   e.reps = C::REPS, e.epi_rows = C::EPI_ROWS, e.wide_rows = C::WIDE_ROWS, e.ncols = C::NCOLS, e.stage_bytes = C::STAGE_BYTES;
   e.smem_fixed = C::smem_bytes(0);
   e.staging_bytes = C::STAGING_BYTES;
@@ -53,10 +53,14 @@ const wb_kernel_entry* table() {
 #define X(id, cg, tm, tn, direct, name) entry<Cfg<cg, tm, tn, direct>>(id, name),
       WB_KERNELS(X)
 #undef X
+      // whole tiles, one a CTA or by stride, stored from the registers, the ring's round fixed: a quarter of the code
+      entry<Cfg<2, 128, 64, true, 32, 2, true, 4>>(13, "pair_128x64_simple"),
+      entry<Cfg<2, 128, 128, true, 32, 2, true, 2>>(14, "pair_128x128_simple"),
+      entry<Cfg<2, 256, 128, true, 32, 2, true, 1>>(15, "pair_256x128_simple"),
   };
   return t;
 }
-constexpr int kKernels = 13;
+constexpr int kKernels = 16;
 
 // ------------------------------------------------------------------ driver entry points
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -337,10 +341,10 @@ int host_run_blocks(Plan* pl, const void* hA, const void* hBt, void* hC) {
 
 }  // namespace
 
-const wb_kernel_entry* wb_find_kernel(int cg, int tile_m, int tile_n, int direct) {
+const wb_kernel_entry* wb_find_kernel(int cg, int tile_m, int tile_n, int direct, int simple) {
   const wb_kernel_entry* t = table();
   for (int i = 0; i < kKernels; ++i)
-    if (t[i].cg == cg && t[i].tile_m == tile_m && t[i].tile_n == tile_n && t[i].direct == (direct ? 1 : 0)) return &t[i];
+    if (t[i].cg == cg && t[i].tile_m == tile_m && t[i].tile_n == tile_n && t[i].direct == direct && t[i].simple == simple) return &t[i];
   return nullptr;
 }
 const wb_kernel_entry* wb_kernel_at(int id) { return (id >= 0 && id < kKernels) ? &table()[id] : nullptr; }
@@ -432,7 +436,14 @@ extern "C" int wg_launch(void* plan, void* cuda_stream) {
   cudaLaunchAttribute attr[2];
   launch_config(pl->li, static_cast<cudaStream_t>(cuda_stream), pl->dependent_launch, &cfg, attr);
   void* args[5] = {&pl->map_a, &pl->map_b, &pl->map_c, &pl->map_cw, &pl->p};
-  return int(cudaLaunchKernelExC(&cfg, pl->k->fn, args));
+  // a simple instance takes no phase stamps: a plan asked for them launches the full instance of the same tile and store
+  const wb_kernel_entry* k = pl->k;
+  if (k->simple && pl->p.stamps != nullptr && !kSimpleStamps) {
+    k = wb_find_kernel(k->cg, k->tile_m, k->tile_n, k->direct, 0);
+    if (!k) return WG_E_NOKERNEL;
+    WG_CUDA(cudaFuncSetAttribute(k->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem));
+  }
+  return int(cudaLaunchKernelExC(&cfg, k->fn, args));
 }
 
 extern "C" int wg_plan_set_replicas(void* plan, int n, void* const* peer_dC) {

@@ -74,6 +74,13 @@ struct KParams {
   unsigned long long* stamps;   // timing builds: 32 events x 4 tiles per CTA, or null
 };
 
+// Timing builds (-DWB_SIMPLE_STAMPS) keep the phase stamps in the simple instances too.
+#ifdef WB_SIMPLE_STAMPS
+constexpr bool kSimpleStamps = true;
+#else
+constexpr bool kSimpleStamps = false;
+#endif
+
 // Builds with -DWB_TIMING_EXPERIMENTS carry a word of switches that make a launch skip its loads or
 // its MMAs (wrong results, for timing one role alone); the library as shipped has no such switch.
 #ifdef WB_TIMING_EXPERIMENTS
@@ -82,10 +89,16 @@ struct KParams {
 #define WB_DEBUG_WORD(p) 0u
 #endif
 
-template <int CG_, int TM_, int TN_, bool DIRECT_, int EPI_ROWS_ = 32, int EPI_COPIES_ = 2>
+template <int CG_, int TM_, int TN_, bool DIRECT_, int EPI_ROWS_ = 32, int EPI_COPIES_ = 2, bool SIMPLE_ = false, int KSUB_ = 0>
 struct Cfg {
   static constexpr int CG = CG_, TM = TM_, TN = TN_, TK = 64;
   static constexpr bool DIRECT = DIRECT_;
+  // whole tiles, one a CTA or a fixed grid walking them by stride, stored from the registers, and nothing else: no launch
+  // control, no K shared between CTAs, no further copies of C.  The launches that last ten to thirty microseconds are
+  // these, and the code they never run is not in their kernel.
+  static constexpr bool SIMPLE = SIMPLE_;
+  static constexpr int KSUB = KSUB_;  // k-steps a ring round, fixed at compile time (0: the launch says)
+  static_assert(!SIMPLE || DIRECT, "the simple instances store from the registers");
   static constexpr bool FOLD = (CG == 2 && TN == 64);  // M = 128 pair: 64 accumulator rows a CTA
   static constexpr int REPS = (TN == 256) ? 2 : 1;    // stacked MMA atoms
   static constexpr int MMA_M = (CG == 2) ? (FOLD ? 128 : 256) : 128;
@@ -182,11 +195,10 @@ WB_DEV void stamp(const KParams& p, int ev, int slot) {
 // The common case is one asm-internal spin.  Only when 4096 polls (each already sleeping in
 // hardware) have failed does the waiter look at the abort words and the GPU-wide timer, which
 // is slow to read.  CLUSTER: acquire at cluster scope (data another CTA stored before arriving).
-template <bool CLUSTER = false, bool WARP = true>
-WB_DEV bool wait_bar(const KParams& p, uint32_t abort_addr, uint32_t bar, uint32_t parity, uint32_t code, uint32_t detail) {
+template <bool CLUSTER, bool WARP>
+__device__ __noinline__ bool wait_bar_timed(const KParams& p, uint32_t abort_addr, uint32_t bar, uint32_t parity, uint32_t code, uint32_t detail) {
   auto all = [](uint32_t ok) { return WARP ? (__all_sync(0xffffffffu, ok) != 0) : (ok != 0u); };
   auto any = [](bool bad) { return WARP ? (__any_sync(0xffffffffu, bad) != 0) : bad; };
-  if (all(mbar_spin_wait<CLUSTER>(bar, parity, 1u << 12))) return true;
   const uint64_t t0 = globaltimer();
   for (;;) {
     if (all(mbar_spin_wait<CLUSTER>(bar, parity, 64))) return true;
@@ -198,6 +210,13 @@ WB_DEV bool wait_bar(const KParams& p, uint32_t abort_addr, uint32_t bar, uint32
       return false;
     }
   }
+}
+// (the timed part is a function of its own, not inlined at the twenty places that wait: it runs only when something is badly late)
+template <bool CLUSTER = false, bool WARP = true>
+WB_DEV bool wait_bar(const KParams& p, uint32_t abort_addr, uint32_t bar, uint32_t parity, uint32_t code, uint32_t detail) {
+  const uint32_t ok = mbar_spin_wait<CLUSTER>(bar, parity, 1u << 12);
+  if (WARP ? (__all_sync(0xffffffffu, ok) != 0) : (ok != 0u)) return true;
+  return wait_bar_timed<CLUSTER, WARP>(p, abort_addr, bar, parity, code, detail);
 }
 
 // Bounded wait until *flag == target (split-K / stream-K hand-off between CTAs).
@@ -253,6 +272,7 @@ struct Walker {
       started = true;
       tile = blockIdx.x;
       w.tile = tile, w.kb = 0, w.ke = p.kt;
+      if constexpr (C::SIMPLE) return tile < p.ntiles;
       if (sched == SCHED_SPLITK) {
         // cluster c is run (c mod S) of tile-cluster (c div S): k-steps [s q + s r / S, ...)
         const int c = blockIdx.x / C::CG, S = p.split, s = c % S, q = p.kt / S, r = p.kt % S;
@@ -277,7 +297,7 @@ struct Walker {
       }
     } else {
       if (sched == SCHED_ONE || sched == SCHED_SPLITK) return false;
-      if (sched == SCHED_STRIDE) {
+      if (C::SIMPLE || sched == SCHED_STRIDE) {
         tile += gridDim.x;
         w.tile = tile, w.kb = 0, w.ke = p.kt;
         return tile < p.ntiles;
@@ -314,7 +334,7 @@ struct Walker {
   WB_DEV bool is_last(const Work& w) const {
     const int sched = p.sched;
     if (sched == SCHED_ONE || sched == SCHED_SPLITK) return true;
-    if (sched == SCHED_STRIDE) return w.tile + int(gridDim.x) >= p.ntiles;
+    if (C::SIMPLE || sched == SCHED_STRIDE) return w.tile + int(gridDim.x) >= p.ntiles;
     if (sched == SCHED_STREAMK) return whole_tiles ? dp_tile >= p.sk_dp : (seg == t_first && p.sk_dp == 0);
     return false;
   }
@@ -572,8 +592,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   const uint32_t warp = warp_uniform(threadIdx.x >> 5), lane = threadIdx.x & 31;
   const uint32_t rank = (CG == 2) ? warp_uniform(cluster_ctarank()) : 0u;
   const bool leader = (rank == 0);
-  const int nbuf = p.nbuf, rounds = p.rounds, ksub = p.ksub;
-  const long long cycles_at_entry = clock64();
+  const int nbuf = p.nbuf, rounds = p.rounds, ksub = (C::KSUB != 0) ? C::KSUB : p.ksub;
+  // the simple instances take no phase stamps (a plan that is asked for stamps launches the full instance of the same tile)
+  auto stamp = [](const KParams& pp, int ev, int slot) {
+    if constexpr (!C::SIMPLE || kSimpleStamps) wb::stamp(pp, ev, slot);
+  };
+  auto stamp_value = [](const KParams& pp, int ev, int slot, long long value) {
+    if constexpr (!C::SIMPLE || kSimpleStamps) wb::stamp_value(pp, ev, slot, value);
+  };
+  const long long cycles_at_entry = C::SIMPLE ? 0 : clock64();
   // Dependent launch (the reference's PREEXIT / ACQBULK, backend/sass.ml:496-502, gemm_swapped.ml:169-172, 232, 368):
   // under the programmatic-stream-serialization launch attribute the next grid in the stream may
   // take SMs as this grid's CTAs leave, from this instruction on -- or, "late launch", once the
@@ -663,11 +690,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         stamp(p, EV_LOAD_FIRST, nth);
         while (kleft != 0u) {
           uint32_t gave_up;
-          if (ksub == 2)
+          if ((C::KSUB == 0 || C::KSUB == 2) && ksub == 2)
             gave_up = load_rounds<CG, 2>(1u, kleft, uint32_t(rounds), stage, phase, x, empty_bar(0), full_bar(0), full_leader0, leader ? 1u : 0u,
                                          C::TX_BYTES, ring, 2u * C::STAGE_BYTES, uint32_t(C::A_BYTES), &map_a, a_row, &map_b, col, 1u << 14, WB_DEBUG_WORD(p),
                                          uint32_t(C::STAGE_BYTES), load_policy);
-          else if (ksub == 4)
+          else if ((C::KSUB == 0 || C::KSUB == 4) && ksub == 4)
             gave_up = load_rounds<CG, 4>(1u, kleft, uint32_t(rounds), stage, phase, x, empty_bar(0), full_bar(0), full_leader0, leader ? 1u : 0u,
                                          C::TX_BYTES, ring, 4u * C::STAGE_BYTES, uint32_t(C::A_BYTES), &map_a, a_row, &map_b, col, 1u << 14, WB_DEBUG_WORD(p),
                                          uint32_t(C::STAGE_BYTES), load_policy);
@@ -715,17 +742,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         const uint32_t d = tmem_base + uint32_t(acc * C::NCOLS);
         uint32_t kleft = uint32_t(w.ke - w.kb), accumulate = 0;
         // timing runs: when the tile's first round of operands has landed (the loop's own first poll then passes at once)
-        if (p.stamps != nullptr && !wait_bar<false, false>(p, abort_addr, full_bar(int(stage)), phase, ST_WAIT_FULL, stage)) {
+        if ((!C::SIMPLE || kSimpleStamps) && p.stamps != nullptr && !wait_bar<false, false>(p, abort_addr, full_bar(int(stage)), phase, ST_WAIT_FULL, stage)) {
           ok = false;
           break;
         }
         stamp(p, EV_MMA_FIRST, nth);
         while (kleft != 0u) {
           uint32_t gave_up;
-          if (C::REPS == 1 && ksub == 2)
+          if (C::REPS == 1 && (C::KSUB == 0 || C::KSUB == 2) && ksub == 2)
             gave_up = mma_rounds<CG, 2>(1u, kleft, uint32_t(rounds), stage, phase, accumulate, full_bar(0), empty_bar(0), d, uint32_t(C::SPAN),
                                         b_lo0, STAGE16, a_lo0, 2u * STAGE16, DESC_HI, C::IDESC, 1u << 14, WB_DEBUG_WORD(p));
-          else if (C::REPS == 1 && ksub == 4)
+          else if (C::REPS == 1 && (C::KSUB == 0 || C::KSUB == 4) && ksub == 4)
             gave_up = mma_rounds<CG, 4>(1u, kleft, uint32_t(rounds), stage, phase, accumulate, full_bar(0), empty_bar(0), d, uint32_t(C::SPAN),
                                         b_lo0, STAGE16, a_lo0, 4u * STAGE16, DESC_HI, C::IDESC, 1u << 14, WB_DEBUG_WORD(p));
           else
@@ -752,7 +779,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   } else if (warp == 2) {
     // ===== scheduler (cluster launch control): the cluster's first CTA asks for one more
     // cluster's tiles at a time and hands the answer to every taker of both CTAs
-    if (p.sched == SCHED_CLC && leader) {
+    if (!C::SIMPLE && p.sched == SCHED_CLC && leader) {
       const uint32_t clc_bar = ctrl_at(offsetof(Ctrl, clc_bar)), answer = ctrl_at(offsetof(Ctrl, clc_answer));
       const uint32_t sched_empty = ctrl_at(offsetof(Ctrl, sched_empty));
       uint32_t pf = 0, pe = 0;
@@ -814,7 +841,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     const bool shared_k = !C::DIRECT && (p.sched == SCHED_SPLITK || p.sched == SCHED_STREAMK);
     // the same sharing through a workspace (store from the registers): split-K counts launches in the CTA's word like
     // the L2 form; stream-K raises the word to 1 and the CTA that takes the partial sum puts it back to 0
-    const bool ws_k = C::DIRECT && (p.sched == SCHED_SPLITK || p.sched == SCHED_STREAMK);
+    const bool ws_k = C::DIRECT && !C::SIMPLE && (p.sched == SCHED_SPLITK || p.sched == SCHED_STREAMK);
     float* ws_slot = ws_k ? p.ws + size_t(blockIdx.x) * size_t(C::TM * C::TN) : nullptr;
     uint32_t target = 0;
     if (ws_k && p.sched == SCHED_SPLITK) target = ld_relaxed_gpu(p.flags + blockIdx.x) + 1u;
@@ -891,7 +918,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         tc_fence_after();
         if (first_warp && lane == 0) stamp(p, EV_ACC_READY, nth);
         // timing runs: the first warp's cycles in each part of the tile's store, events 11-14
-        unsigned long long* prof = (p.stamps != nullptr && first_warp && nth < 4) ? p.stamps + (size_t(blockIdx.x) * 64 + 11) * 4 + nth : nullptr;
+        unsigned long long* prof = (!C::SIMPLE && p.stamps != nullptr && first_warp && nth < 4) ? p.stamps + (size_t(blockIdx.x) * 64 + 11) * 4 + nth : nullptr;
         epi_staged_tile<C>(&map_c, &map_cw, tbase, my_staging, row, col, q, lane, false, acc_empty_addr, store_policy, wide, prof, p.replicas, p.nrep);
         if (p.nrep > 0 && wide == 0u) ok = fwd_hand_over(p, abort_addr, ctrl, handed, row, col, first_warp, lane);
       } else if (p.sched == SCHED_SPLITK) {
@@ -973,7 +1000,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       // release): it says so before waiting for its own stores, not after
       if (CG == 2 && ld_shared_u32(abort_addr) == 0u) {
         tc_fence_before();
-        cluster_arrive();
+        cluster_arrive_relaxed();
         arrived = true;
       }
       if (lane == 0) bulk_wait_read<0>();  // the last stores have read their staging copies
@@ -993,7 +1020,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   }
   tc_fence_before();
   if constexpr (CG == 2) {
-    if (!arrived) cluster_arrive();
+    if (!arrived) cluster_arrive_relaxed();
     cluster_wait();
   } else {
     __syncthreads();

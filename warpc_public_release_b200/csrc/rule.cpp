@@ -296,9 +296,10 @@ extern "C" int wg_realise(const wg_variant* v, int M, int N, int K, wg_launch_in
       // 34.3 / 37.8, 1536^3 12.7 / 13.8).  A one-tile launch ends on its store either way, and a TMA store's source is
       // only read ~1 us after it is issued, which the CTA has to wait out before it may leave; on the fixed-grid walk
       // the register stores of tile t run beside tile t+1's loads without taking the copy engine from them, and the
-      // ring gets the staging copies' room (one more stage).  The 64-column fold tile (1024^3) measures the same both
-      // ways and the 256 x 256 tile's exposed 256 KB store is faster through the copy engine: both stay staged.
-      if (!streamk && !clc && li.tile_n == 128 && M % li.tile_m == 0 && N % li.tile_n == 0) li.direct = 1;
+      // ring gets the staging copies' room (one more stage).  The 64-column fold tile (1024^3) measured the same both
+      // ways in the full kernel and 7.9 against 8.5 us in the simple instance (below), which only stores from the
+      // registers; the 256 x 256 tile's exposed 256 KB store is faster through the copy engine and stays staged.
+      if (!streamk && !clc && li.tile_n <= 128 && M % li.tile_m == 0 && N % li.tile_n == 0) li.direct = 1;
     }
     const int tiles_m = (M + li.tile_m - 1) / li.tile_m, tiles_n = (N + li.tile_n - 1) / li.tile_n;
     const int total = tiles_m * tiles_n;
@@ -331,7 +332,14 @@ extern "C" int wg_realise(const wg_variant* v, int M, int N, int K, wg_launch_in
       li.sched = 1, li.grid = resident_clusters(2) * 2;
     }
   }
-  const wb_kernel_entry* e = wb_find_kernel(li.cg, li.tile_m, li.tile_n, li.direct);
+  // Launches of whole tiles, one a CTA or a fixed grid by stride, stored from the registers, run in the "simple" instance
+  // of their tile where there is one: the same kernel compiled without launch control, shared K, further copies of C
+  // and phase stamps, 26-29 KB of code instead of 67-90.  These are the launches of ten to thirty microseconds, where
+  // every role's first pass through its code is a visible part of the time: measured, full -> simple instance,
+  // 1024^3 9.6 -> 8.5 us, 1536^3 12.3 -> 11.5, 2048^3 17.8 -> 16.9, 4096x4096x1024 31.8 -> 30.3.
+  const wb_kernel_entry* e = nullptr;
+  if (li.direct && li.sched <= 1 && M % li.tile_m == 0 && N % li.tile_n == 0) e = wb_find_kernel(li.cg, li.tile_m, li.tile_n, 1, 1);
+  if (!e) e = wb_find_kernel(li.cg, li.tile_m, li.tile_n, li.direct, 0);
   if (!e) return WG_E_NOKERNEL;
   li.kernel_id = e->id;
   li.epi_rows = e->epi_rows;
@@ -370,6 +378,12 @@ extern "C" int wg_realise(const wg_variant* v, int M, int N, int K, wg_launch_in
   li.stage_bytes = e->stage_bytes;
   li.ksub = (e->reps != 1 || e->stage_bytes > 24 * 1024) ? 1 : (e->stage_bytes <= 16 * 1024 ? 4 : 2);
   while (li.ksub > 1 && li.depth / li.ksub < 2) li.ksub /= 2;
+  if (e->simple && e->ksub != 0 && e->ksub != li.ksub) {
+    // the simple instance fixes its round at compile time: another round runs in the full instance of the same tile
+    e = wb_find_kernel(li.cg, li.tile_m, li.tile_n, li.direct, 0);
+    if (!e) return WG_E_NOKERNEL;
+    li.kernel_id = e->id;
+  }
   li.rounds = li.depth / li.ksub;
   li.mbarriers = 2 * li.rounds + 4 + 3;  // full + empty a round, two accumulators' full + empty, scheduler's three
   // a CTA's last tile is staged whole in the ring when the ring can hold it

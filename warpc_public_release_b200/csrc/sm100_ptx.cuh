@@ -144,6 +144,10 @@ WB_DEV void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" 
 
 WB_DEV void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
 WB_DEV void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+// Arrival that orders nothing: for the barrier the CTAs of a pair meet at before they leave.  Every word one CTA writes
+// into the other's shared or tensor memory has been waited for by its reader by then; a releasing arrival would hold each
+// thread until its own global stores (a tile of C from the registers) had been performed.
+WB_DEV void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); }
 
 WB_DEV void named_bar_sync(uint32_t id, uint32_t nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
