@@ -445,13 +445,15 @@ WB_DEV void umma_commit_if(uint32_t issuer, uint32_t bar, uint16_t mask) {
   "@e tcgen05.mma.cta_group::" G ".kind::f16 [" D "], da, db, %17, " PRED ";\n\t"
 #define WB_KL_MMA_J(G, D, A0, J, PRED) \
   "add.u32 ta, " A0 ", " J ";\n\tadd.u32 tb, mb, " J ";\n\t" WB_KL_MMA(G, D, "ta", "tb", PRED)
-// Order inside one k-step: the first MMA, then the commit that frees the stage BEFORE (issued
-// while that MMA runs, so it never sits between two stages' MMAs), the middle MMAs, a
-// non-blocking probe of the next stage's barrier (its answer is back before the loop comes
-// round), the last two MMAs.
+// Order inside one k-step: the commit that frees the stage BEFORE comes after the first MMA (issued while that MMA
+// runs), the ring's bookkeeping for the next stage (in place: index, barrier addresses, descriptor offset, parity) after
+// the second, the count and a non-blocking probe of the next stage's barrier (its answer is back before the loop comes
+// round) after the third; only the loop's branch sits between the last MMA of one k-step and the first of the next.
+// Measured, the placement of the bookkeeping does not matter (nor do twelve more dependent ALU instructions a k-step):
+// the pace is the tensor pipe's with operands from shared memory, about 143 cycles an N = 256 MMA in the kernel.
 #define WB_KL_HEAD                                                                                   \
-  "{\n\t.reg .pred e, ec, p, q, w, pa, pt, c, pr, pv, pm;\n\t"                                       \
-  ".reg .b32 n, fb, eb, s16, ta, tb, d1, a1, ma, mb, dbg, pb, nst, nfb, neb, ns16, nph;\n\t"         \
+  "{\n\t.reg .pred e, ec, p, q, w, pa, pt, c, pr, pv;\n\t"                                           \
+  ".reg .b32 n, fb, eb, s16, ta, tb, d1, a1, ma, mb, dbg, pb;\n\t"                                   \
   ".reg .b64 da, db;\n\t.reg .b16 mk;\n\t"                                                           \
   "setp.ne.u32 ec, %5, 0;\n\tand.b32 dbg, %15, 2;\n\tsetp.eq.and.u32 e, dbg, 0, ec;\n\t"             \
   "setp.eq.u32 pt, 0, 0;\n\tsetp.ne.u32 pa, %4, 0;\n\tmov.b16 mk, 3;\n\t"                            \
@@ -471,30 +473,30 @@ WB_DEV void umma_commit_if(uint32_t issuer, uint32_t bar, uint16_t mask) {
   "add.u32 ma, %11, s16;\n\tadd.u32 mb, %13, s16;\n\t"
 #define WB_KL_COMMIT2 "@pv tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [pb], mk;\n\t"
 #define WB_KL_COMMIT1 "@pv tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [pb];\n\t"
-// where the ring goes next, and a probe of that stage's full barrier (not past the last k-step)
-#define WB_KL_PROBE                                                                                  \
-  "add.u32 nst, %1, 1;\n\tadd.u32 nfb, fb, 8;\n\tadd.u32 neb, eb, 8;\n\tadd.u32 ns16, s16, %14;\n\tmov.u32 nph, %2;\n\t" \
-  "setp.eq.u32 w, nst, %6;\n\t"                                                                      \
-  "@w mov.u32 nst, 0;\n\t@w mov.u32 nfb, %7;\n\t@w mov.u32 neb, %8;\n\t@w mov.u32 ns16, 0;\n\t@w xor.b32 nph, nph, 1;\n\t" \
-  "setp.eq.u32 pr, 1, 0;\n\tsetp.gt.u32 pm, %3, 1;\n\t"                                              \
-  "@pm mbarrier.test_wait.parity.shared::cta.b64 pr, [nfb], nph;\n\t"
-#define WB_KL_TAIL(COMMIT)                                                                           \
-  "setp.eq.u32 pa, 0, 0;\n\tmov.u32 %4, 1;\n\t"                                                      \
+// this stage is handed back by the commit of the NEXT k-step (or the one after the loop); the ring moves on, in place
+#define WB_KL_NEXT                                                                                   \
   "mov.u32 pb, eb;\n\tsetp.ne.u32 pv, %5, 0;\n\t"                                                    \
-  "mov.u32 %1, nst;\n\tmov.u32 fb, nfb;\n\tmov.u32 eb, neb;\n\tmov.u32 s16, ns16;\n\tmov.u32 %2, nph;\n\t" \
-  "sub.u32 %3, %3, 1;\n\tsetp.ne.u32 c, %3, 0;\n\t@c bra WB_KL_LOOP;\n"                              \
+  "add.u32 %1, %1, 1;\n\tadd.u32 fb, fb, 8;\n\tadd.u32 eb, eb, 8;\n\tadd.u32 s16, s16, %14;\n\t"     \
+  "setp.eq.u32 w, %1, %6;\n\t"                                                                       \
+  "@w mov.u32 %1, 0;\n\t@w mov.u32 fb, %7;\n\t@w mov.u32 eb, %8;\n\t@w mov.u32 s16, 0;\n\t@w xor.b32 %2, %2, 1;\n\t"
+// one k-step fewer to go, and a probe of the next stage's full barrier (not past the last k-step)
+#define WB_KL_PROBE                                                                                  \
+  "sub.u32 %3, %3, 1;\n\tsetp.ne.u32 c, %3, 0;\n\tsetp.eq.u32 pr, 1, 0;\n\t"                         \
+  "@c mbarrier.test_wait.parity.shared::cta.b64 pr, [fb], %2;\n\t"
+#define WB_KL_TAIL(COMMIT)                                                                           \
+  "setp.eq.u32 pa, 0, 0;\n\tmov.u32 %4, 1;\n\t@c bra WB_KL_LOOP;\n"                        \
   "WB_KL_OUT:\n\t"                                                                                   \
   COMMIT                                                                                             \
   "}"
 // one k-step's MMAs for one atom (REPS == 1) or two stacked atoms (REPS == 2)
 #define WB_KL_STEP1(G, COMMIT)                                                                       \
-  WB_KL_MMA(G, "%9", "ma", "mb", "pa") COMMIT WB_KL_MMA_J(G, "%9", "ma", "2", "pt") WB_KL_PROBE     \
-  WB_KL_MMA_J(G, "%9", "ma", "4", "pt") WB_KL_MMA_J(G, "%9", "ma", "6", "pt")
+  WB_KL_MMA(G, "%9", "ma", "mb", "pa") COMMIT WB_KL_MMA_J(G, "%9", "ma", "2", "pt") WB_KL_NEXT      \
+  WB_KL_MMA_J(G, "%9", "ma", "4", "pt") WB_KL_PROBE WB_KL_MMA_J(G, "%9", "ma", "6", "pt")
 #define WB_KL_STEP2(G, COMMIT)                                                                       \
-  WB_KL_MMA(G, "%9", "ma", "mb", "pa") COMMIT WB_KL_MMA_J(G, "%9", "ma", "2", "pt")                 \
-  WB_KL_MMA_J(G, "%9", "ma", "4", "pt") WB_KL_MMA_J(G, "%9", "ma", "6", "pt")                       \
+  WB_KL_MMA(G, "%9", "ma", "mb", "pa") COMMIT WB_KL_MMA_J(G, "%9", "ma", "2", "pt") WB_KL_NEXT      \
+  WB_KL_MMA_J(G, "%9", "ma", "4", "pt") WB_KL_PROBE WB_KL_MMA_J(G, "%9", "ma", "6", "pt")           \
   "add.u32 a1, ma, %12;\n\t"                                                                         \
-  WB_KL_MMA(G, "d1", "a1", "mb", "pa") WB_KL_MMA_J(G, "d1", "a1", "2", "pt") WB_KL_PROBE            \
+  WB_KL_MMA(G, "d1", "a1", "mb", "pa") WB_KL_MMA_J(G, "d1", "a1", "2", "pt")                        \
   WB_KL_MMA_J(G, "d1", "a1", "4", "pt") WB_KL_MMA_J(G, "d1", "a1", "6", "pt")
 #define WB_KL_ARGS                                                                                          \
   : "=r"(status), "+r"(stage), "+r"(phase), "+r"(kleft), "+r"(accumulate)                                   \
@@ -578,15 +580,19 @@ WB_DEV uint32_t load_k_loop(uint32_t issuer, uint32_t& kleft, uint32_t depth, ui
   "add.u32 ga, ga, %12;\n\tadd.u32 gb, gb, %12;\n\t"                                                 \
   WB_KR_MMA(G, "%9", "ga", "gb", "pt", GUARD) WB_KR_MMA_J(G, "ga", "gb", "2", GUARD)                \
   WB_KR_MMA_J(G, "ga", "gb", "4", GUARD) WB_KR_MMA_J(G, "ga", "gb", "6", GUARD)
+// Whole rounds run in a loop of their own with no guards; a tile's last, partly used round (and a tile shorter than a
+// round) runs once after it, every k-step past the first under the guard for "it exists".
 #define WB_KR_HEAD(KSUB)                                                                             \
-  "{\n\t.reg .pred e, e1, e2, e3, ec, p, q, w, pa, pt, c, pr, pv, pm;\n\t"                           \
-  ".reg .b32 n, fb, eb, s16, ta, tb, ga, gb, ma, mb, dbg, pb, nst, nfb, neb, ns16, nph, use;\n\t"    \
+  "{\n\t.reg .pred e, e1, e2, e3, ec, p, q, w, pa, pt, c, pr, pv, pm, pf;\n\t"                       \
+  ".reg .b32 n, fb, eb, s16, ta, tb, ga, gb, ma, mb, dbg, pb;\n\t"                                   \
   ".reg .b64 da, db;\n\t.reg .b16 mk;\n\t"                                                           \
   "setp.ne.u32 ec, %5, 0;\n\tand.b32 dbg, %15, 2;\n\tsetp.eq.and.u32 e, dbg, 0, ec;\n\t"             \
   "setp.eq.u32 pt, 0, 0;\n\tsetp.ne.u32 pa, %4, 0;\n\tmov.b16 mk, 3;\n\t"                            \
   "setp.eq.u32 pr, 1, 0;\n\tsetp.eq.u32 pv, 1, 0;\n\tmov.u32 pb, 0;\n\t"                             \
   "mov.u32 %0, 0;\n\t"                                                                               \
-  "mad.lo.u32 fb, %1, 8, %7;\n\tmad.lo.u32 eb, %1, 8, %8;\n\tmul.lo.u32 s16, %1, %14;\n"             \
+  "mad.lo.u32 fb, %1, 8, %7;\n\tmad.lo.u32 eb, %1, 8, %8;\n\tmul.lo.u32 s16, %1, %14;\n\t"           \
+  "add.u32 ma, %11, s16;\n\tadd.u32 mb, %13, s16;\n\t"                                                \
+  "setp.lt.u32 pf, %3, " KSUB ";\n\t@pf bra WB_KR_LAST;\n"                                           \
   "WB_KR_LOOP:\n\t"                                                                                  \
   "@pr bra WB_KR_GO;\n\t"                                                                            \
   "mov.u32 n, 0;\n"                                                                                  \
@@ -595,33 +601,78 @@ WB_DEV uint32_t load_k_loop(uint32_t issuer, uint32_t& kleft, uint32_t depth, ui
   "@p bra WB_KR_GO;\n\t"                                                                             \
   "add.u32 n, n, 1;\n\tsetp.lt.u32 q, n, %18;\n\t@q bra WB_KR_WAIT;\n\t"                             \
   "mov.u32 %0, 1;\n\tbra WB_KR_OUT;\n"                                                               \
-  "WB_KR_GO:\n\t"                                                                                    \
+  "WB_KR_GO:\n\t"
+// the last round: entered with fewer than KSUB k-steps left (none: nothing to do)
+#define WB_KR_LAST_HEAD                                                                              \
+  "WB_KR_LAST:\n\t"                                                                                  \
+  "setp.eq.u32 pf, %3, 0;\n\t@pf bra WB_KR_OUT;\n\t"                                                 \
+  "@pr bra WB_KR_GO2;\n\t"                                                                           \
+  "mov.u32 n, 0;\n"                                                                                  \
+  "WB_KR_WAIT2:\n\t"                                                                                 \
+  "mbarrier.test_wait.parity.shared::cta.b64 p, [fb], %2;\n\t"                                       \
+  "@p bra WB_KR_GO2;\n\t"                                                                            \
+  "add.u32 n, n, 1;\n\tsetp.lt.u32 q, n, %18;\n\t@q bra WB_KR_WAIT2;\n\t"                            \
+  "mov.u32 %0, 1;\n\tbra WB_KR_OUT;\n"                                                               \
+  "WB_KR_GO2:\n\t"                                                                                   \
   "add.u32 ma, %11, s16;\n\tadd.u32 mb, %13, s16;\n\tmov.u32 ga, ma;\n\tmov.u32 gb, mb;\n\t"         \
   "setp.gt.u32 e1, %3, 1;\n\tand.pred e1, e1, e;\n\t"                                                \
   "setp.gt.u32 e2, %3, 2;\n\tand.pred e2, e2, e;\n\t"                                                \
   "setp.gt.u32 e3, %3, 3;\n\tand.pred e3, e3, e;\n\t"
-// where the ring goes next, and a probe of that round's full barrier (not past the last round)
-#define WB_KR_PROBE(KSUB)                                                                            \
-  "add.u32 nst, %1, 1;\n\tadd.u32 nfb, fb, 8;\n\tadd.u32 neb, eb, 8;\n\tadd.u32 ns16, s16, %14;\n\tmov.u32 nph, %2;\n\t" \
-  "setp.eq.u32 w, nst, %6;\n\t"                                                                      \
-  "@w mov.u32 nst, 0;\n\t@w mov.u32 nfb, %7;\n\t@w mov.u32 neb, %8;\n\t@w mov.u32 ns16, 0;\n\t@w xor.b32 nph, nph, 1;\n\t" \
-  "setp.eq.u32 pr, 1, 0;\n\tsetp.gt.u32 pm, %3, " KSUB ";\n\t"                                       \
-  "@pm mbarrier.test_wait.parity.shared::cta.b64 pr, [nfb], nph;\n\t"
-#define WB_KR_TAIL(KSUB, COMMIT)                                                                     \
-  "setp.eq.u32 pa, 0, 0;\n\tmov.u32 %4, 1;\n\t"                                                      \
-  "mov.u32 pb, eb;\n\tsetp.ne.u32 pv, %5, 0;\n\t"                                                    \
-  "mov.u32 %1, nst;\n\tmov.u32 fb, nfb;\n\tmov.u32 eb, neb;\n\tmov.u32 s16, ns16;\n\tmov.u32 %2, nph;\n\t" \
-  "min.u32 use, %3, " KSUB ";\n\tsub.u32 %3, %3, use;\n\tsetp.ne.u32 c, %3, 0;\n\t@c bra WB_KR_LOOP;\n" \
+#define WB_KR_END(COMMIT)                                                                            \
+  "mov.u32 %3, 0;\n\tsetp.eq.u32 pa, 0, 0;\n\tmov.u32 %4, 1;\n"                                      \
   "WB_KR_OUT:\n\t"                                                                                   \
   COMMIT                                                                                             \
   "}"
-// k-step 0: first MMA, the lagged commit of the round before, the rest; then the later k-steps,
-// with the probe of the next round once the first of them is under way
-#define WB_KR_STEP0(G, COMMIT)                                                                       \
+// A whole round.  An M = 256 MMA narrower than N = 256 takes the tensor pipe about 76 cycles whatever its N, the pipe
+// queues next to nothing, and issuing one takes its thread most of that: what the thread does between two MMAs beyond
+// two or three plain instructions, or one slow one (the commit, the probe), is time the pipe idles.  So the round's
+// bookkeeping is dealt out over the gaps between its MMAs: the lagged commit of the round before after the first MMA;
+// then, a few instructions a gap, the ring moved on (index, parity, this round's empty barrier kept for the next commit,
+// the next round's barriers and descriptor offset), the count, the probe of the next round's full barrier, and the next
+// round's descriptors; nothing but the branch after the last MMA.
+#define WB_KR_G_A "mov.u32 pb, eb;\n\tadd.u32 %1, %1, 1;\n\tsetp.eq.u32 w, %1, %6;\n\t"
+#define WB_KR_G_B "@w mov.u32 %1, 0;\n\t@w xor.b32 %2, %2, 1;\n\tsetp.ne.u32 pv, %5, 0;\n\t"
+#define WB_KR_G_C "mad.lo.u32 fb, %1, 8, %7;\n\tmad.lo.u32 eb, %1, 8, %8;\n\tmul.lo.u32 s16, %1, %14;\n\t"
+#define WB_KR_G_D(KSUB) "sub.u32 %3, %3, " KSUB ";\n\tsetp.ge.u32 c, %3, " KSUB ";\n\tsetp.ne.u32 pm, %3, 0;\n\t"
+#define WB_KR_G_E "setp.eq.u32 pr, 1, 0;\n\t@pm mbarrier.test_wait.parity.shared::cta.b64 pr, [fb], %2;\n\t"
+#define WB_KR_G_F "add.u32 ma, %11, s16;\n\tadd.u32 mb, %13, s16;\n\tsetp.eq.u32 pa, 0, 0;\n\tmov.u32 %4, 1;\n\t"
+#define WB_KR_G_NEXTSLOT "add.u32 ga, ga, %12;\n\tadd.u32 gb, gb, %12;\n\t"
+#define WB_KR_G_FIRSTSLOT "add.u32 ga, ma, %12;\n\tadd.u32 gb, mb, %12;\n\t"
+// rounds of two: eight MMAs, seven gaps
+#define WB_KR_ROUND2(G, COMMIT)                                                                      \
+  WB_KR_MMA(G, "%9", "ma", "mb", "pa", "e") COMMIT                                                   \
+  WB_KR_MMA_J(G, "ma", "mb", "2", "e") WB_KR_G_A                                                     \
+  WB_KR_MMA_J(G, "ma", "mb", "4", "e") WB_KR_G_B                                                     \
+  WB_KR_MMA_J(G, "ma", "mb", "6", "e") WB_KR_G_FIRSTSLOT                                             \
+  WB_KR_MMA(G, "%9", "ga", "gb", "pt", "e") WB_KR_G_C                                                \
+  WB_KR_MMA_J(G, "ga", "gb", "2", "e") WB_KR_G_D("2")                                                \
+  WB_KR_MMA_J(G, "ga", "gb", "4", "e") WB_KR_G_E                                                     \
+  WB_KR_G_F WB_KR_MMA_J(G, "ga", "gb", "6", "e")                                                     \
+  "@c bra WB_KR_LOOP;\n"
+// rounds of four: sixteen MMAs
+#define WB_KR_ROUND4(G, COMMIT)                                                                      \
+  WB_KR_MMA(G, "%9", "ma", "mb", "pa", "e") COMMIT                                                   \
+  WB_KR_MMA_J(G, "ma", "mb", "2", "e") WB_KR_G_A                                                     \
+  WB_KR_MMA_J(G, "ma", "mb", "4", "e") WB_KR_G_B                                                     \
+  WB_KR_MMA_J(G, "ma", "mb", "6", "e") WB_KR_G_FIRSTSLOT                                             \
+  WB_KR_MMA(G, "%9", "ga", "gb", "pt", "e") WB_KR_G_C                                                \
+  WB_KR_MMA_J(G, "ga", "gb", "2", "e") WB_KR_MMA_J(G, "ga", "gb", "4", "e")                         \
+  WB_KR_MMA_J(G, "ga", "gb", "6", "e") WB_KR_G_NEXTSLOT                                              \
+  WB_KR_MMA(G, "%9", "ga", "gb", "pt", "e") WB_KR_G_D("4")                                           \
+  WB_KR_MMA_J(G, "ga", "gb", "2", "e") WB_KR_MMA_J(G, "ga", "gb", "4", "e")                         \
+  WB_KR_MMA_J(G, "ga", "gb", "6", "e") WB_KR_G_NEXTSLOT                                              \
+  WB_KR_MMA(G, "%9", "ga", "gb", "pt", "e") WB_KR_G_E                                                \
+  WB_KR_MMA_J(G, "ga", "gb", "2", "e") WB_KR_MMA_J(G, "ga", "gb", "4", "e")                         \
+  WB_KR_G_F WB_KR_MMA_J(G, "ga", "gb", "6", "e")                                                     \
+  "@c bra WB_KR_LOOP;\n"
+// the same first k-step in the last round (the ring moves on after it, nothing is probed)
+#define WB_KR_STEP0_LAST(G, COMMIT)                                                                  \
   WB_KR_MMA(G, "%9", "ma", "mb", "pa", "e") COMMIT WB_KR_MMA_J(G, "ma", "mb", "2", "e")             \
-  WB_KR_MMA_J(G, "ma", "mb", "4", "e") WB_KR_MMA_J(G, "ma", "mb", "6", "e")
-#define WB_KR_BODY2(G, COMMIT) WB_KR_STEP0(G, COMMIT) WB_KR_PROBE("2") WB_KR_GROUP(G, "e1")
-#define WB_KR_BODY4(G, COMMIT) WB_KR_STEP0(G, COMMIT) WB_KR_GROUP(G, "e1") WB_KR_PROBE("4") WB_KR_GROUP(G, "e2") WB_KR_GROUP(G, "e3")
+  WB_KL_NEXT WB_KR_MMA_J(G, "ma", "mb", "4", "e") WB_KR_MMA_J(G, "ma", "mb", "6", "e")
+#define WB_KR_BODY2(G, COMMIT)                                                                       \
+  WB_KR_ROUND2(G, COMMIT) WB_KR_LAST_HEAD WB_KR_STEP0_LAST(G, COMMIT) WB_KR_GROUP(G, "e1")
+#define WB_KR_BODY4(G, COMMIT)                                                                       \
+  WB_KR_ROUND4(G, COMMIT) WB_KR_LAST_HEAD WB_KR_STEP0_LAST(G, COMMIT) WB_KR_GROUP(G, "e1") WB_KR_GROUP(G, "e2") WB_KR_GROUP(G, "e3")
 
 template <int CG, int KSUB>
 WB_DEV uint32_t mma_rounds(uint32_t issuer, uint32_t& kleft, uint32_t depth, uint32_t& stage, uint32_t& phase, uint32_t& accumulate,
@@ -629,10 +680,10 @@ WB_DEV uint32_t mma_rounds(uint32_t issuer, uint32_t& kleft, uint32_t depth, uin
                            uint32_t step16, uint32_t hi, uint32_t idesc, uint32_t limit, uint32_t debug = 0) {
   static_assert(KSUB == 2 || KSUB == 4, "rounds of two or four k-steps");
   uint32_t status;
-  if constexpr (CG == 2 && KSUB == 2) asm volatile(WB_KR_HEAD("2") WB_KR_BODY2("2", WB_KL_COMMIT2) WB_KR_TAIL("2", WB_KL_COMMIT2) WB_KL_ARGS);
-  if constexpr (CG == 2 && KSUB == 4) asm volatile(WB_KR_HEAD("4") WB_KR_BODY4("2", WB_KL_COMMIT2) WB_KR_TAIL("4", WB_KL_COMMIT2) WB_KL_ARGS);
-  if constexpr (CG == 1 && KSUB == 2) asm volatile(WB_KR_HEAD("2") WB_KR_BODY2("1", WB_KL_COMMIT1) WB_KR_TAIL("2", WB_KL_COMMIT1) WB_KL_ARGS);
-  if constexpr (CG == 1 && KSUB == 4) asm volatile(WB_KR_HEAD("4") WB_KR_BODY4("1", WB_KL_COMMIT1) WB_KR_TAIL("4", WB_KL_COMMIT1) WB_KL_ARGS);
+  if constexpr (CG == 2 && KSUB == 2) asm volatile(WB_KR_HEAD("2") WB_KR_BODY2("2", WB_KL_COMMIT2) WB_KR_END(WB_KL_COMMIT2) WB_KL_ARGS);
+  if constexpr (CG == 2 && KSUB == 4) asm volatile(WB_KR_HEAD("4") WB_KR_BODY4("2", WB_KL_COMMIT2) WB_KR_END(WB_KL_COMMIT2) WB_KL_ARGS);
+  if constexpr (CG == 1 && KSUB == 2) asm volatile(WB_KR_HEAD("2") WB_KR_BODY2("1", WB_KL_COMMIT1) WB_KR_END(WB_KL_COMMIT1) WB_KL_ARGS);
+  if constexpr (CG == 1 && KSUB == 4) asm volatile(WB_KR_HEAD("4") WB_KR_BODY4("1", WB_KL_COMMIT1) WB_KR_END(WB_KL_COMMIT1) WB_KL_ARGS);
   return status;
 }
 
