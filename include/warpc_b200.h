@@ -159,7 +159,9 @@ int wg_plan_set_dependent_launch(void* plan, int on);
  * and 16-21 are times on the GPU nanosecond timer (entry, set-up, first/last load, first/last MMA, accumulator ready,
  * stored, roles done, exit, accumulator free; barriers initialised, tensor memory allocated, first tile found, last
  * stores read, CTAs met, tensor memory freed); 11-14 cycle sums of the first epilogue warp; 15 cycles entry to exit.
- * wg_plan_read_stamps synchronises and returns the words written. */
+ * wg_plan_read_stamps synchronises and returns the words written.  A plan whose kernel is one of the "simple"
+ * instances (whole tiles, one a CTA or a fixed grid, stored from the registers: compiled without the stamps) launches
+ * the full instance of the same tile and store while its stamps are on: same geometry, the timeline of the larger code. */
 int wg_plan_enable_stamps(void* plan, int on);
 int wg_plan_read_stamps(void* plan, unsigned long long* out, size_t cap_words);
 
@@ -202,7 +204,8 @@ int wg_launch_noalloc(int device, const wg_variant* v, int M, int N, int K, cons
 int wg_noalloc_status(int device, unsigned out[4]);
 int wg_noalloc_max_flags(void);
 
-/* Number of compiled kernels and the name of each (for listing). */
+/* Number of compiled kernels and the name of each (for listing): one template, an instance per (CTA group, tile, store
+ * path), and "simple" instances of three tiles that hold nothing but the one-tile / fixed-grid path from the registers. */
 int wg_kernel_count(void);
 const char* wg_kernel_name(int kernel_id);
 

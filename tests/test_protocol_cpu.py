@@ -102,6 +102,49 @@ def test_a_forwarding_slot_overwritten_before_it_is_taken_is_caught():
     assert "forwarding slot" in str(e.value) or "beyond its" in str(e.value) or "parity would alias" in str(e.value)
 
 
+SIMPLE_SHAPES = [(1024, 1024, 512), (1536, 1536, 256), (2048, 2048, 256), (4096, 4096, 128), (1024, 1024, 192)]
+
+
+@pytest.mark.parametrize("shape", SIMPLE_SHAPES)
+def test_ctas_of_a_simple_instance_may_leave_on_their_own(shape):
+    # one tile a CTA or a fixed grid by stride, stored from the registers: no cluster barrier before the exit.  Nothing may
+    # reach a CTA after its own roles are done -- and the same holds, trivially, with the cluster barrier kept
+    v = w.choose(*shape)
+    li = w.realise(v, *shape)
+    assert w.kernel_is_simple(li.kernel_id) and li.sched in (0, 1) and li.direct
+    for seed in range(4):
+        assert protocol.check(v, *shape, seed=seed) > 0                       # the kernel's own way: each CTA on its own
+    assert protocol.check(v, *shape, seed=9, teardown="cluster") > 0
+
+
+def test_a_leader_that_leaves_before_its_accumulator_is_released_is_caught():
+    # what lets the pair's leader go alone is its MMA issuer's last wait, for every accumulator's release: eight arrivals,
+    # four of them from the other CTA.  Without that wait an epilogue warp of the other CTA arrives on a barrier of a CTA
+    # that has left.  Held at a cluster barrier the leader would still be there.
+    shape = (1024, 1024, 256)
+    v = w.choose(*shape)
+    with pytest.raises(protocol.Violation) as e:
+        for seed in range(40):
+            protocol.check(v, *shape, seed=seed, mutate={"mma_no_final_drain": True})
+    assert "has left" in str(e.value)
+    for seed in range(4):
+        assert protocol.check(v, *shape, seed=seed, mutate={"mma_no_final_drain": True}, teardown="cluster") > 0
+
+
+def test_full_instances_keep_the_cluster_barrier():
+    # launch control's last answer is released on the first CTA's barrier by takers of both CTAs, and nobody waits for
+    # that: letting those CTAs go alone is a finding
+    shape = (2048, 4096, 256)
+    v = w.swapped(*shape, 256, 256, 4, clc=True)
+    li = w.realise(v, *shape)
+    assert li.sched == 2 and not w.kernel_is_simple(li.kernel_id)
+    assert protocol.check(v, *shape, seed=1) > 0
+    with pytest.raises(protocol.Violation) as e:
+        for seed in range(20):
+            protocol.check(v, *shape, seed=seed, teardown="cta")
+    assert "has left" in str(e.value)
+
+
 @pytest.mark.parametrize("shape", [(1024, 1024, 1024), (1536, 1536, 1536), (3072, 1280, 2048), (4096, 4096, 1024), (1024, 1024, 65536)],
                          ids=lambda s: "x".join(map(str, s)))
 def test_the_rules_program_for_a_benchmark_shape(shape):

@@ -4,7 +4,7 @@ Host code here is thin: the rule, the launch header and the launch / check / tim
 call the C ABI in ``include/warpc_b200.h`` (``libwarpc_b200.so``, hand-written sm_100a CUDA)
 through ctypes.  There is no CPU fallback: without the shared library every entry raises.
 """
-from .programs import Variant, LaunchInfo, choose, swapped, pair, one, realise, header  # noqa: F401
+from .programs import Variant, LaunchInfo, choose, swapped, pair, one, realise, header, kernel_is_simple  # noqa: F401
 from .plan import Plan, HostPlan, DeviceWaitError  # noqa: F401
 
 __all__ = ["Variant", "LaunchInfo", "choose", "swapped", "pair", "one", "realise", "header", "Plan", "HostPlan",

@@ -52,6 +52,13 @@ def realise(v, m, n, k):
     return li
 
 
+def kernel_is_simple(kernel_id):
+    """Is the compiled kernel with this id one of the "simple" instances (whole tiles, one a CTA or a fixed grid by stride,
+    stored from the registers, nothing else compiled in)?  Their CTAs leave without meeting their pair's other CTA."""
+    name = _lib.lib().wg_kernel_name(kernel_id)
+    return bool(name) and name.decode().endswith("_simple")
+
+
 def header(v, m, n, k):
     """The launch header text (`.kernel/.tmap/.grid/...`, backend/compile.ml:171-186)."""
     buf = ctypes.create_string_buffer(4096)

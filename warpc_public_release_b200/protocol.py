@@ -17,7 +17,12 @@ step.  It reports
   * a k-step of a tile multiplied twice or never, a tile stored twice or added to before it
     was stored (split-K, stream-K),
   * roles that can no longer move (what would be a hang on the GPU), and CTAs that would leave
-    with copies or commits still in flight.
+    with copies or commits still in flight,
+  * anything that reaches a CTA after it has left: an arrival on one of its barriers, a load landing in its ring, an
+    MMA reading its slots or writing its tensor memory, a commit reporting to it.  The kernel's full instances hold
+    both CTAs of a pair at a cluster barrier until every role of both is done; its simple instances (whole tiles, one
+    a CTA or by stride, stored from the registers) let each CTA go when its own roles are done (`teardown="cta"`):
+    every word one CTA sends the other is waited for by a role of the receiving CTA before that role ends.
 
     python -m warpc_public_release_b200.protocol M N K [seed]      # the rule's program for a shape
 """
@@ -67,8 +72,12 @@ class Barrier:
 
 
 class Model:
-    def __init__(self, li, m, n, k, seed=0, mutate=None, replicas=0):
+    def __init__(self, li, m, n, k, seed=0, mutate=None, replicas=0, teardown=None):
         self.li, self.m, self.n, self.k = li, m, n, k
+        # when a CTA leaves: "cluster": when every role of every CTA of its cluster is done (a cluster barrier before
+        # the exit); "cta": when its own roles are done.  Default: what the kernel that `li` names does.
+        self.teardown = teardown or ("cta" if programs.kernel_is_simple(li.kernel_id) else "cluster")
+        self.gone = set()
         # further copies of C (wg_plan_set_replicas): the epilogue hands stored tiles to a forwarding warp
         self.replicas = replicas if (not li.direct and li.sched in (SCHED_ONE, SCHED_STRIDE, SCHED_CLC)) else 0
         self.fwd_slot, self.forwarded, self.peer_stored = {}, defaultdict(int), defaultdict(int)
@@ -212,7 +221,7 @@ class Model:
             acc += 1
             if acc == self.nbuf:
                 acc, acc_use = 0, acc_use + 1
-        for _ in range(self.nbuf):  # every accumulator has been read out in both CTAs before leaving
+        for _ in range(0 if self.mut.get("mma_no_final_drain") else self.nbuf):  # every accumulator has been read out in both CTAs before leaving
             yield ("wait", (cta, "acc_empty", acc), acc_use - 1)
             acc += 1
             if acc == self.nbuf:
@@ -368,6 +377,7 @@ class Model:
             self.nbar[cta, seq].add(warp)
             return len(self.nbar[cta, seq]) == 4
         if kind == "arrive":
+            self.still_here(ev[1][0], "%s arrives on %s" % (role, self.bars[ev[1]].name))
             self.bars[ev[1]].arrive(ev[2])
         elif kind == "flag":
             self.flags[ev[1]] = ev[2]
@@ -378,12 +388,15 @@ class Model:
             self.slots[cta, slot] = ["loading", tile, kstep]
 
             def land(cta=cta, slot=slot, bar=bar):
+                self.still_here(cta, "a load lands in slot %d of CTA %d" % (slot, cta))
+                self.still_here(bar[0], "a load of CTA %d reports its bytes to %s" % (cta, self.bars[bar].name))
                 self.slots[cta, slot][0] = "full"
                 self.bars[bar].complete_tx(self.stage_bytes)
             self.asyncs.append(land)
         elif kind == "mma":
             _, c, acc, ctas, slot, tile, kstep, first = ev
             for x in ctas:
+                self.still_here(x, "cluster %d multiplies k-step %d from CTA %d's ring into its tensor memory" % (c, kstep, x))
                 have = self.slots[x, slot]
                 want_tile = tile - tile % self.cg + x % self.cg
                 if have is None or have[0] != "full" or have[1] != want_tile or have[2] != kstep:
@@ -401,7 +414,9 @@ class Model:
         elif kind == "commit":
             _, cta, bar_keys, freed, acc_key = ev
 
-            def fire(bar_keys=bar_keys, freed=freed, acc_key=acc_key):
+            def fire(bar_keys=bar_keys, freed=freed, acc_key=acc_key, cta=cta):
+                for key in bar_keys:
+                    self.still_here(key[0], "a commit of CTA %d's MMAs reports to %s" % (cta, self.bars[key].name))
                 for x, slot in freed:
                     self.slots[x, slot] = None
                 if acc_key is not None:
@@ -426,6 +441,7 @@ class Model:
             a["readers"] += 1
             if a["readers"] == 4 * self.cg:
                 a["state"] = "read"
+            self.still_here(leader, "CTA %d warp %d releases accumulator %d on the leader's barrier" % (cta, warp, acc))
             self.bars[leader, "acc_empty", acc].arrive(0)
         elif kind == "fwdslot":
             _, cta, s, tile = ev
@@ -463,6 +479,21 @@ class Model:
                     cta, warp, acc, tile, a["state"], a["tile"], a["complete"]))
         return True
 
+    def still_here(self, cta, what):
+        if cta in self.gone:
+            raise Violation("%s, but CTA %d has left" % (what, cta))
+
+    def role_done(self, cta):
+        """A role of `cta` has ended; CTAs whose roles are all done leave (with a cluster barrier before the exit: once the
+        whole cluster's are)."""
+        self.unfinished[cta] -= 1
+        mates = [x for x in range((cta // self.cg) * self.cg, (cta // self.cg + 1) * self.cg) if x in self.unfinished]
+        if self.teardown == "cta":
+            if self.unfinished[cta] == 0:
+                self.gone.add(cta)
+        elif all(self.unfinished[x] == 0 for x in mates):
+            self.gone.update(mates)
+
     def blocks_per_warp(self):
         """32-row blocks of C one epilogue warp handles per tile (Cfg::NBLK in gemm_kernel.cuh)."""
         fold = self.cg == 2 and self.li.tile_n == 64
@@ -476,15 +507,18 @@ class Model:
         started = self.li.grid if self.li.sched != SCHED_CLC else min(self.clusters, RESIDENT_CLUSTERS) * self.cg
         for cta in range(started):
             leader = cta % self.cg == 0
-            roles.append(["CTA %d producer" % cta, self.producer(cta), None])
+            roles.append(["CTA %d producer" % cta, self.producer(cta), None, cta])
             if leader:
-                roles.append(["CTA %d MMA issuer" % cta, self.mma(cta), None])
+                roles.append(["CTA %d MMA issuer" % cta, self.mma(cta), None, cta])
                 if self.li.sched == SCHED_CLC:
-                    roles.append(["CTA %d scheduler" % cta, self.scheduler(cta), None])
+                    roles.append(["CTA %d scheduler" % cta, self.scheduler(cta), None, cta])
             for w in range(4):
-                roles.append(["CTA %d epilogue warp %d" % (cta, w), self.epilogue(cta, w), None])
+                roles.append(["CTA %d epilogue warp %d" % (cta, w), self.epilogue(cta, w), None, cta])
             if self.replicas:
-                roles.append(["CTA %d forwarding warp" % cta, self.forwarder(cta), None])
+                roles.append(["CTA %d forwarding warp" % cta, self.forwarder(cta), None, cta])
+        self.unfinished = defaultdict(int)
+        for role in roles:
+            self.unfinished[role[3]] += 1
         live = list(range(len(roles)))
         while live or self.asyncs or any(self.commit_queue.values()):
             progressed = False
@@ -500,13 +534,14 @@ class Model:
             still = []
             for i in live:
                 role = roles[i]
-                moved = 0
-                while moved < 8:  # a few events at a time, so roles interleave
+                moved, turn = 0, self.rng.randint(1, 8)
+                while moved < turn:  # a few events at a time (one to eight), so roles interleave at every boundary
                     if role[2] is None:
                         try:
                             role[2] = next(role[1])
                         except StopIteration:
                             role[2] = "done"
+                            self.role_done(role[3])
                             break
                     if not self.step(role[0], role[2]):
                         break
@@ -582,11 +617,12 @@ def _ranges(xs):
     return ",".join(out) or "none"
 
 
-def check(variant, m, n, k, seed=0, mutate=None, replicas=0):
+def check(variant, m, n, k, seed=0, mutate=None, replicas=0, teardown=None):
     """Run the model for `variant` on an M x N x K problem; returns the number of events, raises
-    Violation with the first finding.  `replicas` > 0: with further copies of C (wg_plan_set_replicas)."""
+    Violation with the first finding.  `replicas` > 0: with further copies of C (wg_plan_set_replicas).
+    `teardown`: "cluster" or "cta" (see the module text); default: what the kernel the variant runs in does."""
     li = programs.realise(variant, m, n, k)
-    return Model(li, m, n, k, seed=seed, mutate=mutate, replicas=replicas).run()
+    return Model(li, m, n, k, seed=seed, mutate=mutate, replicas=replicas, teardown=teardown).run()
 
 
 def main(argv=None):
