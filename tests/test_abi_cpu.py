@@ -155,6 +155,24 @@ def test_realisation_invariants():
     assert w.choose(2048, 2048, 2048).tile_m == 128 and w.choose(2048, 2048, 2048).retile == 1
 
 
+def test_whole_tile_launches_from_the_registers_run_in_the_simple_instances():
+    name = lambda li: _lib.lib().wg_kernel_name(li.kernel_id).decode()
+    for s, kernel in (((1024, 1024, 1024), "pair_128x64_simple"), ((1536, 1536, 1536), "pair_128x128_simple"),
+                      ((2048, 2048, 2048), "pair_256x128_simple"), ((3072, 1280, 2048), "pair_256x128_simple"),
+                      ((4096, 4096, 1024), "pair_256x128_simple")):
+        li = w.realise(w.choose(*s), *s)
+        assert name(li) == kernel and li.direct == 1 and li.sched in (0, 1) and w.kernel_is_simple(li.kernel_id)
+        assert "# b200 kernel %s:" % kernel in w.header(w.choose(*s), *s) and ".ptr c %d %d 4" % s[:2] in w.header(w.choose(*s), *s)
+    # launch control, K shared between CTAs, the staged store and ragged tiles stay in the full instances
+    for s in ((8192, 8192, 8192), (4096, 4096, 4096), (1024, 1024, 65536), (2048, 2048, 16384)):
+        assert not w.kernel_is_simple(w.realise(w.choose(*s), *s).kernel_id)
+    assert not w.kernel_is_simple(w.realise(w.swapped(2048, 2048, 2048, 256, 128, 6), 2048, 2048, 2048).kernel_id)        # staged
+    assert not w.kernel_is_simple(w.realise(w.swapped(1920, 2048, 512, 256, 128, 6), 1920, 2048, 512).kernel_id)            # 7.5 tiles down
+    # an instance fixes its round: a launch that needs another one runs in the full instance
+    li = w.realise(w.swapped(1024, 1024, 1024, 128, 128, 3, direct=True), 1024, 1024, 1024)
+    assert (li.ksub, w.kernel_is_simple(li.kernel_id)) in ((2, True), (1, False))
+
+
 def test_stream_k_shares_only_the_last_wave_where_the_library_chose_it():
     # 4096^3: 256 pair tiles on 74 resident pairs: two waves walked whole by stride, the third and the remainder dealt out
     li = w.realise(w.choose(4096, 4096, 4096), 4096, 4096, 4096)
