@@ -23,7 +23,9 @@ def main():
     import warpc_public_release_b200 as w
     clc = lambda r, n, k: w.swapped(r, n, k, 256, 256, 4, clc=True, serpentine=True, ask_ahead=True)   # the large shape's program
     stride = lambda r, n, k: w.swapped(r, n, k, 128, 128, 8, bufs=2)                                    # a fixed grid, two accumulators
-    cases = [((1024, 1024, 512), "fused", None, "fused"),          # the rule's program for the slab: staged, one tile a CTA
+    fold = lambda r, n, k: w.swapped(r, n, k, 128, 64, 13)                                              # one tile a CTA, staged store
+    cases = [((1024, 1024, 512), "fused", fold, "fused"),
+             ((1024, 1024, 512), "fused", None, "nccl"),           # the rule's program for the slab stores from the registers
              ((4096, 4096, 1024), "fused", clc, "fused"), ((8192, 2304, 256), "fused", stride, "fused"),
              ((8192, 4096, 1024), "fused", None, "nccl"),          # the rule's program stores from the registers: NCCL in row bands
              ((8192, 4096, 1024), "nccl", clc, "nccl"),

@@ -24,7 +24,7 @@ using namespace wb;
 template <class C>
 wb_kernel_entry entry(int id, const char* name) {
   wb_kernel_entry e;
-  e.id = id, e.cg = C::CG, e.tile_m = C::TM, e.tile_n = C::TN, e.direct = C::DIRECT ? 1 : 0, e.simple = C::SIMPLE ? 1 : 0, e.ksub = C::KSUB;
+  e.id = id, e.cg = C::CG, e.tile_m = C::TM, e.tile_n = C::TN, e.direct = C::DIRECT ? 1 : 0, e.simple = C::SIMPLE ? 1 : 0, e.ksub = C::KSUB, e.mode = C::MODE;
   e.reps = C::REPS, e.epi_rows = C::EPI_ROWS, e.wide_rows = C::WIDE_ROWS, e.ncols = C::NCOLS, e.stage_bytes = C::STAGE_BYTES;
   e.smem_fixed = C::smem_bytes(0);
   e.staging_bytes = C::STAGING_BYTES;
@@ -57,10 +57,15 @@ const wb_kernel_entry* table() {
       entry<Cfg<2, 128, 64, true, 32, 2, true, 4>>(13, "pair_128x64_simple"),
       entry<Cfg<2, 128, 128, true, 32, 2, true, 2>>(14, "pair_128x128_simple"),
       entry<Cfg<2, 256, 128, true, 32, 2, true, 1>>(15, "pair_256x128_simple"),
+      // one scheduling mode each, for the three long programs the rule names: stream-K on 256 x 128 tiles, launch control
+      // and split-K over the grid on 256 x 256 tiles (staged store; phase stamps and further copies of C as in the full ones)
+      entry<Cfg<2, 256, 128, false, 32, 2, false, 0, SCHED_STREAMK>>(16, "pair_256x128_staged_stream_k"),
+      entry<Cfg<2, 256, 256, false, 32, 2, false, 0, SCHED_CLC>>(17, "pair_256x256_staged_launch_control"),
+      entry<Cfg<2, 256, 256, false, 32, 2, false, 0, SCHED_SPLITK>>(18, "pair_256x256_staged_split_k"),
   };
   return t;
 }
-constexpr int kKernels = 16;
+constexpr int kKernels = 19;
 
 // ------------------------------------------------------------------ driver entry points
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -341,10 +346,11 @@ int host_run_blocks(Plan* pl, const void* hA, const void* hBt, void* hC) {
 
 }  // namespace
 
-const wb_kernel_entry* wb_find_kernel(int cg, int tile_m, int tile_n, int direct, int simple) {
+const wb_kernel_entry* wb_find_kernel(int cg, int tile_m, int tile_n, int direct, int simple, int mode) {
   const wb_kernel_entry* t = table();
   for (int i = 0; i < kKernels; ++i)
-    if (t[i].cg == cg && t[i].tile_m == tile_m && t[i].tile_n == tile_n && t[i].direct == direct && t[i].simple == simple) return &t[i];
+    if (t[i].cg == cg && t[i].tile_m == tile_m && t[i].tile_n == tile_n && t[i].direct == direct && t[i].simple == simple && t[i].mode == mode)
+      return &t[i];
   return nullptr;
 }
 const wb_kernel_entry* wb_kernel_at(int id) { return (id >= 0 && id < kKernels) ? &table()[id] : nullptr; }
@@ -439,7 +445,7 @@ extern "C" int wg_launch(void* plan, void* cuda_stream) {
   // a simple instance takes no phase stamps: a plan asked for them launches the full instance of the same tile and store
   const wb_kernel_entry* k = pl->k;
   if (k->simple && pl->p.stamps != nullptr && !kSimpleStamps) {
-    k = wb_find_kernel(k->cg, k->tile_m, k->tile_n, k->direct, 0);
+    k = wb_find_kernel(k->cg, k->tile_m, k->tile_n, k->direct, 0, -1);
     if (!k) return WG_E_NOKERNEL;
     WG_CUDA(cudaFuncSetAttribute(k->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem));
   }

@@ -89,7 +89,7 @@ constexpr bool kSimpleStamps = false;
 #define WB_DEBUG_WORD(p) 0u
 #endif
 
-template <int CG_, int TM_, int TN_, bool DIRECT_, int EPI_ROWS_ = 32, int EPI_COPIES_ = 2, bool SIMPLE_ = false, int KSUB_ = 0>
+template <int CG_, int TM_, int TN_, bool DIRECT_, int EPI_ROWS_ = 32, int EPI_COPIES_ = 2, bool SIMPLE_ = false, int KSUB_ = 0, int MODE_ = -1>
 struct Cfg {
   static constexpr int CG = CG_, TM = TM_, TN = TN_, TK = 64;
   static constexpr bool DIRECT = DIRECT_;
@@ -98,6 +98,11 @@ struct Cfg {
   // these, and the code they never run is not in their kernel.
   static constexpr bool SIMPLE = SIMPLE_;
   static constexpr int KSUB = KSUB_;  // k-steps a ring round, fixed at compile time (0: the launch says)
+  // the one scheduling mode (SCHED_*) the instance is compiled for, or -1: the launch says.  An instance of one mode holds
+  // no other mode's code (the walker's, the scheduler warp's, the epilogue's hand-offs), and none for further copies of C
+  // where that mode cannot have them.
+  static constexpr int MODE = MODE_;
+  static constexpr bool REPLICAS = !DIRECT_ && !SIMPLE_ && (MODE_ < 0 || MODE_ <= 2);
   static_assert(!SIMPLE || DIRECT, "the simple instances store from the registers");
   static constexpr bool FOLD = (CG == 2 && TN == 64);  // M = 128 pair: 64 accumulator rows a CTA
   static constexpr int REPS = (TN == 256) ? 2 : 1;    // stacked MMA atoms
@@ -242,6 +247,19 @@ WB_DEV bool wait_flag(const KParams& p, uint32_t abort_addr, const uint32_t* fla
   }
 }
 
+// The launch's scheduling mode and its number of further copies of C, as the instance sees them: constants where the
+// instance is compiled for one mode, so the other modes' branches fold away.
+template <class C>
+WB_DEV int sched_of(const KParams& p) {
+  if constexpr (C::MODE >= 0) return C::MODE;
+  else return p.sched;
+}
+template <class C>
+WB_DEV int nrep_of(const KParams& p) {
+  if constexpr (C::REPLICAS) return p.nrep;
+  else return 0;
+}
+
 // One unit of work for a role: an output tile and the k-steps [kb, ke) of it.
 struct Work {
   int tile, kb, ke;
@@ -267,7 +285,7 @@ struct Walker {
   // WARP: called by a whole converged warp, else by one lane running its role alone
   template <bool WARP = true>
   WB_DEV bool next(Work& w) {
-    const int sched = p.sched;
+    const int sched = sched_of<C>(p);
     if (!started) {
       started = true;
       tile = blockIdx.x;
@@ -332,7 +350,7 @@ struct Walker {
   // `w` (the unit next() gave last) is known to be this CTA's final one.  Cluster launch
   // control only learns that from the answer after it, so it never says yes.
   WB_DEV bool is_last(const Work& w) const {
-    const int sched = p.sched;
+    const int sched = sched_of<C>(p);
     if (sched == SCHED_ONE || sched == SCHED_SPLITK) return true;
     if (C::SIMPLE || sched == SCHED_STRIDE) return w.tile + int(gridDim.x) >= p.ntiles;
     if (sched == SCHED_STREAMK) return whole_tiles ? dp_tile >= p.sk_dp : (seg == t_first && p.sk_dp == 0);
@@ -779,7 +797,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   } else if (warp == 2) {
     // ===== scheduler (cluster launch control): the cluster's first CTA asks for one more
     // cluster's tiles at a time and hands the answer to every taker of both CTAs
-    if (!C::SIMPLE && p.sched == SCHED_CLC && leader) {
+    if (!C::SIMPLE && sched_of<C>(p) == SCHED_CLC && leader) {
       const uint32_t clc_bar = ctrl_at(offsetof(Ctrl, clc_bar)), answer = ctrl_at(offsetof(Ctrl, clc_answer));
       const uint32_t sched_empty = ctrl_at(offsetof(Ctrl, sched_empty));
       uint32_t pf = 0, pe = 0;
@@ -812,7 +830,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   } else if (warp == 3) {
     // ===== forwarding warp (a replicated C): tiles the epilogue has stored, on to the other GPUs' copies
     if constexpr (!C::DIRECT) {
-      if (p.nrep > 0) {
+      if (nrep_of<C>(p) > 0) {
         for (uint32_t taken = 0;; ++taken) {
           const uint32_t s = taken & 1u, phase = (taken >> 1) & 1u;
           if (!wait_bar(p, abort_addr, ctrl_at(offsetof(Ctrl, fwd_full) + 8 * s), phase, ST_WAIT_FULL, 0x300u + s)) break;
@@ -838,16 +856,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     // K split between CTAs (split-K over the grid, stream-K): hand-off words count launches,
     // never reset: every CTA's own word holds how many launches have gone by, so one past it
     // is the value all flags of this launch reach (gemm_swapped.ml:608-626)
-    const bool shared_k = !C::DIRECT && (p.sched == SCHED_SPLITK || p.sched == SCHED_STREAMK);
+    const bool shared_k = !C::DIRECT && (sched_of<C>(p) == SCHED_SPLITK || sched_of<C>(p) == SCHED_STREAMK);
     // the same sharing through a workspace (store from the registers): split-K counts launches in the CTA's word like
     // the L2 form; stream-K raises the word to 1 and the CTA that takes the partial sum puts it back to 0
-    const bool ws_k = C::DIRECT && !C::SIMPLE && (p.sched == SCHED_SPLITK || p.sched == SCHED_STREAMK);
+    const bool ws_k = C::DIRECT && !C::SIMPLE && (sched_of<C>(p) == SCHED_SPLITK || sched_of<C>(p) == SCHED_STREAMK);
     float* ws_slot = ws_k ? p.ws + size_t(blockIdx.x) * size_t(C::TM * C::TN) : nullptr;
     uint32_t target = 0;
-    if (ws_k && p.sched == SCHED_SPLITK) target = ld_relaxed_gpu(p.flags + blockIdx.x) + 1u;
+    if (ws_k && sched_of<C>(p) == SCHED_SPLITK) target = ld_relaxed_gpu(p.flags + blockIdx.x) + 1u;
     if (shared_k) {
       target = ld_relaxed_gpu(p.flags + blockIdx.x) + 1u;
-      if (p.sched == SCHED_STREAMK) {
+      if (sched_of<C>(p) == SCHED_STREAMK) {
         named_bar_sync(2, 128);  // every epilogue thread has read the word before it moves on
         if (first_warp && lane == 0) st_relaxed_gpu(p.flags + blockIdx.x, target);
       }
@@ -858,7 +876,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       const uint32_t tbase = tmem_base + uint32_t(acc * C::NCOLS) + (uint32_t(q * 32) << 16);
       const uint32_t acc_empty_addr = acc_empty_leader + 8u * uint32_t(acc);
       if constexpr (C::DIRECT) {
-        if (ws_k && p.sched == SCHED_SPLITK) {
+        if (ws_k && sched_of<C>(p) == SCHED_SPLITK) {
           // ---- split-K through the workspace (gemm_swapped.ml:737-791): every run leaves the blocks it does not sum up
           // itself in its slot and raises its flag; once the tile's other runs' flags are up it adds their parts of its
           // own blocks, in run order, and stores them.  No warp leaves this block early: all four meet at the barriers.
@@ -912,16 +930,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           if (first_warp && lane == 0) stamp(p, EV_ACC_READY, nth);
           epi_direct_tile<C>(p, tbase, row, col, q, lane, acc_empty_addr);
         }
-      } else if (!shared_k || (p.sched == SCHED_STREAMK && w.kb == 0 && w.ke == p.kt)) {
+      } else if (!shared_k || (sched_of<C>(p) == SCHED_STREAMK && w.kb == 0 && w.ke == p.kt)) {
         // (a tile one cluster computes whole has no other part to wait for or to tell: stored like any tile)
         if (!wait_bar(p, abort_addr, acc_full_bar(acc), acc_phase, ST_WAIT_ACC_FULL, uint32_t(acc))) break;
         tc_fence_after();
         if (first_warp && lane == 0) stamp(p, EV_ACC_READY, nth);
         // timing runs: the first warp's cycles in each part of the tile's store, events 11-14
         unsigned long long* prof = (!C::SIMPLE && p.stamps != nullptr && first_warp && nth < 4) ? p.stamps + (size_t(blockIdx.x) * 64 + 11) * 4 + nth : nullptr;
-        epi_staged_tile<C>(&map_c, &map_cw, tbase, my_staging, row, col, q, lane, false, acc_empty_addr, store_policy, wide, prof, p.replicas, p.nrep);
-        if (p.nrep > 0 && wide == 0u) ok = fwd_hand_over(p, abort_addr, ctrl, handed, row, col, first_warp, lane);
-      } else if (p.sched == SCHED_SPLITK) {
+        epi_staged_tile<C>(&map_c, &map_cw, tbase, my_staging, row, col, q, lane, false, acc_empty_addr, store_policy, wide, prof, p.replicas, nrep_of<C>(p));
+        if (nrep_of<C>(p) > 0 && wide == 0u) ok = fwd_hand_over(p, abort_addr, ctrl, handed, row, col, first_warp, lane);
+      } else if (sched_of<C>(p) == SCHED_SPLITK) {
         // ---- split-K over the grid, adding in the L2 (gemm_swapped.ml:660-710).  The S runs
         // of a tile first zero disjoint shares of it (while their k loops run), raise their
         // flags, and once all S flags are up each adds its whole accumulator to C.
@@ -995,7 +1013,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       ++nth;
     }
     if constexpr (!C::DIRECT) {
-      if (p.nrep > 0) fwd_hand_over(p, abort_addr, ctrl, handed, -1, 0, first_warp, lane);  // the forwarding warp may leave
+      if (nrep_of<C>(p) > 0) fwd_hand_over(p, abort_addr, ctrl, handed, -1, 0, first_warp, lane);  // the forwarding warp may leave
       // this warp is done with its partner CTA (its last word there was the accumulator's
       // release): it says so before waiting for its own stores, not after
       if (CG == 2 && ld_shared_u32(abort_addr) == 0u) {

@@ -8,6 +8,7 @@ struct wb_kernel_entry {
   int cg, tile_m, tile_n, direct;
   int simple;          // whole tiles, one a CTA or by stride, stored from the registers: the kernel holds no other path
   int ksub;            // k-steps a ring round when the instance fixes it (0: a launch parameter)
+  int mode;            // the one scheduling mode the instance is compiled for (-1: a launch parameter)
   int reps;            // stacked MMA atoms a CTA (2 for 256-column tiles)
   int epi_rows;        // C rows per epilogue block (the C tensor map's box rows)
   int wide_rows;       // C rows per store of a CTA's last tile, staged whole in the drained ring
@@ -19,6 +20,6 @@ struct wb_kernel_entry {
   const void* fn;      // the __global__ function
 };
 
-const wb_kernel_entry* wb_find_kernel(int cg, int tile_m, int tile_n, int direct, int simple);
+const wb_kernel_entry* wb_find_kernel(int cg, int tile_m, int tile_n, int direct, int simple, int mode);
 const wb_kernel_entry* wb_kernel_at(int id);
 int wb_kernel_total();

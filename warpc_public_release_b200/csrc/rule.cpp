@@ -338,8 +338,10 @@ extern "C" int wg_realise(const wg_variant* v, int M, int N, int K, wg_launch_in
   // every role's first pass through its code is a visible part of the time: measured, full -> simple instance,
   // 1024^3 9.6 -> 8.5 us, 1536^3 12.3 -> 11.5, 2048^3 17.8 -> 16.9, 4096x4096x1024 31.8 -> 30.3.
   const wb_kernel_entry* e = nullptr;
-  if (li.direct && li.sched <= 1 && M % li.tile_m == 0 && N % li.tile_n == 0) e = wb_find_kernel(li.cg, li.tile_m, li.tile_n, 1, 1);
-  if (!e) e = wb_find_kernel(li.cg, li.tile_m, li.tile_n, li.direct, 0);
+  if (li.direct && li.sched <= 1 && M % li.tile_m == 0 && N % li.tile_n == 0) e = wb_find_kernel(li.cg, li.tile_m, li.tile_n, 1, 1, -1);
+  // ... and the long programs in the instance compiled for their one scheduling mode, where there is one
+  if (!e && !getenv("WARPC_NO_MODE")) e = wb_find_kernel(li.cg, li.tile_m, li.tile_n, li.direct, 0, li.sched);
+  if (!e) e = wb_find_kernel(li.cg, li.tile_m, li.tile_n, li.direct, 0, -1);
   if (!e) return WG_E_NOKERNEL;
   li.kernel_id = e->id;
   li.epi_rows = e->epi_rows;
@@ -380,7 +382,7 @@ extern "C" int wg_realise(const wg_variant* v, int M, int N, int K, wg_launch_in
   while (li.ksub > 1 && li.depth / li.ksub < 2) li.ksub /= 2;
   if (e->simple && e->ksub != 0 && e->ksub != li.ksub) {
     // the simple instance fixes its round at compile time: another round runs in the full instance of the same tile
-    e = wb_find_kernel(li.cg, li.tile_m, li.tile_n, li.direct, 0);
+    e = wb_find_kernel(li.cg, li.tile_m, li.tile_n, li.direct, 0, -1);
     if (!e) return WG_E_NOKERNEL;
     li.kernel_id = e->id;
   }
