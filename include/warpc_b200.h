@@ -205,7 +205,8 @@ int wg_noalloc_status(int device, unsigned out[4]);
 int wg_noalloc_max_flags(void);
 
 /* Number of compiled kernels and the name of each (for listing): one template, an instance per (CTA group, tile, store
- * path), and "simple" instances of three tiles that hold nothing but the one-tile / fixed-grid path from the registers. */
+ * path), "simple" instances of three tiles that hold nothing but the one-tile / fixed-grid path from the registers, and
+ * three instances compiled for one scheduling mode each (stream-K, launch control, split-K over the grid). */
 int wg_kernel_count(void);
 const char* wg_kernel_name(int kernel_id);
 

@@ -168,6 +168,11 @@ def test_whole_tile_launches_from_the_registers_run_in_the_simple_instances():
         assert not w.kernel_is_simple(w.realise(w.choose(*s), *s).kernel_id)
     assert not w.kernel_is_simple(w.realise(w.swapped(2048, 2048, 2048, 256, 128, 6), 2048, 2048, 2048).kernel_id)        # staged
     assert not w.kernel_is_simple(w.realise(w.swapped(1920, 2048, 512, 256, 128, 6), 1920, 2048, 512).kernel_id)            # 7.5 tiles down
+    # the rule's long programs run in the instance compiled for their one scheduling mode
+    for s, kernel in (((4096, 4096, 4096), "pair_256x128_staged_stream_k"), ((2048, 2048, 16384), "pair_256x128_staged_stream_k"),
+                      ((8192, 8192, 8192), "pair_256x256_staged_launch_control"), ((1024, 1024, 65536), "pair_256x256_staged_split_k")):
+        assert name(w.realise(w.choose(*s), *s)) == kernel
+    assert name(w.realise(w.swapped(4096, 4096, 1024, 256, 128, 6, clc=True), 4096, 4096, 1024)) == "pair_256x128_staged"   # no such instance
     # an instance fixes its round: a launch that needs another one runs in the full instance
     li = w.realise(w.swapped(1024, 1024, 1024, 128, 128, 3, direct=True), 1024, 1024, 1024)
     assert (li.ksub, w.kernel_is_simple(li.kernel_id)) in ((2, True), (1, False))

@@ -339,8 +339,11 @@ extern "C" int wg_realise(const wg_variant* v, int M, int N, int K, wg_launch_in
   // 1024^3 9.6 -> 8.5 us, 1536^3 12.3 -> 11.5, 2048^3 17.8 -> 16.9, 4096x4096x1024 31.8 -> 30.3.
   const wb_kernel_entry* e = nullptr;
   if (li.direct && li.sched <= 1 && M % li.tile_m == 0 && N % li.tile_n == 0) e = wb_find_kernel(li.cg, li.tile_m, li.tile_n, 1, 1, -1);
-  // ... and the long programs in the instance compiled for their one scheduling mode, where there is one
-  if (!e && !getenv("WARPC_NO_MODE")) e = wb_find_kernel(li.cg, li.tile_m, li.tile_n, li.direct, 0, li.sched);
+  // ... and the long programs in the instance compiled for their one scheduling mode, where there is one (52-89 KB of code
+  // against 135-173).  Measured against the full instance of the same tile, call by call in one process, same bits:
+  // 4096^3 81.6 against 82.5 us, 8192x2048x4096 83.7 / 84.6, 2048x2048x16384 87.6 / 87.9, 1024x1024x65536 84.6 / 87.3,
+  // 8192^3 692 / 694.
+  if (!e) e = wb_find_kernel(li.cg, li.tile_m, li.tile_n, li.direct, 0, li.sched);
   if (!e) e = wb_find_kernel(li.cg, li.tile_m, li.tile_n, li.direct, 0, -1);
   if (!e) return WG_E_NOKERNEL;
   li.kernel_id = e->id;
