@@ -511,25 +511,43 @@ WB_DEV void fwd_copy_tile(const KParams& p, int row, int col, uint32_t lane) {
 template <class C>
 WB_DEV void epi_direct_tile(const KParams& p, uint32_t tbase, int row, int col, int q, uint32_t lane, uint32_t acc_empty_addr) {
   uint32_t v[2][C::EPI_ROWS];
-  epi_load<C>(tbase, 0, v[0]);
-#pragma unroll
-  for (int i = 0; i < C::NBLK; ++i) {
-    tmem_wait_ld();
-    if (i + 1 < C::NBLK) {
-      epi_load<C>(tbase, i + 1, v[(i + 1) & 1]);
-    } else {
-      tc_fence_before();
-      __syncwarp();
-      if constexpr (C::CG == 2) mbar_arrive_cluster_if(lane == 0 ? 1u : 0u, acc_empty_addr);
-      else mbar_arrive_if(lane == 0 ? 1u : 0u, acc_empty_addr);
-    }
+  const size_t ld = size_t(p.ldc);
+  // whole tiles only (the host refuses the store from the registers otherwise): no bounds to test
+  auto store = [&](int i, const uint32_t* regs) {
     int y, x;
     epi_coords<C>(row, col, q, i, y, x);
-    float* dst = p.C + size_t(y) * size_t(p.ldc) + size_t(x) + lane;
-    // whole tiles only (the host refuses the store from the registers otherwise): no bounds to test
-    const size_t ld = size_t(p.ldc);
+    float* dst = p.C + size_t(y) * ld + size_t(x) + lane;
 #pragma unroll
-    for (int j = 0; j < C::EPI_ROWS; ++j) dst[size_t(j) * ld] = __uint_as_float(v[i & 1][j]);
+    for (int j = 0; j < C::EPI_ROWS; ++j) dst[size_t(j) * ld] = __uint_as_float(regs[j]);
+  };
+  auto release = [&]() {
+    tc_fence_before();
+    __syncwarp();
+    if constexpr (C::CG == 2) mbar_arrive_cluster_if(lane == 0 ? 1u : 0u, acc_empty_addr);
+    else mbar_arrive_if(lane == 0 ? 1u : 0u, acc_empty_addr);
+  };
+  epi_load<C>(tbase, 0, v[0]);
+  if constexpr (C::NBLK % 2 == 0) {
+    // two blocks a turn of a loop that is not unrolled (the two register sets alternate): an eight-block tile's store is a
+    // quarter of the code, which a launch of one tile a CTA runs exactly once, cold
+#pragma unroll 1
+    for (int i = 0; i < C::NBLK; i += 2) {
+      tmem_wait_ld();
+      epi_load<C>(tbase, i + 1, v[1]);
+      store(i, v[0]);
+      tmem_wait_ld();
+      if (i + 2 < C::NBLK) epi_load<C>(tbase, i + 2, v[0]);
+      else release();
+      store(i + 1, v[1]);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < C::NBLK; ++i) {
+      tmem_wait_ld();
+      if (i + 1 < C::NBLK) epi_load<C>(tbase, i + 1, v[(i + 1) & 1]);
+      else release();
+      store(i, v[i & 1]);
+    }
   }
 }
 
