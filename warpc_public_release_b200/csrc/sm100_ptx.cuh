@@ -450,7 +450,7 @@ WB_DEV void umma_commit_if(uint32_t issuer, uint32_t bar, uint16_t mask) {
 // the second, the count and a non-blocking probe of the next stage's barrier (its answer is back before the loop comes
 // round) after the third; only the loop's branch sits between the last MMA of one k-step and the first of the next.
 // Measured, the placement of the bookkeeping does not matter (nor do twelve more dependent ALU instructions a k-step):
-// the pace is the tensor pipe's with operands from shared memory, about 143 cycles an N = 256 MMA in the kernel.
+// the pace is the tensor pipe's with operands from shared memory, about 75 ns (135 cycles) an N = 256 MMA in the kernel.
 #define WB_KL_HEAD                                                                                   \
   "{\n\t.reg .pred e, ec, p, q, w, pa, pt, c, pr, pv;\n\t"                                           \
   ".reg .b32 n, fb, eb, s16, ta, tb, d1, a1, ma, mb, dbg, pb;\n\t"                                   \
@@ -624,7 +624,7 @@ WB_DEV uint32_t load_k_loop(uint32_t issuer, uint32_t& kleft, uint32_t depth, ui
   COMMIT                                                                                             \
   "}"
 // A whole round.  An M = 256 pair MMA narrower than N = 256 takes the tensor pipe about 76 cycles whatever its N
-// (stand-alone loop; 84-105 in the kernel).  The round's bookkeeping is dealt out over the gaps between its MMAs: the
+// (stand-alone loop; 79-97 in the kernel).  The round's bookkeeping is dealt out over the gaps between its MMAs: the
 // lagged commit of the round before after the first MMA; then, a few instructions a gap, the ring moved on (index,
 // parity, the round's own empty barrier kept for the next commit, the next round's barriers and descriptor offset), the
 // count, the probe of the next round's full barrier, and the next round's descriptors; nothing but the branch after the
