@@ -365,6 +365,38 @@ def test_phase_stamps_layout_and_order():
     plan.close()
 
 
+@pytest.mark.parametrize("shape", [(1024, 1024, 512), (1536, 1536, 320), (2048, 2048, 256), (4096, 4096, 128), (4608, 4096, 192)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_simple_instance_and_its_full_twin_give_the_same_bits(shape):
+    """The rule's whole-tile launches from the registers run in a simple instance of their tile; with phase stamps on, the
+    same plan launches the full instance.  Same geometry, same parameters: the products must be the same bits, and exact."""
+    m, n, k = shape
+    v = w.choose(m, n, k)
+    li = w.realise(v, m, n, k)
+    assert w.kernel_is_simple(li.kernel_id) and li.sched in (0, 1)
+    a, bt = gemm_ref.inputs_integers(m, n, k)
+    da, db = torch.from_numpy(a).cuda(), torch.from_numpy(bt).cuda()
+    dc = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+    plan = w.Plan(v, m, n, k, da.data_ptr(), db.data_ptr(), dc.data_ptr())
+    plan.launch()
+    plan.status()
+    simple = dc.cpu().numpy().copy()
+    dc.fill_(float("nan"))
+    plan.enable_stamps(True)
+    plan.launch()
+    st = plan.read_stamps()
+    plan.enable_stamps(False)
+    plan.status()
+    full = dc.cpu().numpy().copy()
+    assert st.any(), "the launch with stamps on wrote no stamps: it did not run in the full instance"
+    dc.fill_(float("nan"))
+    plan.launch()                                  # and back in the simple instance
+    plan.status()
+    assert np.array_equal(simple, gemm_ref.gemm_ref(a, bt))
+    assert np.array_equal(simple, full) and np.array_equal(simple, dc.cpu().numpy())
+    plan.close()
+
+
 def test_one_thread_two_devices_and_replicated_c():
     """Two GPUs (skipped with fewer).  (1) One host thread drives a plan on each device in turn, the current device
     left where the caller had it.  (2) Two ranks under NCCL: ShardedGemm with a replicated C; every rank's gathered C
