@@ -54,10 +54,17 @@ def test_slab_rows_and_programs():
         shard.slab_rows(1000, 3, 0)
     covered = sorted(shard.slab_rows(16384, 4, r) for r in range(4))
     assert covered[0][0] == 0 and covered[-1][1] == 16384 and all(covered[i][1] == covered[i + 1][0] for i in range(3))
-    # every slab of the sharded shape keeps the large-shape program; the rule alone would drop to 192 x 128 at 8 GPUs
-    for g in (1, 2, 4, 8):
+    # the slabs of the sharded shape keep the large-shape program while their 512 x 256 pair tiles fill the last wave of the
+    # 74 resident pairs (13.8 and 6.9 waves on 2 and 4 GPUs); at 8 GPUs (3.46 waves) the rule's own program, re-tiled, runs
+    for g in (1, 2, 4):
         v = shard.slab_variant(16384 // g, 16384, 16384)
         assert (v.tile_m, v.tile_n, v.depth, v.clc, v.serpentine) == (256, 256, 4, 1, 1)
+    import warpc_public_release_b200 as w
+    v = shard.slab_variant(2048, 16384, 16384)
+    li = w.realise(v, 2048, 16384, 16384)
+    assert (v.tile_m, v.tile_n) == (192, 128) and (li.tile_m, li.tile_n, li.sched, li.direct) == (256, 128, 1, 1)
+    v = shard.slab_variant(2048, 16384, 16384, staged=True)          # the kernel is to fill other GPUs' copies of C too
+    assert (v.tile_m, v.tile_n, v.clc) == (256, 256, 1)
     v = shard.slab_variant(2048, 16384, 16384, pin_large=False)
     assert (v.tile_m, v.tile_n) == (192, 128)
     v = shard.slab_variant(1024, 1024, 1024)

@@ -8,6 +8,8 @@ NVLink.  The reference has no multi-GPU path (its harness opens device 0 only,
 backend/node/cuda.py:105-114); the per-GPU program is what its rule picks for the slab's shape
 (backend/programs.ml:46-80), or the 256 x 256 program pinned when the slab keeps whole tiles.
 """
+import os
+
 from . import programs
 
 
@@ -19,16 +21,26 @@ def slab_rows(m, world, rank):
     return rank * rows, (rank + 1) * rows
 
 
-def slab_variant(m_local, n, k, pin_large=True):
+RESIDENT_PAIRS = 74   # CTA pairs the machine holds at one CTA an SM
+
+
+def slab_variant(m_local, n, k, pin_large=True, staged=False):
     """The program for one GPU's (M/g) x N x K share.  The rule falls back to 192 x 128 tiles
     once min(M/g, N, K) < 8192; a slab that still holds whole 256 x 256 pair tiles keeps the
-    large-shape program (cluster launch control, serpentine walk, asking ahead).  (Dealing a poorly
-    filled last wave's k-steps out stream-K does not pay at this tile: 2048 x 16384 x 16384, 3.46 waves,
-    measured 965 us against 757 us -- the partial tiles' 256 KB stores are exposed and clusters stop
-    sharing operand panels in step.)"""
+    large-shape program (cluster launch control, serpentine walk, asking ahead) -- as long as its
+    512 x 256 pair tiles fill their last wave of the 74 resident pairs: 16384^3 over 2 and 4 GPUs is 13.8 and 6.9
+    waves, over 8 GPUs 3.46, a seventh of the machine idle at the end.  There the rule's own program, re-tiled to
+    256 x 128 on a fixed grid (6.9 waves again), is the faster one: 2048 x 16384 x 16384 on one GPU, twenty launches
+    back to back, 721-870 us against 762-984 (cuBLASLt 727-854).  (Dealing the poorly filled last wave's k-steps out
+    stream-K does not pay at the large tile: 965 us against 757 -- the partial tiles' 256 KB stores are exposed and
+    clusters stop sharing operand panels in step.)  `staged`: the caller needs a program that stores through staging
+    copies (further copies of C filled by the kernel itself), which the re-tiled one does not: the large program then."""
     if pin_large and m_local % 256 == 0 and n % 512 == 0 and k % 64 == 0 and min(n, k) >= 8192 and \
             (m_local // 256) * (n // 256) >= 148:
-        return programs.swapped(m_local, n, k, 256, 256, 4, clc=True, ask_ahead=True, serpentine=True)
+        pairs = (m_local // 256) * (n // 256) // 2
+        waves = -(-pairs // RESIDENT_PAIRS)
+        if staged or 20 * pairs >= 19 * waves * RESIDENT_PAIRS:     # the last wave at least 95 % full
+            return programs.swapped(m_local, n, k, 256, 256, 4, clc=True, ask_ahead=True, serpentine=True)
     return programs.choose(m_local, n, k)
 
 
@@ -80,14 +92,16 @@ class ShardedGemm:
         else:
             self.c_full = None
             self.c_local = torch.empty((rows, n), dtype=torch.float32, device=device)
-        self.variant = variant if variant is not None else slab_variant(rows, n, k, pin_large)   # `variant`: a program named by the caller for the slab's shape
+        # `variant`: a program named by the caller for the slab's shape; else the slab's own (with a replicated C one the
+        # kernel itself can send on: stored through staging copies)
+        fusable = replicate_c and world > 1 and (how or os.environ.get("WARPC_REPLICATE", "fused")) == "fused"
+        self.variant = variant if variant is not None else slab_variant(rows, n, k, pin_large, staged=fusable)
         dev_index = device.index or 0
         self.plan = Plan(self.variant, rows, n, k, a_local.data_ptr(), bt.data_ptr(), self.c_local.data_ptr(), device=dev_index)
         self._keep = (a_local, bt)
         self.band_plans, self._pending = [], []
         self.how = None
         if replicate_c and world > 1 and device.type == "cuda":
-            import os
             want = how or os.environ.get("WARPC_REPLICATE", "fused")
             self.how = "fused" if want == "fused" and self._open_peers() else "nccl"
         if self.how == "nccl":
