@@ -674,6 +674,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       if constexpr (!C::DIRECT) prefetch_tmap(&map_c), prefetch_tmap(&map_cw);
     }
     fence_mbar_init();
+    __threadfence_block();  // the abort word, for this CTA's own warps (the arrival at the barrier below is a relaxed one)
     if (lane == 0) stamp(p, 16, 0);
   }
   if (warp == 1) {
@@ -692,7 +693,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   if (threadIdx.x == 0) stamp(p, 18, 0);
   tc_fence_before();
   if constexpr (CG == 2) {
-    cluster_arrive();
+    // What one CTA needs to see of the other's set-up is its barriers' initialisation, which warp 3 has fenced
+    // (fence.mbarrier_init.release.cluster) before this arrival; within the CTA, the tensor-memory base is ordered by the
+    // tcgen05 fences either side and the abort word by warp 3's CTA-scope fence.  The arrival itself orders nothing
+    // more: a releasing one put the pair's meeting at 1.06 us after entry, this one at 0.80.
+    cluster_arrive_relaxed();
     cluster_wait();
   } else {
     __syncthreads();
