@@ -412,7 +412,7 @@ WB_DEV void epi_staged_tile(const CUtensorMap* map_c, const CUtensorMap* map_cw,
     } else {
       tc_fence_before();
       __syncwarp();
-      if constexpr (C::CG == 2) mbar_arrive_cluster_if(lane == 0 ? 1u : 0u, acc_empty_addr);
+      if constexpr (C::CG == 2) mbar_arrive_cluster_relaxed_if(lane == 0 ? 1u : 0u, acc_empty_addr);
       else mbar_arrive_if(lane == 0 ? 1u : 0u, acc_empty_addr);
     }
     if (prof) t_issue += clock64() - t0;
@@ -523,7 +523,7 @@ WB_DEV void epi_direct_tile(const KParams& p, uint32_t tbase, int row, int col, 
   auto release = [&]() {
     tc_fence_before();
     __syncwarp();
-    if constexpr (C::CG == 2) mbar_arrive_cluster_if(lane == 0 ? 1u : 0u, acc_empty_addr);
+    if constexpr (C::CG == 2) mbar_arrive_cluster_relaxed_if(lane == 0 ? 1u : 0u, acc_empty_addr);
     else mbar_arrive_if(lane == 0 ? 1u : 0u, acc_empty_addr);
   };
   epi_load<C>(tbase, 0, v[0]);
@@ -604,7 +604,7 @@ WB_DEV void epi_ws_sum(const KParams& p, uint32_t tbase, int row, int col, int q
   }
   tc_fence_before();
   __syncwarp();
-  if constexpr (C::CG == 2) mbar_arrive_cluster_if(lane == 0 ? 1u : 0u, acc_empty_addr);
+  if constexpr (C::CG == 2) mbar_arrive_cluster_relaxed_if(lane == 0 ? 1u : 0u, acc_empty_addr);
   else mbar_arrive_if(lane == 0 ? 1u : 0u, acc_empty_addr);
 }
 
@@ -929,7 +929,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             epi_ws_put<C>(ws_slot, tbase, q, lane, 1, 0);
             tc_fence_before();
             __syncwarp();
-            if constexpr (CG == 2) mbar_arrive_cluster_if(lane == 0 ? 1u : 0u, acc_empty_addr);
+            if constexpr (CG == 2) mbar_arrive_cluster_relaxed_if(lane == 0 ? 1u : 0u, acc_empty_addr);
             else mbar_arrive_if(lane == 0 ? 1u : 0u, acc_empty_addr);
           }
           __threadfence();

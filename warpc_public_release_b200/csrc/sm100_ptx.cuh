@@ -319,6 +319,14 @@ WB_DEV void mbar_arrive_expect_tx_if(uint32_t issuer, uint32_t bar, uint32_t tx)
 WB_DEV void mbar_arrive_if(uint32_t issuer, uint32_t bar) {
   asm volatile("{\n\t.reg .pred e;\n\tsetp.ne.u32 e, %0, 0;\n\t@e mbarrier.arrive.shared::cta.b64 _, [%1];\n\t}" ::"r"(issuer), "r"(bar) : "memory");
 }
+// The same arrival ordering nothing: for the accumulator's release.  What the MMA issuer must not overtake is this warp's
+// tcgen05.ld of the accumulator, which tcgen05.wait::ld and the tcgen05 fences either side of the barrier order; a releasing
+// arrival would also wait for the warp's global stores of the tile (measured: 2 000-3 500 cycles with a tile's stores in flight).
+WB_DEV void mbar_arrive_cluster_relaxed_if(uint32_t issuer, uint32_t bar) {
+  asm volatile("{\n\t.reg .pred e;\n\tsetp.ne.u32 e, %0, 0;\n\t@e mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%1];\n\t}" ::"r"(issuer),
+               "r"(bar)
+               : "memory");
+}
 WB_DEV void mbar_arrive_cluster_if(uint32_t issuer, uint32_t bar) {
   asm volatile("{\n\t.reg .pred e;\n\tsetp.ne.u32 e, %0, 0;\n\t@e mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%1];\n\t}" ::"r"(issuer),
                "r"(bar)
