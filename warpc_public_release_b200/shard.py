@@ -32,7 +32,7 @@ def slab_variant(m_local, n, k, pin_large=True, staged=False):
     waves, over 8 GPUs 3.46, a seventh of the machine idle at the end.  There the rule's own program, re-tiled to
     256 x 128 on a fixed grid (6.9 waves again), is the faster one: 2048 x 16384 x 16384 on one GPU, twenty launches
     back to back, 721-870 us against 762-984 (cuBLASLt 727-854); on eight GPUs in one job, the slowest rank's time,
-    836-905 against 957-1003 once the GPUs have been working (810 against 784 on GPUs that had idled).  (Dealing the poorly filled last wave's k-steps out
+    820-842 against 802-1060 over sixty launches back to back (779 against 774 on GPUs that had idled).  (Dealing the poorly filled last wave's k-steps out
     stream-K does not pay at the large tile: 965 us against 757 -- the partial tiles' 256 KB stores are exposed and
     clusters stop sharing operand panels in step.)  `staged`: the caller needs a program that stores through staging
     copies (further copies of C filled by the kernel itself), which the re-tiled one does not: the large program then."""
