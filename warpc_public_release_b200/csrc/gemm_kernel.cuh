@@ -97,6 +97,11 @@ struct Cfg {
   // control, no K shared between CTAs, no further copies of C.  The launches that last ten to thirty microseconds are
   // these, and the code they never run is not in their kernel.
   static constexpr bool SIMPLE = SIMPLE_;
+  // Simple instances of the small tiles rehearse their epilogue (epi_direct_tile) while the first k loop runs: measured,
+  // one tile a CTA, 1024^3 7.6 -> 7.2 us (two blocks a warp: the code runs once), 1536^3 10.7 -> 10.4 (four blocks: the
+  // loop's second turn finds it fetched anyway); eight blocks (256 x 128) gain nothing at 2048^3 and lose 0.45 us on the
+  // fixed grid's four tiles at 4096 x 4096 x 1024, so those do not.
+  static constexpr bool REHEARSE = SIMPLE_ && (TN_ == 256 ? 2 : 1) * ((CG_ == 2 && TN_ == 64 ? TM_ / 2 : TM_) / 32) <= 4;
   static constexpr int KSUB = KSUB_;  // k-steps a ring round, fixed at compile time (0: the launch says)
   // the one scheduling mode (SCHED_*) the instance is compiled for, or -1: the launch says.  An instance of one mode holds
   // no other mode's code (the walker's, the scheduler warp's, the epilogue's hand-offs), and none for further copies of C
@@ -148,6 +153,7 @@ struct Ctrl {
   uint32_t sched_slot[2];  // valid, first CTA of the cancelled cluster
   uint32_t tmem_base;
   uint32_t abort;
+  uint32_t scratch;        // where a rehearsal of the epilogue (below) puts its stores
   // a replicated C: the epilogue hands each tile it has stored to the forwarding warp through two slots
   uint64_t fwd_full[2];    // the four epilogue warps' stores of the slot's tile are written
   uint64_t fwd_empty[2];   // the forwarding warp has taken the slot's coordinates
@@ -508,19 +514,25 @@ WB_DEV void fwd_copy_tile(const KParams& p, int row, int col, uint32_t lane) {
 
 // Straight from the registers: register j of a block is row y + j, the warp's lanes are 32
 // consecutive columns, so each register goes out as one 128-byte row segment.
+// `rehearsal` (a generic address of a word of this CTA's shared memory, or null): run the same instructions with every
+// store going to that word and the accumulator not released.  A launch of one tile a CTA runs this code exactly once, at
+// its very end, and pays for fetching it then; run once before, while the warp only waits for the k loop, it is in the
+// instruction caches when it counts.  What the rehearsal reads from tensor memory is whatever is there.
 template <class C>
-WB_DEV void epi_direct_tile(const KParams& p, uint32_t tbase, int row, int col, int q, uint32_t lane, uint32_t acc_empty_addr) {
+WB_DEV void epi_direct_tile(const KParams& p, uint32_t tbase, int row, int col, int q, uint32_t lane, uint32_t acc_empty_addr,
+                            float* rehearsal = nullptr) {
   uint32_t v[2][C::EPI_ROWS];
-  const size_t ld = size_t(p.ldc);
+  const size_t ld = rehearsal ? size_t(0) : size_t(p.ldc);
   // whole tiles only (the host refuses the store from the registers otherwise): no bounds to test
   auto store = [&](int i, const uint32_t* regs) {
     int y, x;
     epi_coords<C>(row, col, q, i, y, x);
-    float* dst = p.C + size_t(y) * ld + size_t(x) + lane;
+    float* dst = rehearsal ? rehearsal : p.C + size_t(y) * ld + size_t(x) + lane;
 #pragma unroll
     for (int j = 0; j < C::EPI_ROWS; ++j) dst[size_t(j) * ld] = __uint_as_float(regs[j]);
   };
   auto release = [&]() {
+    if (rehearsal) return;
     tc_fence_before();
     __syncwarp();
     if constexpr (C::CG == 2) mbar_arrive_cluster_relaxed_if(lane == 0 ? 1u : 0u, acc_empty_addr);
@@ -549,6 +561,14 @@ WB_DEV void epi_direct_tile(const KParams& p, uint32_t tbase, int row, int col, 
       store(i, v[i & 1]);
     }
   }
+}
+
+// One copy of that code per kernel, called (not inlined) from both places a simple instance uses it: the rehearsal warms
+// the instruction caches only if the real store runs the same instructions at the same addresses.
+template <class C>
+__device__ __noinline__ void epi_direct_tile_once(const KParams& p, uint32_t tbase, int row, int col, int q, uint32_t lane, uint32_t acc_empty_addr,
+                                                  float* rehearsal) {
+  epi_direct_tile<C>(p, tbase, row, col, q, lane, acc_empty_addr, rehearsal);
 }
 
 // ------------------------------------------------------------------ K shared through a workspace
@@ -893,6 +913,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         if (first_warp && lane == 0) st_relaxed_gpu(p.flags + blockIdx.x, target);
       }
     }
+    if constexpr (C::REHEARSE) {
+      // the epilogue's code once through while there is nothing to do but wait for the first tile's k loop
+      if (have) epi_direct_tile_once<C>(p, tmem_base + (uint32_t(q * 32) << 16), row, col, q, lane, 0u,
+                                        reinterpret_cast<float*>(__cvta_shared_to_generic(size_t(ctrl_at(offsetof(Ctrl, scratch))))));
+    }
     for (; have; have = walk.template next<true>(w)) {
       if (nth != 0) tile_origin<C>(p, w.tile, row, col);
       const uint32_t wide = (p.epi_ring != 0 && walk.is_last(w)) ? ring + uint32_t(q) * uint32_t(C::NBLK) * C::EPI_COPY_BYTES : 0u;
@@ -951,7 +976,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           if (!wait_bar(p, abort_addr, acc_full_bar(acc), acc_phase, ST_WAIT_ACC_FULL, uint32_t(acc))) break;
           tc_fence_after();
           if (first_warp && lane == 0) stamp(p, EV_ACC_READY, nth);
-          epi_direct_tile<C>(p, tbase, row, col, q, lane, acc_empty_addr);
+          if constexpr (C::REHEARSE) epi_direct_tile_once<C>(p, tbase, row, col, q, lane, acc_empty_addr, nullptr);
+          else epi_direct_tile<C>(p, tbase, row, col, q, lane, acc_empty_addr);
         }
       } else if (!shared_k || (sched_of<C>(p) == SCHED_STREAMK && w.kb == 0 && w.ke == p.kt)) {
         // (a tile one cluster computes whole has no other part to wait for or to tell: stored like any tile)
