@@ -680,22 +680,27 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       mbar_init(acc_full_bar(int(lane) - 16), 1);        // one commit
       mbar_init(acc_empty_bar(int(lane) - 16), 4 * CG);  // every epilogue warp of the pair
     } else if (lane == 18) {
-      mbar_init(ctrl_at(offsetof(Ctrl, clc_bar)), 1);
-      mbar_init(ctrl_at(offsetof(Ctrl, sched_full)), 1);
-      // takers of an answer: a producer a CTA, the leader's MMA warp, four epilogue warps a CTA
-      mbar_init(ctrl_at(offsetof(Ctrl, sched_empty)), CG + 1 + 4 * CG);
+      // (the lanes of this warp take their branches one after the other: a simple instance, which has no launch control
+      // and no forwarding warp, leaves those barriers alone, and the tensor maps' prefetch is warp 2's)
+      if constexpr (!C::SIMPLE) {
+        mbar_init(ctrl_at(offsetof(Ctrl, clc_bar)), 1);
+        mbar_init(ctrl_at(offsetof(Ctrl, sched_full)), 1);
+        // takers of an answer: a producer a CTA, the leader's MMA warp, four epilogue warps a CTA
+        mbar_init(ctrl_at(offsetof(Ctrl, sched_empty)), CG + 1 + 4 * CG);
+      }
       st_shared_u32(abort_addr, 0u);
-    } else if (lane == 20 || lane == 21) {
+    } else if (!C::SIMPLE && (lane == 20 || lane == 21)) {
       mbar_init(ctrl_at(offsetof(Ctrl, fwd_full) + 8 * (lane - 20)), 4);   // the four epilogue warps
       mbar_init(ctrl_at(offsetof(Ctrl, fwd_empty) + 8 * (lane - 20)), 1);  // the forwarding warp
-    } else if (lane == 19) {
-      prefetch_tmap(&map_a);
-      prefetch_tmap(&map_b);
-      if constexpr (!C::DIRECT) prefetch_tmap(&map_c), prefetch_tmap(&map_cw);
     }
     fence_mbar_init();
     __threadfence_block();  // the abort word, for this CTA's own warps (the arrival at the barrier below is a relaxed one)
     if (lane == 0) stamp(p, 16, 0);
+  }
+  if (warp == 2 && lane == 0) {
+    prefetch_tmap(&map_a);
+    prefetch_tmap(&map_b);
+    if constexpr (!C::DIRECT) prefetch_tmap(&map_c), prefetch_tmap(&map_cw);
   }
   if (warp == 1) {
     // both CTAs of a pair allocate, each into its own slot word
