@@ -345,9 +345,13 @@ def test_phase_stamps_layout_and_order():
     for cta in range(148):
         e = st[cta]
         leader = cta % 2 == 0
-        # set-up: entry <= barriers initialised (16), tensor memory allocated (17), first tile found (18) <= CTAs met (23) <= set-up done
-        for ev in (16, 17, 18):
+        # set-up: entry <= barriers initialised (16), first tile found (18) <= CTAs met (23) <= set-up done; a pair's tensor
+        # memory is allocated (17) after the arrival at that barrier, before the first MMA (the timer ticks every 32 ns)
+        for ev in (16, 18):
             assert e[ENTRY, 0] <= e[ev, 0] <= e[23, 0], (cta, ev)
+        assert e[ENTRY, 0] <= e[17, 0] <= e[ACC_READY, 0]
+        if leader:
+            assert e[17, 0] <= e[ACC_FREE, 0] + 64
         assert e[23, 0] <= e[SETUP, 0] <= e[LOAD_FIRST, 0]
         for t in range(2):
             assert 0 < e[LOAD_FIRST, t] <= e[LOAD_LAST, t]

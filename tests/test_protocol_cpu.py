@@ -131,6 +131,23 @@ def test_a_leader_that_leaves_before_its_accumulator_is_released_is_caught():
         assert protocol.check(v, *shape, seed=seed, mutate={"mma_no_final_drain": True}, teardown="cluster") > 0
 
 
+@pytest.mark.parametrize("mutation,needle,shape", [
+    ("mma_no_tmem_wait", "which is not allocated yet", (1024, 1024, 128)),
+    ("mma_no_tmem_wait", "which is not allocated yet", (2048, 2048, 128)),
+    ("epilogue_no_tmem_wait", "rehearses its epilogue on tensor memory that is not allocated", (1536, 1536, 128)),
+])
+def test_tensor_memory_allocated_after_the_set_up_barrier_has_its_own_hand_offs(mutation, needle, shape):
+    # a pair's CTAs allocate after arriving at the set-up barrier: the leader's MMA lane waits for the other CTA's warp 1
+    # on a barrier of its own, each CTA's epilogue warps for their own warp 1 at a named barrier; without either wait
+    # tensor memory is touched before it exists
+    v = w.choose(*shape)
+    assert protocol.check(v, *shape, seed=2) > 0
+    with pytest.raises(protocol.Violation) as e:
+        for seed in range(12):
+            protocol.check(v, *shape, seed=seed, mutate={mutation: True})
+    assert needle in str(e.value)
+
+
 def test_full_instances_keep_the_cluster_barrier():
     # launch control's last answer is released on the first CTA's barrier by takers of both CTAs, and nobody waits for
     # that: letting those CTAs go alone is a finding

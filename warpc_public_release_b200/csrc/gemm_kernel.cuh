@@ -154,6 +154,7 @@ struct Ctrl {
   uint32_t tmem_base;
   uint32_t abort;
   uint32_t scratch;        // where a rehearsal of the epilogue (below) puts its stores
+  uint64_t tmem_ready;     // pair leader's: the other CTA's tensor memory is allocated
   // a replicated C: the epilogue hands each tile it has stored to the forwarding warp through two slots
   uint64_t fwd_full[2];    // the four epilogue warps' stores of the slot's tile are written
   uint64_t fwd_empty[2];   // the forwarding warp has taken the slot's coordinates
@@ -688,6 +689,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         // takers of an answer: a producer a CTA, the leader's MMA warp, four epilogue warps a CTA
         mbar_init(ctrl_at(offsetof(Ctrl, sched_empty)), CG + 1 + 4 * CG);
       }
+      if constexpr (CG == 2) mbar_init(ctrl_at(offsetof(Ctrl, tmem_ready)), 1);  // the other CTA's warp 1
       st_shared_u32(abort_addr, 0u);
     } else if (!C::SIMPLE && (lane == 20 || lane == 21)) {
       mbar_init(ctrl_at(offsetof(Ctrl, fwd_full) + 8 * (lane - 20)), 4);   // the four epilogue warps
@@ -702,8 +704,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     prefetch_tmap(&map_b);
     if constexpr (!C::DIRECT) prefetch_tmap(&map_c), prefetch_tmap(&map_cw);
   }
-  if (warp == 1) {
-    // both CTAs of a pair allocate, each into its own slot word
+  // (a pair's CTAs allocate their tensor memory after they have arrived at the barrier below)
+  if (CG == 1 && warp == 1) {
     tmem_alloc<CG>(ctrl_at(offsetof(Ctrl, tmem_base)), uint32_t(C::pow2_ge(C::NCOLS * nbuf)));
     tmem_relinquish<CG>();
     if (lane == 0) stamp(p, 17, 0);
@@ -723,7 +725,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     // tcgen05 fences either side and the abort word by warp 3's CTA-scope fence.  The arrival itself orders nothing
     // more: a releasing one put the pair's meeting at 1.06 us after entry, this one at 0.80.
     cluster_arrive_relaxed();
+    // The paired tcgen05.alloc (each CTA into its own slot word) takes 0.15 us longer than the barriers' initialisation,
+    // and nothing needs it before the first MMA, a microsecond on: warp 1 allocates between its arrival and its wait, so
+    // the pair meets without it.  Its readers are told otherwise: this CTA's epilogue warps at a named barrier, the
+    // leader's MMA lane (which writes into both CTAs' tensor memory) at a barrier of its own that the other CTA's
+    // warp 1 arrives at.
+    if (warp == 1) {
+      tmem_alloc<CG>(ctrl_at(offsetof(Ctrl, tmem_base)), uint32_t(C::pow2_ge(C::NCOLS * nbuf)));
+      tmem_relinquish<CG>();
+      if (lane == 0) stamp(p, 17, 0);
+      tc_fence_before();
+      named_bar_arrive(3, 160);
+    }
     cluster_wait();
+    // (a relaxed arrival: tcgen05.alloc has returned, and the tcgen05 fences either side order it against the MMAs)
+    if (warp == 1 && !leader) mbar_arrive_cluster_relaxed_if(lane == 0 ? 1u : 0u, mapa(ctrl_at(offsetof(Ctrl, tmem_ready)), 0));
   } else {
     __syncthreads();
   }
@@ -732,6 +748,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   // nothing above touched global memory (a timing build's entry stamp aside); everything below
   // may read what the grid before this one wrote
   griddep_wait();
+  if (CG == 2 && warp >= 4) {
+    named_bar_sync(3, 160);
+    tc_fence_after();
+  }
   const uint32_t tmem_base = warp_uniform(ld_shared_u32(ctrl_at(offsetof(Ctrl, tmem_base))));
   if (threadIdx.x == 0) stamp(p, EV_SETUP, 0);
 
@@ -798,6 +818,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       constexpr uint32_t STAGE16 = C::STAGE_BYTES >> 4, ATOM16 = uint32_t((C::MMA_M / CG) * 128) >> 4;
       const uint32_t a_lo0 = ((ring & 0x3FFFFu) >> 4) | (1u << 16);  // stage 0's A tile (the MMA's B operand)
       const uint32_t b_lo0 = a_lo0 + (C::A_BYTES >> 4);              // stage 0's B^T tile (the MMA's A operand)
+      // the other CTA's half of every accumulator exists (long since: the first operands are still on their way)
+      if (CG == 2 && have) ok = wait_bar<false, false>(p, abort_addr, ctrl_at(offsetof(Ctrl, tmem_ready)), 0u, ST_WAIT_ACC_EMPTY, 0x200u);
       for (; ok && have; have = ok && walk.template next<false>(w)) {
         if (!wait_bar<false, false>(p, abort_addr, acc_empty_bar(acc), acc_phase ^ 1u, ST_WAIT_ACC_EMPTY, uint32_t(acc))) {
           ok = false;

@@ -152,6 +152,10 @@ WB_DEV void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.rela
 WB_DEV void named_bar_sync(uint32_t id, uint32_t nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
+// a warp that only announces (it does not wait for the others of the barrier)
+WB_DEV void named_bar_arrive(uint32_t id, uint32_t nthreads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
 
 // ---------------------------------------------------------------- flags in global memory
 WB_DEV uint32_t ld_relaxed_gpu(const uint32_t* p) {

@@ -16,6 +16,8 @@ step.  It reports
     an epilogue read of an accumulator whose MMAs are not complete,
   * a k-step of a tile multiplied twice or never, a tile stored twice or added to before it
     was stored (split-K, stream-K),
+  * an MMA into, or an epilogue read of, tensor memory that its CTA's warp 1 has not allocated yet (a pair's CTAs
+    allocate after their arrival at the set-up barrier, so the pair meets without waiting for it),
   * roles that can no longer move (what would be a hang on the GPU), and CTAs that would leave
     with copies or commits still in flight,
   * anything that reaches a CTA after it has left: an arrival on one of its barriers, a load landing in its ring, an
@@ -101,6 +103,7 @@ class Model:
         self.tile_log = defaultdict(list)  # tile -> [(kind, frozenset(ksteps))]
         self.clc_next = min(self.clusters, RESIDENT_CLUSTERS)  # first cluster not resident at launch
         self.sched_slot = {}
+        self.tmem = set()         # CTAs whose tensor memory is allocated (warp 1 of each, after the set-up barrier has its arrival)
         for cta in range(li.grid):
             for r in range(self.rounds):
                 self.bars[cta, "full", r] = Barrier("CTA %d full[%d]" % (cta, r), self.mut.get("full_count", 1))
@@ -111,6 +114,7 @@ class Model:
             for s_ in range(2):
                 self.bars[cta, "fwd_full", s_] = Barrier("CTA %d fwd_full[%d]" % (cta, s_), 4)
                 self.bars[cta, "fwd_empty", s_] = Barrier("CTA %d fwd_empty[%d]" % (cta, s_), 1)
+            self.bars[cta, "tmem_ready", 0] = Barrier("CTA %d tmem_ready" % cta, 1)
             self.bars[cta, "sched_full", 0] = Barrier("CTA %d sched_full" % cta, 1)
             self.bars[cta, "sched_empty", 0] = Barrier("CTA %d sched_empty" % cta, self.cg + 1 + 4 * self.cg)
             for s in range(li.depth):
@@ -198,11 +202,17 @@ class Model:
         cg, c = self.cg, cta // self.cg
         ctas = [c * cg + r for r in range(cg)]
         rnd, use_index, acc, acc_use = 0, 0, 0, 0
+        yield ("alloc", cta)   # the issuing warp allocates its own CTA's tensor memory itself
+        yield ("tmemwait", cta)
+        waited = cg == 1 or bool(self.mut.get("mma_no_tmem_wait"))
         for item in self.works(cta, "mma"):
             if item[0] != "work":
                 yield item
                 continue
             _, tile, kb, ke, _last = item
+            if not waited:   # a pair's MMAs write into both CTAs' tensor memory
+                yield ("wait", (cta, "tmem_ready", 0), 0)
+                waited = True
             if not self.mut.get("no_acc_empty_wait"):
                 yield ("wait", (cta, "acc_empty", acc), acc_use - 1)
             first, kk = True, kb
@@ -227,10 +237,20 @@ class Model:
             if acc == self.nbuf:
                 acc, acc_use = 0, acc_use + 1
 
+    def allocator(self, cta):
+        """Warp 1 of a pair's second CTA: allocates, then tells the leader's MMA lane."""
+        yield ("alloc", cta)
+        yield ("tmemwait", cta)
+        yield ("arrive", (cta - cta % self.cg, "tmem_ready", 0), 0)
+
     def epilogue(self, cta, warp):
         li, cg, c = self.li, self.cg, cta // self.cg
         leader, rank = c * cg, cta % cg
         acc, acc_use, nth, handed = 0, 0, 0, 0
+        if not self.mut.get("epilogue_no_tmem_wait"):
+            yield ("tmemwait", cta)   # the named barrier warp 1 arrives at once the CTA's tensor memory exists
+        if programs.kernel_is_simple(li.kernel_id) and self.blocks_per_warp() <= 4:
+            yield ("rehearse", cta, warp)   # a simple instance's pass through its epilogue on whatever tensor memory holds
         shared_k = (not li.direct) and li.sched in (SCHED_SPLITK, SCHED_STREAMK)
         ws_k = bool(li.direct) and li.sched in (SCHED_SPLITK, SCHED_STREAMK)   # the same sharing through a workspace
         # hand-off words count launches; every epilogue thread reads its CTA's word before any of them
@@ -372,6 +392,8 @@ class Model:
             return index < 0 or self.bars[key].passed(index)
         if kind == "flagwait":
             return self.flags[ev[1]] == ev[2]
+        if kind == "tmemwait":
+            return ev[1] in self.tmem
         if kind == "nbar":
             _, cta, seq, warp = ev
             self.nbar[cta, seq].add(warp)
@@ -381,6 +403,11 @@ class Model:
             self.bars[ev[1]].arrive(ev[2])
         elif kind == "flag":
             self.flags[ev[1]] = ev[2]
+        elif kind == "alloc":   # tcgen05.alloc returns when the columns are free: at some later time
+            self.asyncs.append(lambda cta=ev[1]: self.tmem.add(cta))
+        elif kind == "rehearse":
+            if ev[1] not in self.tmem:
+                raise Violation("CTA %d warp %d rehearses its epilogue on tensor memory that is not allocated yet" % (ev[1], ev[2]))
         elif kind == "load":
             _, cta, slot, tile, kstep, bar = ev
             if self.slots[cta, slot] is not None:
@@ -397,6 +424,8 @@ class Model:
             _, c, acc, ctas, slot, tile, kstep, first = ev
             for x in ctas:
                 self.still_here(x, "cluster %d multiplies k-step %d from CTA %d's ring into its tensor memory" % (c, kstep, x))
+                if x not in self.tmem:
+                    raise Violation("cluster %d multiplies k-step %d into CTA %d's tensor memory, which is not allocated yet" % (c, kstep, x))
                 have = self.slots[x, slot]
                 want_tile = tile - tile % self.cg + x % self.cg
                 if have is None or have[0] != "full" or have[1] != want_tile or have[2] != kstep:
@@ -426,6 +455,8 @@ class Model:
             self.commit_queue[cta].append(fire)
         elif kind == "read":
             _, c, acc, leader, tile, how, warp, cta, wide = ev
+            if cta not in self.tmem:
+                raise Violation("CTA %d warp %d reads tensor memory that is not allocated yet" % (cta, warp))
             if wide:
                 busy = [(slot, have) for (x, slot), have in self.slots.items() if x == cta and have is not None]
                 if busy:
@@ -508,6 +539,8 @@ class Model:
         for cta in range(started):
             leader = cta % self.cg == 0
             roles.append(["CTA %d producer" % cta, self.producer(cta), None, cta])
+            if not leader:
+                roles.append(["CTA %d warp 1" % cta, self.allocator(cta), None, cta])
             if leader:
                 roles.append(["CTA %d MMA issuer" % cta, self.mma(cta), None, cta])
                 if self.li.sched == SCHED_CLC:
