@@ -718,6 +718,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   int row = 0, col = 0;
   if (have) tile_origin<C>(p, w.tile, row, col);
   if (threadIdx.x == 0) stamp(p, 18, 0);
+  // (the producer's constants too: its first load goes out the sooner after the pair has met)
+  const uint64_t load_policy = (warp != 0) ? 0ull : ((((WB_DEBUG_WORD(p) >> 4) ^ uint32_t(p.l2_hints)) & 2u) ? l2_policy_evict_last() : l2_policy_evict_normal());
+  const uint32_t full_leader0 = (CG == 2) ? mapa(full_bar(0), 0) : full_bar(0);
   tc_fence_before();
   if constexpr (CG == 2) {
     // What one CTA needs to see of the other's set-up is its barriers' initialisation, which warp 3 has fenced
@@ -752,7 +755,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     named_bar_sync(3, 160);
     tc_fence_after();
   }
-  const uint32_t tmem_base = warp_uniform(ld_shared_u32(ctrl_at(offsetof(Ctrl, tmem_base))));
+  // (warp 1 and the epilogue warps use it; a pair's other warps may be here before it is written)
+  const uint32_t tmem_base = (warp == 1 || warp >= 4) ? warp_uniform(ld_shared_u32(ctrl_at(offsetof(Ctrl, tmem_base)))) : 0u;
   if (threadIdx.x == 0) stamp(p, EV_SETUP, 0);
 
   // ---------------------------------------------------------------- roles
@@ -765,8 +769,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       uint32_t stage = 0, phase = 0;
       int nth = 0;
       bool ok = true;
-      const uint64_t load_policy = (((WB_DEBUG_WORD(p) >> 4) ^ uint32_t(p.l2_hints)) & 2u) ? l2_policy_evict_last() : l2_policy_evict_normal();
-      const uint32_t full_leader0 = (CG == 2) ? mapa(full_bar(0), 0) : full_bar(0);
       for (; ok && have; have = ok && walk.template next<false>(w)) {
         if (nth != 0) tile_origin<C>(p, w.tile, row, col);
         // a pair's CTAs sit side by side: same rows, so they split the A tile between them
